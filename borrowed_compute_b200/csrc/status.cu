@@ -1,0 +1,21 @@
+// The library's last error text and its version, readable from any binding.
+#include <stdarg.h>
+#include <stdio.h>
+
+#include "common.cuh"
+
+static thread_local char g_error[512] = "";
+
+void bc_set_error(const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_error, sizeof(g_error), fmt, ap);
+    va_end(ap);
+}
+
+extern "C" const char* bc_last_error() { return g_error; }
+
+// Bumped when an exported signature changes, so a stale build is never called.
+extern "C" int bc_abi_version() { return 1; }
+
+extern "C" int bc_page_size() { return BC_PAGE; }

@@ -1,0 +1,198 @@
+"""The engine: a loaded model, its cache, and the one step function everything runs through.
+
+``step`` takes a batch of sequences that either all start (their prompts, of unequal
+lengths, in one step) or all go on, runs exactly the tokens it is given as one batch
+against what earlier steps left in the cache, and returns float32 scores at the wanted
+places.  Generation, trace replay and the benchmark all call it.  The reference's
+counterpart feeds one sequence a call (crates/bc-mesh/src/engine.rs:287-363;
+crates/bc-infer/src/model.rs:285-352) and guards the same things: positions may not skip
+(model.rs:303-305), the context may not overflow (306-308), tokens must lie in the
+vocabulary (274-276).
+"""
+
+from __future__ import annotations
+
+from typing import Any, Dict, List, Mapping, Optional, Sequence
+
+import numpy as np
+import torch
+
+from .. import ops
+from ..cache import PAGE, PagedCache
+from ..config.errors import CacheError
+from ..parts.base import Runtime, StepContext
+from ..weights import TensorSource, load_tensors, random_tensors, read_config_json
+from .batch import StepEntry, StepPlan, plan_step
+from .model import DecoderModel, model_for_config
+
+DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32,
+          torch.bfloat16: torch.bfloat16, torch.float32: torch.float32}
+
+
+class Engine:
+    def __init__(self, config: Mapping[str, Any], model: DecoderModel, typed_config: Any, rt: Runtime, max_tokens: int,
+                 max_slots: int, max_seq: int):
+        self.config, self.model, self.typed_config, self.rt = dict(config), model, typed_config, rt
+        self.vocab_size = model.spec.vocab_size
+        self.max_seq = max_seq
+        needs, states, memory_of = model.memory_needs()
+        self.cache = PagedCache(rt, needs, states, memory_of, max_tokens=max_tokens, n_slots=max_slots, max_seq=max_seq)
+        self._ints: Optional[torch.Tensor] = None
+        self._host_ints: Optional[torch.Tensor] = None
+        self._staged: Optional[torch.cuda.Event] = None
+        self.steps_run = 0
+
+    # ------------------------------------------------------------------------ construction
+    @staticmethod
+    def _runtime(dtype, device) -> Runtime:
+        if dtype not in DTYPES:
+            raise ValueError(f"dtype {dtype!r} is neither bfloat16 nor float32")
+        dev = torch.device(device)
+        if dev.type != "cuda":
+            raise RuntimeError(f"the engine runs on a CUDA device only, not on {dev}")
+        if not torch.cuda.is_available():
+            raise RuntimeError("no CUDA device is available; there is no CPU path")
+        ops.lib()  # fail now, and loudly, if the kernels cannot be had
+        return Runtime(device=dev, dtype=DTYPES[dtype])
+
+    @classmethod
+    def _sized(cls, config, model, typed, rt, max_tokens, max_slots, max_seq) -> "Engine":
+        limit = model.spec.max_positions
+        max_seq = min(limit, max_seq) if max_seq else min(limit, 8192)
+        if max_tokens is None:
+            max_tokens = min(max_seq * (max_slots or 8), 1 << 17)
+        max_tokens = -(-int(max_tokens) // PAGE) * PAGE
+        max_seq = min(max_seq, max_tokens)
+        if max_slots is None:
+            max_slots = max(1, min(max_tokens // PAGE, 1024))
+        rt.max_positions = max_seq
+        return cls(config, model, typed, rt, max_tokens, max_slots, max_seq)
+
+    @classmethod
+    def from_folder(cls, folder: str, dtype="bfloat16", device="cuda:0", max_tokens: Optional[int] = None,
+                    max_slots: Optional[int] = None, max_seq: Optional[int] = None) -> "Engine":
+        """Loads ``config.json`` and the safetensors of a model folder."""
+        config = read_config_json(folder)
+        typed, model = model_for_config(config)
+        rt = cls._runtime(dtype, device)
+        eng = cls._sized(config, model, typed, rt, max_tokens, max_slots, max_seq)
+        model.load(load_tensors(model.expected_tensors(), TensorSource(folder), rt), rt)
+        return eng
+
+    @classmethod
+    def from_random(cls, config: Mapping[str, Any], seed: int, dtype="bfloat16", device="cuda:0",
+                    max_tokens: Optional[int] = None, max_slots: Optional[int] = None, max_seq: Optional[int] = None) -> "Engine":
+        """Random weights drawn on the device, without a folder (other values than a
+        folder written from the same seed holds: the device's generator differs)."""
+        typed, model = model_for_config(config)
+        rt = cls._runtime(dtype, device)
+        eng = cls._sized(config, model, typed, rt, max_tokens, max_slots, max_seq)
+        expected = model.expected_tensors()
+        tensors = {}
+        for name, spec in expected.items():
+            if spec.optional:
+                continue
+            want = torch.float32 if spec.role == "vector" else (torch.int32 if spec.role == "index" else rt.dtype)
+            tensors.update(random_tensors({name: spec}, seed, want, rt.device))
+        model.load(tensors, rt)
+        return eng
+
+    @classmethod
+    def from_tensors(cls, config: Mapping[str, Any], tensors: Mapping[str, torch.Tensor], dtype="bfloat16", device="cuda:0",
+                     max_tokens: Optional[int] = None, max_slots: Optional[int] = None, max_seq: Optional[int] = None) -> "Engine":
+        """Tensors given by name in memory, checked like a folder's."""
+        from ..weights.loader import check_tensors, device_type
+
+        typed, model = model_for_config(config)
+        rt = cls._runtime(dtype, device)
+        eng = cls._sized(config, model, typed, rt, max_tokens, max_slots, max_seq)
+        expected = model.expected_tensors()
+        check_tensors(expected, {n: (t.dtype, tuple(t.shape)) for n, t in tensors.items()}, "the given tensors")
+        model.load({n: tensors[n].to(device=rt.device, dtype=device_type(s, tensors[n].dtype, rt)).contiguous()
+                    for n, s in expected.items() if n in tensors}, rt)
+        return eng
+
+    # ------------------------------------------------------------------------------- slots
+    def acquire(self) -> int:
+        """A slot for a new sequence; its state is zero and it holds no positions."""
+        return self.cache.acquire()
+
+    def release(self, slot: int) -> None:
+        """Gives a sequence's slot and pages back."""
+        self.cache.release(slot)
+
+    def length(self, slot: int) -> int:
+        return self.cache.slots.length(slot)
+
+    def rollback(self, slot: int, length: int) -> None:
+        """Cuts a sequence back to ``length`` positions; the next step writes from there."""
+        self.cache.slots.rollback(slot, length)
+
+    # -------------------------------------------------------------------------------- step
+    def _stage(self, plan: StepPlan) -> Dict[str, torch.Tensor]:
+        packed = plan.packed()
+        n = packed.size
+        if self._ints is None or self._ints.numel() < n:
+            cap = max(4096, 2 * n)
+            self._ints = torch.empty(cap, dtype=torch.int32, device=self.rt.device)
+            self._host_ints = torch.empty(cap, dtype=torch.int32).pin_memory()
+            self._staged = None
+        if self._staged is not None:
+            self._staged.synchronize()   # the last copy out of the pinned buffer is done
+        self._host_ints[:n].copy_(torch.from_numpy(packed))
+        self._ints[:n].copy_(self._host_ints[:n], non_blocking=True)
+        if self._staged is None:
+            self._staged = torch.cuda.Event()
+        self._staged.record()
+        views, at = {}, 0
+        for name, size in plan.layout():
+            views[name] = self._ints[at:at + size]
+            at += size
+        return views
+
+    def check_entries(self, entries: Sequence[StepEntry]) -> List[int]:
+        """The guards of a step; returns every entry's start position."""
+        starts = []
+        for e in entries:
+            start = self.cache.slots.length(e.slot)   # raises if the slot is not held
+            if len(e.tokens) == 0:
+                raise ValueError(f"slot {e.slot} brings no tokens")
+            if start + len(e.tokens) > self.max_seq:
+                raise CacheError(f"{start + len(e.tokens)} tokens are past the {self.max_seq} positions a sequence can hold")
+            for t in e.tokens:
+                if not 0 <= int(t) < self.vocab_size:
+                    raise ValueError(f"token {t} is outside the vocabulary")
+            starts.append(start)
+        return starts
+
+    def step(self, entries: Sequence[StepEntry], pad_rows_to: int = 1) -> torch.Tensor:
+        """Runs the given tokens of every entry as one batch from the cache and returns
+        the scores [wanted, vocab] (float32, on the device) at the wanted places, in entry
+        order then ``want`` order.  ``pad_rows_to`` adds rows that belong to no sequence;
+        they change no result."""
+        starts = self.check_entries(entries)
+        plan = plan_step(entries, starts, pad_rows_to)
+        for e, start in zip(entries, starts):
+            self.cache.slots.reserve(e.slot, start + len(e.tokens), rows=len(e.tokens))
+        self.cache.sync_tables()
+        v = self._stage(plan)
+        ctx = StepContext(
+            rows=plan.padded_rows, seqs=plan.seqs, tokens=v["tokens"], row_pos=v["row_pos"], row_slot=v["row_slot"],
+            seq_rows=v["seq_rows"], seq_slot=v["seq_slot"], seq_start=v["seq_start"], max_new=plan.max_new,
+            max_total=plan.max_total, decode=plan.decode, host_seq_rows=tuple(int(x) for x in plan.seq_rows),
+            host_seq_slot=tuple(int(x) for x in plan.seq_slot), host_seq_start=tuple(int(x) for x in plan.seq_start))
+        scores = self.model.forward(ctx, self.cache, v["want_rows"], len(plan.want_rows))
+        for e, start in zip(entries, starts):
+            self.cache.slots.commit(e.slot, start + len(e.tokens))
+        self.steps_run += 1
+        return scores
+
+    # ---------------------------------------------------------------------------- accounts
+    def weight_bytes(self) -> int:
+        seen, total = set(), 0
+        for _, part in self.model._named_parts():
+            for v in vars(part).values():
+                if isinstance(v, torch.Tensor) and v.data_ptr() not in seen:
+                    seen.add(v.data_ptr())
+                    total += v.numel() * v.element_size()
+        return total

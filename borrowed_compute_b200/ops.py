@@ -1,0 +1,218 @@
+"""Python faces of the CUDA launchers: argument checks, then one call into the kernel library.
+
+Every function launches on torch's current CUDA stream and allocates nothing unless it
+says so.  There is no CPU path and no library stand-in: a tensor that is not on a CUDA
+device, or a kernel library that cannot be loaded, raises.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from .csrc import build as _build
+
+PAGE = 64  # tokens per cache page; checked against the library at load
+
+EPI_STORE, EPI_STORE_F32, EPI_ADD_F32, EPI_SWIGLU = 0, 1, 2, 3
+
+_c_int, _c_float, _c_void_p = ctypes.c_int, ctypes.c_float, ctypes.c_void_p
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+_checked_page = False
+
+
+def lib() -> ctypes.CDLL:
+    global _checked_page
+    handle = _build.load()
+    if not _checked_page:
+        handle.bc_page_size.restype = _c_int
+        if handle.bc_page_size() != PAGE:
+            raise KernelError(f"the kernel library pages {handle.bc_page_size()} tokens, the package {PAGE}")
+        _checked_page = True
+    return handle
+
+
+def _stream() -> _c_void_p:
+    return _c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _ptr(t: Optional[torch.Tensor]) -> _c_void_p:
+    return _c_void_p(0 if t is None else t.data_ptr())
+
+
+def _need(t: torch.Tensor, name: str, dtype=None) -> None:
+    if not isinstance(t, torch.Tensor) or not t.is_cuda:
+        raise KernelError(f"{name} must be a CUDA tensor (there is no CPU path)")
+    if not t.is_contiguous():
+        raise KernelError(f"{name} must be contiguous")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name} must be {dtype}, got {t.dtype}")
+
+
+def _suffix(dtype: torch.dtype) -> str:
+    if dtype == torch.float32:
+        return "f32"
+    if dtype == torch.bfloat16:
+        return "bf16"
+    raise KernelError(f"no kernels for {dtype}: float32 and bfloat16 only")
+
+
+def _call(fn, *args) -> None:
+    status = fn(*args)
+    if status != 0:
+        msg = lib().bc_last_error()
+        raise KernelError(f"{fn.__name__} failed ({status}): {msg.decode() if msg else ''}")
+
+
+def _fn(name: str):
+    f = getattr(lib(), name)
+    f.restype = _c_int
+    return f
+
+
+# ---------------------------------------------------------------------------------- row-wise
+
+def embed(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor) -> None:
+    """out[r, :] = table[tokens[r], :] widened to float32."""
+    _need(table, "table")
+    _need(tokens, "tokens", torch.int32)
+    _need(out, "out", torch.float32)
+    rows, (V, E) = tokens.numel(), table.shape
+    if out.shape != (rows, E):
+        raise KernelError(f"embed: out is {tuple(out.shape)}, wanted {(rows, E)}")
+    _call(_fn("bc_embed_" + _suffix(table.dtype)), _ptr(table), _ptr(tokens), _ptr(out), _c_int(rows), _c_int(E), _c_int(V), _stream())
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, eps: float, gather: Optional[torch.Tensor] = None) -> None:
+    """out[i] = x[gather[i] or i] * rsqrt(mean(x^2) + eps) * weight; x and weight float32."""
+    _need(x, "x", torch.float32)
+    _need(weight, "weight", torch.float32)
+    _need(out, "out")
+    E = x.shape[-1]
+    rows = out.shape[0]
+    if weight.numel() != E or out.shape[-1] != E:
+        raise KernelError(f"rmsnorm: widths differ: x {E}, weight {weight.numel()}, out {out.shape[-1]}")
+    if gather is not None:
+        _need(gather, "gather", torch.int32)
+        if gather.numel() != rows:
+            raise KernelError("rmsnorm: gather and out differ in rows")
+    elif x.shape[0] != rows:
+        raise KernelError("rmsnorm: x and out differ in rows")
+    _call(_fn("bc_rmsnorm_" + _suffix(out.dtype)), _ptr(x), _ptr(weight), _ptr(out), _ptr(gather), _c_int(rows), _c_int(E),
+          _c_float(eps), _stream())
+
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    """out[r, j] = silu(gate_up[r, j]) * gate_up[r, F + j]."""
+    _need(gate_up, "gate_up")
+    _need(out, "out", gate_up.dtype)
+    rows, F = out.shape
+    if gate_up.shape != (rows, 2 * F):
+        raise KernelError(f"swiglu: gate_up is {tuple(gate_up.shape)}, wanted {(rows, 2 * F)}")
+    _call(_fn("bc_swiglu_" + _suffix(out.dtype)), _ptr(gate_up), _ptr(out), _c_int(rows), _c_int(F), _stream())
+
+
+def rope_append(qkv: torch.Tensor, cos_sin: Optional[torch.Tensor], row_pos: torch.Tensor, row_slot: torch.Tensor,
+                page_table: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, heads: int, kv_heads: int, head_dim: int,
+                pairing: int, write_cache: bool = True) -> None:
+    """Rotates q and k of the fused projection in place by each row's position and writes
+    rotated k and v into the row's cache page.  k_cache, v_cache: [pages, kv_heads, PAGE, head_dim]."""
+    _need(qkv, "qkv")
+    _need(row_pos, "row_pos", torch.int32)
+    _need(row_slot, "row_slot", torch.int32)
+    _need(page_table, "page_table", torch.int32)
+    _need(k_cache, "k_cache", qkv.dtype)
+    _need(v_cache, "v_cache", qkv.dtype)
+    rows = qkv.shape[0]
+    if qkv.shape[1] != (heads + 2 * kv_heads) * head_dim:
+        raise KernelError(f"rope_append: qkv width {qkv.shape[1]} is not (heads + 2 kv_heads) * head_dim")
+    if row_pos.numel() < rows or row_slot.numel() < rows:
+        raise KernelError("rope_append: fewer positions or slots than rows")
+    n_pages = k_cache.shape[0]
+    if tuple(k_cache.shape[1:]) != (kv_heads, PAGE, head_dim) or k_cache.shape != v_cache.shape:
+        raise KernelError(f"rope_append: cache is {tuple(k_cache.shape)}, wanted [pages, {kv_heads}, {PAGE}, {head_dim}]")
+    if cos_sin is not None:
+        _need(cos_sin, "cos_sin", torch.float32)
+        if tuple(cos_sin.shape[1:]) != (head_dim // 2, 2):
+            raise KernelError(f"rope_append: cos_sin is {tuple(cos_sin.shape)}, wanted [positions, {head_dim // 2}, 2]")
+    _call(_fn("bc_rope_append_" + _suffix(qkv.dtype)), _ptr(qkv), _ptr(cos_sin), _ptr(row_pos), _ptr(row_slot), _ptr(page_table),
+          _ptr(k_cache), _ptr(v_cache), _c_int(rows), _c_int(heads), _c_int(kv_heads), _c_int(head_dim), _c_int(pairing),
+          _c_int(page_table.shape[1]), _c_int(n_pages), _c_int(1 if write_cache else 0), _stream())
+
+
+# ---------------------------------------------------------------------------------- products
+
+def gemm_simt(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int) -> None:
+    """out = x @ w.T on the CUDA cores with float accumulation in ascending k.
+    EPI_STORE: out in x's type; EPI_STORE_F32: float32; EPI_ADD_F32: out += (float32);
+    EPI_SWIGLU: w stacks gate rows on up rows, out[:, j] = silu(g_j) * u_j in x's type."""
+    _need(x, "x")
+    _need(w, "w", x.dtype)
+    M, K = x.shape
+    n_w = w.shape[0]
+    N = n_w // 2 if epilogue == EPI_SWIGLU else n_w
+    if w.shape[1] != K or (epilogue == EPI_SWIGLU and n_w % 2):
+        raise KernelError(f"gemm: x is {tuple(x.shape)}, w is {tuple(w.shape)}")
+    _need(out, "out", torch.float32 if epilogue in (EPI_STORE_F32, EPI_ADD_F32) else x.dtype)
+    if tuple(out.shape) != (M, N):
+        raise KernelError(f"gemm: out is {tuple(out.shape)}, wanted {(M, N)}")
+    _call(_fn("bc_gemm_simt_" + _suffix(x.dtype)), _ptr(x), _ptr(w), _ptr(out), _c_int(M), _c_int(N), _c_int(K), _c_int(epilogue), _stream())
+
+
+# --------------------------------------------------------------------------------- attention
+
+def attention_rows(q: torch.Tensor, q_stride: int, k_cache: torch.Tensor, v_cache: torch.Tensor, page_table: torch.Tensor,
+                   row_pos: torch.Tensor, row_slot: torch.Tensor, out: torch.Tensor, heads: int, kv_heads: int, head_dim: int,
+                   window: int = 0, scale: Optional[float] = None) -> None:
+    """Causal attention of every row against its slot's cached positions, one warp a (row, head)."""
+    _need(q, "q")
+    _need(k_cache, "k_cache", q.dtype)
+    _need(v_cache, "v_cache", q.dtype)
+    _need(page_table, "page_table", torch.int32)
+    _need(row_pos, "row_pos", torch.int32)
+    _need(row_slot, "row_slot", torch.int32)
+    _need(out, "out", q.dtype)
+    rows = out.shape[0]
+    if out.shape[1] != heads * head_dim:
+        raise KernelError(f"attention: out width {out.shape[1]} is not heads * head_dim")
+    if tuple(k_cache.shape[1:]) != (kv_heads, PAGE, head_dim) or k_cache.shape != v_cache.shape:
+        raise KernelError(f"attention: cache is {tuple(k_cache.shape)}, wanted [pages, {kv_heads}, {PAGE}, {head_dim}]")
+    if scale is None:
+        scale = 1.0 / float(head_dim) ** 0.5
+    _call(_fn("bc_attention_rows_" + _suffix(q.dtype)), _ptr(q), _c_int(q_stride), _ptr(k_cache), _ptr(v_cache), _ptr(page_table),
+          _ptr(row_pos), _ptr(row_slot), _ptr(out), _c_int(rows), _c_int(heads), _c_int(kv_heads), _c_int(head_dim),
+          _c_int(page_table.shape[1]), _c_int(k_cache.shape[0]), _c_int(window), _c_float(scale), _stream())
+
+
+# ---------------------------------------------------------------------------------- sampling
+
+def argmax(scores: torch.Tensor, out: torch.Tensor) -> None:
+    """out[r] = index of the first largest score of row r."""
+    _need(scores, "scores", torch.float32)
+    _need(out, "out", torch.int32)
+    rows, V = scores.shape
+    _call(_fn("bc_argmax"), _ptr(scores), _c_int(rows), _c_int(V), _ptr(out), _stream())
+
+
+def sample(scores: torch.Tensor, temperature: torch.Tensor, top_p: torch.Tensor, seed: torch.Tensor, step: torch.Tensor,
+           out: torch.Tensor) -> None:
+    """One draw a row: greedy where temperature <= 0, else temperature / nucleus sampling
+    with the draw keyed by (seed, step).  seed is int64 (its bits are the 64-bit seed)."""
+    _need(scores, "scores", torch.float32)
+    _need(temperature, "temperature", torch.float32)
+    _need(top_p, "top_p", torch.float32)
+    _need(seed, "seed", torch.int64)
+    _need(step, "step", torch.int32)
+    _need(out, "out", torch.int32)
+    rows, V = scores.shape
+    for name, t in (("temperature", temperature), ("top_p", top_p), ("seed", seed), ("step", step), ("out", out)):
+        if t.numel() < rows:
+            raise KernelError(f"sample: {name} has fewer entries than rows")
+    _call(_fn("bc_sample"), _ptr(scores), _c_int(rows), _c_int(V), _ptr(temperature), _ptr(top_p), _ptr(seed), _ptr(step), _ptr(out), _stream())
