@@ -1,0 +1,307 @@
+"""Each kernel alone against a plain float64 computation of the same operation, at sizes
+other than the engine's: widths that are no power of two, head size 48, ragged lengths."""
+
+from __future__ import annotations
+
+import math
+
+import numpy as np
+import pytest
+
+import plain_llama
+
+pytestmark = pytest.mark.gpu
+
+torch = pytest.importorskip("torch")
+
+
+def dev(a, dtype=None):
+    t = torch.as_tensor(np.ascontiguousarray(a)).cuda()
+    return t.to(dtype) if dtype is not None else t
+
+
+def f64(t):
+    return t.detach().float().cpu().numpy().astype(np.float64)
+
+
+def rng(seed):
+    return np.random.default_rng(seed)
+
+
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def stored(a, dtype):
+    """Values as the device holds them in ``dtype``, as float64."""
+    return f64(dev(a.astype(np.float32), dtype))
+
+
+def out_tol(dtype, ref):
+    return (1e-5 if dtype == torch.float32 else 2.0 ** -8) * (1.0 + np.abs(ref).max())
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_embed(dtype):
+    from borrowed_compute_b200 import ops
+
+    table = rng(0).standard_normal((37, 50)).astype(np.float32)
+    tokens = np.array([0, 36, 5, 5, 17, 99, -1], dtype=np.int32)
+    out = torch.full((7, 50), 7.0, dtype=torch.float32, device="cuda")
+    ops.embed(dev(table, dtype), dev(tokens), out)
+    ref = stored(table, dtype)
+    got = f64(out)
+    assert np.array_equal(got[:5], ref[tokens[:5]])
+    assert np.all(got[5:] == 0.0), "a token outside the table must give zeros, never a wild read"
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_rmsnorm(dtype):
+    from borrowed_compute_b200 import ops
+
+    x = (rng(1).standard_normal((37, 200)) * 3).astype(np.float32)
+    w = (1 + 0.3 * rng(2).standard_normal(200)).astype(np.float32)
+    ref = plain_llama.rms_norm(x.astype(np.float64), w.astype(np.float64), 1e-6)
+    out = torch.empty((37, 200), dtype=dtype, device="cuda")
+    ops.rmsnorm(dev(x), dev(w), out, 1e-6)
+    assert np.abs(f64(out) - ref).max() <= out_tol(dtype, ref)
+    gather = np.array([36, 0, 5], dtype=np.int32)
+    out = torch.empty((3, 200), dtype=dtype, device="cuda")
+    ops.rmsnorm(dev(x), dev(w), out, 1e-6, dev(gather))
+    assert np.abs(f64(out) - ref[gather]).max() <= out_tol(dtype, ref)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_swiglu(dtype):
+    from borrowed_compute_b200 import ops
+
+    gu = (rng(3).standard_normal((5, 2 * 176)) * 2).astype(np.float32)
+    g, u = stored(gu, dtype)[:, :176], stored(gu, dtype)[:, 176:]
+    ref = g / (1 + np.exp(-g)) * u
+    out = torch.empty((5, 176), dtype=dtype, device="cuda")
+    ops.swiglu(dev(gu, dtype), out)
+    assert np.abs(f64(out) - ref).max() <= out_tol(dtype, ref)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("M,N,K", [(37, 70, 176), (1, 130, 51), (65, 64, 96), (3, 5, 1024)])
+def test_gemm_simt(dtype, M, N, K):
+    """Odd row counts (the reference self-checks 37 rows, gpu/mod.rs:181-206), K with and
+    without the vector path, all four epilogues."""
+    from borrowed_compute_b200 import ops
+
+    x = rng(4).standard_normal((M, K)).astype(np.float32)
+    w = (rng(5).standard_normal((2 * N, K)) / math.sqrt(K)).astype(np.float32)
+    xs, ws = stored(x, dtype), stored(w, dtype)
+    full = xs @ ws.T
+    xd, wd = dev(x, dtype), dev(w, dtype)
+    out = torch.empty((M, N), dtype=dtype, device="cuda")
+    ops.gemm_simt(xd, wd[:N].contiguous(), out, ops.EPI_STORE)
+    assert np.abs(f64(out) - full[:, :N]).max() <= out_tol(dtype, full)
+    out32 = torch.empty((M, N), dtype=torch.float32, device="cuda")
+    ops.gemm_simt(xd, wd[:N].contiguous(), out32, ops.EPI_STORE_F32)
+    assert np.abs(f64(out32) - full[:, :N]).max() <= 1e-5 * (1 + np.abs(full).max())
+    base = rng(6).standard_normal((M, N)).astype(np.float32)
+    acc = dev(base)
+    ops.gemm_simt(xd, wd[:N].contiguous(), acc, ops.EPI_ADD_F32)
+    assert np.abs(f64(acc) - (base + full[:, :N])).max() <= 1e-5 * (1 + np.abs(full).max())
+    g, u = full[:, :N], full[:, N:]
+    ref = g / (1 + np.exp(-g)) * u
+    ops.gemm_simt(xd, wd, out, ops.EPI_SWIGLU)
+    assert np.abs(f64(out) - ref).max() <= out_tol(dtype, ref)
+
+
+def paged(values, page_ids, G, D, n_pages, dtype):
+    """Lays values [tokens, G, D] of one sequence out in pages [n_pages, G, 64, D]."""
+    pages = np.zeros((n_pages, G, 64, D), dtype=np.float32)
+    for t in range(values.shape[0]):
+        pages[page_ids[t // 64], :, t % 64, :] = values[t]
+    return pages
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("pairing", ["half", "adjacent"])
+def test_rope_append(dtype, pairing):
+    from borrowed_compute_b200 import ops
+    from borrowed_compute_b200.parts.rope import inverse_frequencies, rotary_table
+
+    H, G, D, n_pages, max_pages = 6, 3, 48, 9, 4
+    rows = 7
+    pos = np.array([0, 1, 63, 64, 130, 5, 200], dtype=np.int32)
+    slot = np.array([0, 1, 0, 1, 2, -1, 2], dtype=np.int32)
+    table = np.full((3, max_pages), -1, dtype=np.int32)
+    table[0, :1], table[1, :2], table[2, :4] = [4], [7, 2], [1, 8, 3, 0]
+    qkv = rng(7).standard_normal((rows, (H + 2 * G) * D)).astype(np.float32)
+    inv_freq = inverse_frequencies(D, 10000.0, None)
+    assert np.array_equal(inv_freq.numpy(), plain_llama.rope_inv_freq(D, 10000.0, None))
+    cos_sin = rotary_table(inv_freq, 256)
+    qd = dev(qkv, dtype)
+    k_pages = torch.zeros((n_pages, G, 64, D), dtype=dtype, device="cuda")
+    v_pages = torch.zeros_like(k_pages)
+    ops.rope_append(qd, cos_sin.cuda(), dev(pos), dev(slot), dev(table), k_pages, v_pages, H, G, D, 0 if pairing == "half" else 1)
+    src = stored(qkv, dtype).reshape(rows, H + 2 * G, D)
+    rot = plain_llama.rope(src[:, :H + G, :], pos, inv_freq.numpy(), pairing)
+    got = f64(qd).reshape(rows, H + 2 * G, D)
+    tol = out_tol(dtype, src)
+    live = slot >= 0
+    assert np.abs(got[live, :H] - rot[live, :H]).max() <= tol
+    assert np.array_equal(got[~live], src[~live]), "a padding row was touched"
+    kp, vp = f64(k_pages), f64(v_pages)
+    expect_k, expect_v = np.zeros_like(kp), np.zeros_like(vp)
+    for r in range(rows):
+        if slot[r] < 0:
+            continue
+        page = table[slot[r], pos[r] // 64]
+        expect_k[page, :, pos[r] % 64, :] = rot[r, H:H + G]
+        expect_v[page, :, pos[r] % 64, :] = src[r, H + G:]
+    assert np.abs(kp - expect_k).max() <= tol
+    assert np.array_equal(vp, expect_v)
+
+
+def attention_reference(q, k, v, window=0):
+    """q [H, D] at the last position of k, v [T, G, D]."""
+    H, D = q.shape
+    T, G, _ = k.shape
+    lo = max(0, T - window) if window > 0 else 0
+    out = np.zeros((H, D))
+    for h in range(H):
+        g = h // (H // G)
+        s = k[lo:, g, :] @ q[h] / math.sqrt(D)
+        p = np.exp(s - s.max())
+        out[h] = (p / p.sum()) @ v[lo:, g, :]
+    return out
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("window", [0, 20])
+def test_attention_rows(dtype, window):
+    """Rows of five sequences of lengths around the page and tile edges, pages scattered."""
+    from borrowed_compute_b200 import ops
+
+    H, G, D, n_pages = 6, 3, 48, 16
+    lengths = [1, 32, 64, 65, 200]
+    r = rng(8)
+    page_lists = [[5], [9], [2], [11, 0], [7, 3, 14, 1]]
+    table = np.full((6, 4), -1, dtype=np.int32)
+    kp = np.zeros((n_pages, G, 64, D), dtype=np.float32)
+    vp = np.zeros_like(kp)
+    ks, vs = [], []
+    for s, (n, pages) in enumerate(zip(lengths, page_lists)):
+        table[s, :len(pages)] = pages
+        k, v = r.standard_normal((n, G, D)).astype(np.float32), r.standard_normal((n, G, D)).astype(np.float32)
+        ks.append(k), vs.append(v)
+        kp += paged(k, pages, G, D, n_pages, dtype)
+        vp += paged(v, pages, G, D, n_pages, dtype)
+    # Rows: the last position of every sequence, two earlier positions of the longest, and padding.
+    row_slot = np.array([0, 1, 2, 3, 4, 4, -1, 4], dtype=np.int32)
+    row_pos = np.array([0, 31, 63, 64, 199, 63, 0, 128], dtype=np.int32)
+    q = (r.standard_normal((8, H * D)) * 2).astype(np.float32)
+    out = torch.full((8, H * D), 9.0, dtype=dtype, device="cuda")
+    ops.attention_rows(dev(q, dtype), H * D, dev(kp, dtype), dev(vp, dtype), dev(table), dev(row_pos), dev(row_slot), out,
+                       H, G, D, window=window)
+    got = f64(out)
+    qs = stored(q, dtype)
+    for i in range(8):
+        if row_slot[i] < 0:
+            assert np.all(got[i] == 0.0)
+            continue
+        s, p = row_slot[i], row_pos[i]
+        ref = attention_reference(qs[i].reshape(H, D), stored(ks[s][:p + 1], dtype), stored(vs[s][:p + 1], dtype), window)
+        assert np.abs(got[i].reshape(H, D) - ref).max() <= out_tol(dtype, ref), f"row {i}"
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_attention_finds_one_far_key(dtype):
+    """Random keys hide a lost position: here one key among 300 matches the query, so the
+    output must be that position's value, wherever it lies; and just outside a window it
+    must vanish."""
+    from borrowed_compute_b200 import ops
+
+    H, G, D, n_pages, T = 2, 1, 16, 8, 300
+    table = np.array([[6, 1, 4, 2, 7]], dtype=np.int32)
+    for far in (0, 31, 32, 63, 64, 127, 128, 255, 256, 299):
+        k = np.zeros((T, G, D), dtype=np.float32)
+        v = rng(far).standard_normal((T, G, D)).astype(np.float32)
+        k[far, 0, 3] = 100.0
+        q = np.zeros((1, H * D), dtype=np.float32)
+        q[0, 3] = q[0, D + 3] = 4.0
+        args = (dev(paged(k, table[0], G, D, n_pages, dtype), dtype), dev(paged(v, table[0], G, D, n_pages, dtype), dtype), dev(table),
+                dev(np.array([T - 1], dtype=np.int32)), dev(np.array([0], dtype=np.int32)))
+        out = torch.empty((1, H * D), dtype=dtype, device="cuda")
+        ops.attention_rows(dev(q, dtype), H * D, *args, out, H, G, D)
+        want = stored(v[far, 0], dtype)
+        assert np.abs(f64(out).reshape(H, D) - want).max() <= 2.0 ** -7, f"the key at {far} was not found"
+        inside, outside = T - far, T - far - 1
+        ops.attention_rows(dev(q, dtype), H * D, *args, out, H, G, D, window=inside)
+        assert np.abs(f64(out).reshape(H, D) - want).max() <= 2.0 ** -7, f"window {inside} must still see position {far}"
+        if outside > 0:
+            ops.attention_rows(dev(q, dtype), H * D, *args, out, H, G, D, window=outside)
+            assert np.abs(f64(out).reshape(H, D) - want).max() > 0.05, f"window {outside} must not see position {far}"
+
+
+def test_argmax_first_largest_wins():
+    from borrowed_compute_b200 import ops
+
+    scores = rng(9).standard_normal((5, 1001)).astype(np.float32)
+    scores[1, [7, 500, 900]] = 50.0
+    scores[2, 1000] = 60.0
+    scores[3, 0] = 60.0
+    scores[4, :] = -3.0
+    out = torch.empty(5, dtype=torch.int32, device="cuda")
+    ops.argmax(dev(scores), out)
+    assert out.cpu().tolist() == [plain_llama.argmax(row) for row in scores] == [int(scores[0].argmax()), 7, 1000, 0, 0]
+
+
+def run_sampler(scores, temperature, top_p, seed, steps):
+    from borrowed_compute_b200 import ops
+
+    n = scores.shape[0]
+    out = torch.empty(n, dtype=torch.int32, device="cuda")
+    seeds = np.array([seed - (1 << 64) if seed >= (1 << 63) else seed] * n, dtype=np.int64)
+    ops.sample(dev(scores), dev(np.full(n, temperature, dtype=np.float32)), dev(np.full(n, top_p, dtype=np.float32)),
+               dev(seeds), dev(np.asarray(steps, dtype=np.int32)), out)
+    return out.cpu().tolist()
+
+
+def test_sampler_on_the_reference_case():
+    """crates/bc-infer/src/sample.rs:77-89."""
+    scores = np.array([[0.1, 3.0, 2.9, -5.0]], dtype=np.float32)
+    assert run_sampler(scores, 0.0, 1.0, 0, [0]) == [1]
+    rows = np.repeat(scores, 200, axis=0)
+    assert set(run_sampler(rows[:20], 1.0, 0.01, 7, range(20))) == {1}
+    picks = run_sampler(rows, 1.0, 0.95, 7, range(200))
+    assert 1 in picks and 2 in picks and 3 not in picks
+    assert picks == run_sampler(rows, 1.0, 0.95, 7, range(200)), "seeded"
+    assert picks == [plain_llama.sample(scores[0], 1.0, 0.95, 7, i) for i in range(200)]
+
+
+@pytest.mark.parametrize("V", [1000, 5003])
+@pytest.mark.parametrize("temperature,top_p", [(0.8, 0.9), (1.0, 1.0), (1.5, 0.5), (0.3, 0.95)])
+def test_sampler_matches_the_plain_one(V, temperature, top_p):
+    """The device picks the token the sorted walk picks.  Where the uniform draw lands
+    within rounding of a boundary between two tokens either may be picked; such rows are
+    told apart by the margin and must be rare."""
+    scale = 3.0 if V == 1000 else 0.5
+    scores = (rng(V).standard_normal((64, V)) * scale).astype(np.float32)
+    scores[5, 10:20] = scores[5, 3]          # ties: equal weights keep ascending ids
+    seed = 0x9E3779B97F4A7C15
+    got = run_sampler(scores, temperature, top_p, seed, range(100, 164))
+    same = 0
+    for r in range(64):
+        want = plain_llama.sample(scores[r], temperature, top_p, seed, 100 + r)
+        if got[r] == want:
+            same += 1
+            continue
+        order, w = plain_llama.nucleus(scores[r], temperature, top_p)
+        assert got[r] in order, f"row {r}: token {got[r]} is outside the nucleus"
+        u = plain_llama.uniform((seed ^ (((100 + r) * 0x9E3779B97F4A7C15) & plain_llama.MASK64)) & plain_llama.MASK64) * w.sum()
+        cum = np.cumsum(w)
+        i = order.index(got[r])
+        lo, hi = (cum[i - 1] if i else 0.0), cum[i]
+        assert lo - 1e-4 * w.sum() <= u <= hi + 1e-4 * w.sum(), f"row {r}: token {got[r]} does not hold the draw"
+    assert same >= 60
+
+
+def test_sampler_rows_are_independent():
+    scores = (rng(11).standard_normal((8, 777)) * 2).astype(np.float32)
+    alone = [run_sampler(scores[i:i + 1], 0.9, 0.9, 42, [50 + i])[0] for i in range(8)]
+    assert run_sampler(scores, 0.9, 0.9, 42, range(50, 58)) == alone
