@@ -1,0 +1,458 @@
+// bf16 matrix product on the 5th-generation tensor cores: Y[t, n] = sum_k X[t, k] * W[n, k].
+//
+// The reference multiplies with one warp a weight row on the CUDA cores
+// (crates/bc-infer/src/gpu/kernels.h:204-223, launched seven times a layer,
+// crates/bc-infer/src/gpu/mod.rs:456-489).  Here the product is laid out for Blackwell:
+//
+//   - The WEIGHT tile is the MMA's M operand: 128 weight rows by 64 k, and the activation
+//     tile is the N operand: BN tokens by 64 k (BN = 16 .. 256).  Both matrices are stored
+//     k-major already ([out, in] weights, [token, hidden] activations), so neither needs a
+//     transpose, and a decode step of a few tokens still fills all 128 rows of the tensor
+//     core while it streams the weights once.  The accumulator D[n, t] lives in TMEM:
+//     lane = weight row, column = token.
+//   - Operands come by TMA (cp.async.bulk.tensor, 128-byte swizzle, no multicast) into a
+//     ring of shared-memory stages guarded by mbarriers; one thread issues tcgen05.mma
+//     (kind::f16, bf16 in, float accumulate); tcgen05.commit releases a stage when the
+//     MMAs that read it are done.  TMA zero-fills past the edges, so any K that is a
+//     multiple of 8 and any N and T work; the epilogue writes only what exists.
+//   - Warp roles: warp 0 loads, warp 1 owns TMEM and issues MMAs, warps 2..5 read the
+//     accumulator back (tcgen05.ld; a warp may touch lanes 32 (w mod 4) ..) and apply the
+//     epilogue: store bf16, store float (scores), add into the float residual stream, or
+//     SwiGLU over a weight that stacks gate rows on up rows (two accumulators, one B tile).
+//   - With split-K (grid z > 1, for products with few weight tiles and a long K) every
+//     split adds its partial into a float workspace tile in a fixed order: split s waits
+//     for a tile counter to reach s, so the sum's order never changes from run to run.
+//
+// Every wait is bounded: after about a second without progress a thread records where it
+// gave up in a status word, stops waiting, and the block frees its TMEM and returns.
+#include <cuda.h>
+
+#include <mutex>
+#include <unordered_map>
+
+#include "common.cuh"
+
+enum { EPI_STORE = 0, EPI_STORE_F32 = 1, EPI_ADD_F32 = 2, EPI_SWIGLU = 3 };
+
+#define TC_BM 128          // weight rows a tile (MMA M)
+#define TC_BK 64           // k a stage: 64 bf16 = one 128-byte swizzle row
+#define TC_THREADS 192     // warp 0 TMA, warp 1 MMA, warps 2-5 epilogue
+#define TC_SMEM_LIMIT 230400   // dynamic bytes asked for at most; static barriers take a little more
+#define TC_WAIT_CYCLES 2000000000ll
+
+// Status word: 0 while all is well, else (code << 16 | detail) of the first wait that gave up.
+__device__ int g_tc_status = 0;
+
+// ------------------------------------------------------------------------------ PTX pieces
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Waits for a phase of a barrier, at most about a second.  False (and a recorded status)
+// if it gave up; the caller then stops doing work but still reaches the teardown.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int code) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long start = clock64();
+    while (!mbar_try_wait(bar, parity)) {
+        if (clock64() - start > TC_WAIT_CYCLES) {
+            atomicCAS(&g_tc_status, 0, (code << 16) | (int)(blockIdx.x & 0xffff));
+            return false;
+        }
+    }
+    return true;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
+                 "l"(map), "r"(bar), "r"(x), "r"(y)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t slot, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot), "r"(cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void mma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+        "}\n" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void mma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tmem_load16(uint32_t taddr, uint32_t* v) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]),
+          "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_load_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory operand descriptor: k-major tile of 128-byte rows, 128-byte swizzle, as TMA
+// writes it.  Bits 0-13 address/16; 16-29 leading offset/16 (unused for swizzled k-major,
+// 1); 32-45 stride between 8-row groups/16 (1024 bytes); 46-47 version 1; 61-63 layout 2
+// (SWIZZLE_128B).  Stepping 16 k (32 bytes) inside the swizzle row adds 2 to the address.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
+    return (uint64_t)((addr >> 4) & 0x3fff) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+}
+// Instruction descriptor of kind::f16: float accumulate (bit 4), A and B bf16 (bits 7, 10),
+// both k-major (bits 15, 16 clear), N / 8 at bit 17, M / 16 at bit 24.
+__host__ __device__ constexpr uint32_t instr_desc(int n) { return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24); }
+
+__device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.0f + expf(-g)) * u; }
+
+// ---------------------------------------------------------------------------------- kernel
+struct TcParams {
+    void* out;          // bf16 [T, N] (store, swiglu) or float [T, N] (store_f32, add_f32)
+    float* partial;     // split-K: float [tiles, BN, TC_BM] workspace (contents need not be zero)
+    int* counters;      // split-K: four a tile, zero before the first launch (a launch leaves them zero)
+    int T, N, K;
+    int up_row_offset;  // SwiGLU: rows of the up half start here in W
+    int stages;
+    int k_iters_per_split;
+};
+
+template <int BN, int EPI>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, const TcParams p) {
+    constexpr int A_BYTES = TC_BM * TC_BK * 2;
+    constexpr int B_BYTES = BN * TC_BK * 2;
+    constexpr int N_ACC = EPI == EPI_SWIGLU ? 2 : 1;
+    constexpr int STAGE_BYTES = N_ACC * A_BYTES + B_BYTES;
+    constexpr int TMEM_COLS = N_ACC * BN < 32 ? 32 : N_ACC * BN;
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    // Tiles need 1024-byte alignment for the 128-byte swizzle.
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    __shared__ __align__(8) uint64_t bars[2 * 16 + 1];
+    __shared__ uint32_t tmem_slot;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int stages = p.stages;
+    const int n0 = blockIdx.x * TC_BM, t0 = blockIdx.y * BN;
+    const int total_k_iters = (p.K + TC_BK - 1) / TC_BK;
+    const int k_first = blockIdx.z * p.k_iters_per_split;
+    const int k_iters = min(p.k_iters_per_split, total_k_iters - k_first);
+    const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[16]), acc_bar = smem_u32(&bars[32]);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < stages; s++) {
+            mbar_init(full0 + 8 * s, 1);
+            mbar_init(empty0 + 8 * s, 1);
+        }
+        mbar_init(acc_bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) tmem_alloc(smem_u32(&tmem_slot), TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            for (int i = 0; i < k_iters; i++) {
+                const int s = i % stages;
+                if (!mbar_wait(empty0 + 8 * s, ((i / stages) & 1) ^ 1, 1)) break;
+                const uint32_t a = smem_u32(smem + (size_t)s * STAGE_BYTES);
+                mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
+                const int k = (k_first + i) * TC_BK;
+                tma_load_2d(a, &map_w, full0 + 8 * s, k, n0);
+                if (EPI == EPI_SWIGLU) tma_load_2d(a + A_BYTES, &map_w, full0 + 8 * s, k, p.up_row_offset + n0);
+                tma_load_2d(a + N_ACC * A_BYTES, &map_x, full0 + 8 * s, k, t0);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = instr_desc(BN);
+            bool ok = true;
+            for (int i = 0; i < k_iters && ok; i++) {
+                const int s = i % stages;
+                ok = mbar_wait(full0 + 8 * s, (i / stages) & 1, 2);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t a = smem_u32(smem + (size_t)s * STAGE_BYTES);
+                const uint64_t da = smem_desc(a), db = smem_desc(a + N_ACC * A_BYTES);
+#pragma unroll
+                for (int kk = 0; kk < TC_BK / 16; kk++) {
+                    const uint32_t acc = (i | kk) != 0;
+                    mma_bf16(tmem, da + 2 * kk, db + 2 * kk, idesc, acc);
+                    if (EPI == EPI_SWIGLU) mma_bf16(tmem + BN, smem_desc(a + A_BYTES) + 2 * kk, db + 2 * kk, idesc, acc);
+                }
+                mma_commit(empty0 + 8 * s);
+            }
+            mma_commit(acc_bar);
+        }
+    } else {
+        // Epilogue: this warp reads TMEM lanes 32 q .. 32 q + 31, i.e. weight rows n0 + 32 q + lane.
+        const int q = warp & 3;
+        const int n = n0 + 32 * q + lane;
+        const bool split = gridDim.z > 1;
+        const bool last = blockIdx.z == gridDim.z - 1;
+        const int tile = blockIdx.y * gridDim.x + blockIdx.x;
+        // Split-K: the four row quarters of a tile each have a counter; split z adds its
+        // partial to the quarter's workspace once the counter says z, so the order of the
+        // sum is fixed.  Workspace layout [column][row]: a warp touches 32 consecutive floats.
+        float* part = split ? p.partial + (size_t)tile * TC_BM * BN + 32 * q + lane : nullptr;
+        int* counter = split ? p.counters + (size_t)tile * 4 + q : nullptr;
+        bool ok = true;
+        if (lane == 0) {
+            ok = mbar_wait(acc_bar, 0, 3);
+            if (ok && split && blockIdx.z > 0) {
+                const long long start = clock64();
+                while (atomicAdd(counter, 0) != (int)blockIdx.z) {
+                    if (clock64() - start > TC_WAIT_CYCLES) {
+                        atomicCAS(&g_tc_status, 0, (4 << 16) | (int)(blockIdx.x & 0xffff));
+                        ok = false;
+                        break;
+                    }
+                }
+            }
+        }
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        __threadfence();
+        tc_fence_after();
+        if (ok) {
+            const uint32_t taddr = tmem + ((uint32_t)(32 * q) << 16);
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 16) {
+                uint32_t v[16], u[16];
+                tmem_load16(taddr + c0, v);
+                if (EPI == EPI_SWIGLU) tmem_load16(taddr + BN + c0, u);
+                tmem_load_wait();
+#pragma unroll
+                for (int j = 0; j < 16; j++) {
+                    const int t = t0 + c0 + j;
+                    float val = __uint_as_float(v[j]);
+                    if (split) {
+                        float* w = part + (size_t)(c0 + j) * TC_BM;
+                        if (blockIdx.z > 0) val += __ldcg(w);
+                        if (!last) __stcg(w, val);
+                    }
+                    if (last && t < p.T && n < p.N) {
+                        const size_t o = (size_t)t * p.N + n;
+                        if (EPI == EPI_STORE) ((bf16*)p.out)[o] = __float2bfloat16_rn(val);
+                        if (EPI == EPI_STORE_F32) ((float*)p.out)[o] = val;
+                        if (EPI == EPI_ADD_F32) ((float*)p.out)[o] += val;
+                        if (EPI == EPI_SWIGLU) ((bf16*)p.out)[o] = __float2bfloat16_rn(silu_mul(val, __uint_as_float(u[j])));
+                    }
+                }
+            }
+        }
+        if (split) {
+            // Hand the quarter to the next split (or, from the last, back to zero for the
+            // next launch) only after this warp's sums are visible.
+            __threadfence();
+            __syncwarp();
+            if (lane == 0) {
+                if (last) atomicExch(counter, 0);
+                else if (ok) atomicAdd(counter, 1);
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem, TMEM_COLS);
+    }
+}
+
+// -------------------------------------------------------------------------------- the host
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    });
+    return fn;
+}
+
+// A k-major bf16 matrix [rows, K] cut into boxes of box_rows x 64, 128-byte swizzle, zero fill.
+static int make_map(CUtensorMap* map, const void* base, int rows, int K, int box_rows) {
+    EncodeTiledFn enc = encode_fn();
+    if (!enc) {
+        bc_set_error("gemm_tc: the driver gives no cuTensorMapEncodeTiled");
+        return BC_ERR_DRIVER;
+    }
+    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+    cuuint32_t box[2] = {TC_BK, (cuuint32_t)box_rows};
+    cuuint32_t elem[2] = {1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        bc_set_error("gemm_tc: cuTensorMapEncodeTiled failed (%d) for a [%d, %d] matrix, box %d x %d", (int)r, rows, K, box_rows, TC_BK);
+        return BC_ERR_DRIVER;
+    }
+    return BC_OK;
+}
+
+// Weight maps are made once per (pointer, shape) and kept: weights do not move.
+struct MapKey {
+    const void* p;
+    int rows, K, box;
+    bool operator==(const MapKey& o) const { return p == o.p && rows == o.rows && K == o.K && box == o.box; }
+};
+struct MapKeyHash {
+    size_t operator()(const MapKey& k) const { return std::hash<const void*>()(k.p) ^ ((size_t)k.rows * 1000003u) ^ ((size_t)k.K << 20) ^ (size_t)k.box; }
+};
+static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_weight_maps;
+static std::mutex g_weight_maps_mutex;
+
+static int weight_map(CUtensorMap* out, const void* base, int rows, int K) {
+    std::lock_guard<std::mutex> lock(g_weight_maps_mutex);
+    MapKey key{base, rows, K, TC_BM};
+    auto it = g_weight_maps.find(key);
+    if (it == g_weight_maps.end()) {
+        CUtensorMap m;
+        int st = make_map(&m, base, rows, K, TC_BM);
+        if (st != BC_OK) return st;
+        if (g_weight_maps.size() > 65536) g_weight_maps.clear();
+        it = g_weight_maps.emplace(key, m).first;
+    }
+    *out = it->second;
+    return BC_OK;
+}
+
+template <int BN, int EPI>
+static int launch(const CUtensorMap& mw, const CUtensorMap& mx, TcParams p, int splits, cudaStream_t s) {
+    constexpr int N_ACC = EPI == EPI_SWIGLU ? 2 : 1;
+    constexpr int STAGE_BYTES = N_ACC * TC_BM * TC_BK * 2 + BN * TC_BK * 2;
+    const int total_k_iters = (p.K + TC_BK - 1) / TC_BK;
+    p.k_iters_per_split = (total_k_iters + splits - 1) / splits;
+    splits = (total_k_iters + p.k_iters_per_split - 1) / p.k_iters_per_split;
+    int stages = (TC_SMEM_LIMIT - 1024) / STAGE_BYTES;
+    if (stages > 12) stages = 12;
+    if (stages > p.k_iters_per_split) stages = p.k_iters_per_split < 2 ? 2 : p.k_iters_per_split;
+    p.stages = stages;
+    const int smem = stages * STAGE_BYTES + 1024;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_LIMIT);
+        if (e != cudaSuccess) {
+            bc_set_error("gemm_tc: cannot raise the shared memory limit: %s", cudaGetErrorString(e));
+            return (int)e;
+        }
+        configured = true;
+    }
+    dim3 grid((p.N + TC_BM - 1) / TC_BM, (p.T + BN - 1) / BN, splits);
+    gemm_tc_kernel<BN, EPI><<<grid, TC_THREADS, smem, s>>>(mw, mx, p);
+    BC_LAUNCH_STATUS();
+}
+
+template <int EPI>
+static int launch_bn(int bn, const CUtensorMap& mw, const CUtensorMap& mx, const TcParams& p, int splits, cudaStream_t s) {
+    switch (bn) {
+        case 16: return launch<16, EPI>(mw, mx, p, splits, s);
+        case 32: return launch<32, EPI>(mw, mx, p, splits, s);
+        case 64: return launch<64, EPI>(mw, mx, p, splits, s);
+        case 128: return launch<128, EPI>(mw, mx, p, splits, s);
+        case 256: return launch<256, EPI>(mw, mx, p, splits, s);
+    }
+    bc_set_error("gemm_tc: no kernel for a token tile of %d", bn);
+    return BC_ERR_ARG;
+}
+
+// Token tile for T tokens: the smallest that covers them, up to 256 (128 for SwiGLU, whose
+// two accumulators would otherwise fill all of TMEM).
+extern "C" int bc_gemm_tc_token_tile(int T, int epilogue) {
+    const int cap = epilogue == EPI_SWIGLU ? 128 : 256;
+    int bn = 16;
+    while (bn < T && bn < cap) bn <<= 1;
+    return bn;
+}
+
+// Floats of workspace and ints of counters a split-K launch needs.  The counters are zero
+// before the first launch and every launch leaves them zero; the floats may hold anything.
+extern "C" int bc_gemm_tc_workspace(int T, int N, int epilogue, int splits, long long* floats, long long* ints) {
+    const int bn = bc_gemm_tc_token_tile(T, epilogue);
+    const long long tiles = (long long)((N + TC_BM - 1) / TC_BM) * ((T + bn - 1) / bn);
+    *floats = splits > 1 ? tiles * TC_BM * bn : 0;
+    *ints = splits > 1 ? tiles * 4 : 0;
+    return BC_OK;
+}
+
+// X [T, K] bf16, W [N, K] bf16 (SwiGLU: [2N, K], gate rows then up rows); out [T, N] bf16 or
+// float by epilogue.  K must be a multiple of 8 (a TMA row stride is a multiple of 16
+// bytes); pointers 16-byte aligned.  splits > 1 needs the workspace above.
+extern "C" int bc_gemm_tc_bf16(const void* X, const void* W, void* out, int T, int N, int K, int epilogue, int splits, float* partial,
+                               int* counters, cudaStream_t s) {
+    BC_CHECK_ARG(T >= 0 && N > 0 && K > 0, "gemm_tc: bad sizes T=%d N=%d K=%d", T, N, K);
+    BC_CHECK_ARG(K % 8 == 0, "gemm_tc: K=%d is not a multiple of 8 (TMA needs 16-byte row strides); use the CUDA-core product", K);
+    BC_CHECK_ARG(((uintptr_t)X % 16 == 0) && ((uintptr_t)W % 16 == 0), "gemm_tc: operands must be 16-byte aligned");
+    BC_CHECK_ARG(epilogue >= 0 && epilogue <= 3, "gemm_tc: unknown epilogue %d", epilogue);
+    BC_CHECK_ARG(splits >= 1 && (splits == 1 || (partial && counters)), "gemm_tc: split-K needs a workspace");
+    BC_CHECK_ARG(splits == 1 || epilogue != EPI_SWIGLU, "gemm_tc: SwiGLU cannot be split along K");
+    if (T == 0) return BC_OK;
+    const int bn = bc_gemm_tc_token_tile(T, epilogue);
+    BC_CHECK_ARG((T + bn - 1) / bn <= 65535, "gemm_tc: %d tokens are too many token tiles", T);
+    const int w_rows = epilogue == EPI_SWIGLU ? 2 * N : N;
+    CUtensorMap mw, mx;
+    int st = weight_map(&mw, W, w_rows, K);
+    if (st != BC_OK) return st;
+    st = make_map(&mx, X, T, K, bn);
+    if (st != BC_OK) return st;
+    TcParams p;
+    p.out = out;
+    p.partial = partial;
+    p.counters = counters;
+    p.T = T;
+    p.N = N;
+    p.K = K;
+    p.up_row_offset = N;
+    p.stages = 0;
+    p.k_iters_per_split = 0;
+    switch (epilogue) {
+        case EPI_STORE: return launch_bn<EPI_STORE>(bn, mw, mx, p, splits, s);
+        case EPI_STORE_F32: return launch_bn<EPI_STORE_F32>(bn, mw, mx, p, splits, s);
+        case EPI_ADD_F32: return launch_bn<EPI_ADD_F32>(bn, mw, mx, p, splits, s);
+        case EPI_SWIGLU: return launch_bn<EPI_SWIGLU>(bn, mw, mx, p, 1, s);
+    }
+    return BC_ERR_ARG;
+}
+
+// The status word of the tensor-core kernels: 0, or where a bounded wait gave up.  Reading
+// it waits for the device; `reset` clears it.
+extern "C" int bc_gemm_tc_status(int reset) {
+    int v = 0;
+    cudaMemcpyFromSymbol(&v, g_tc_status, sizeof(int));
+    if (reset && v != 0) {
+        int zero = 0;
+        cudaMemcpyToSymbol(g_tc_status, &zero, sizeof(int));
+    }
+    return v;
+}

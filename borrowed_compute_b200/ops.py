@@ -166,6 +166,71 @@ def gemm_simt(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int
     _call(_fn("bc_gemm_simt_" + _suffix(x.dtype)), _ptr(x), _ptr(w), _ptr(out), _c_int(M), _c_int(N), _c_int(K), _c_int(epilogue), _stream())
 
 
+_tc_workspace = {}
+
+
+def _tc_scratch(device: torch.device):
+    """Split-K scratch of the tensor-core product, one a device, allocated at first use:
+    float partial tiles (any contents) and int counters (zero between launches)."""
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    if key not in _tc_workspace:
+        _tc_workspace[key] = (torch.empty(148 * 128 * 256, dtype=torch.float32, device=device),
+                              torch.zeros(4096, dtype=torch.int32, device=device))
+    return _tc_workspace[key]
+
+
+def gemm_tc_accepts(x: torch.Tensor, w: torch.Tensor) -> bool:
+    """Whether the tensor-core product takes these operands (K a multiple of 8, bf16)."""
+    return x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[-1] % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
+
+
+def gemm_tc_splits(T: int, N: int, K: int, epilogue: int) -> int:
+    """How many ways to split K so that a product with few weight tiles still fills the
+    device's 148 SMs: as many as fit, each at least 8 k-steps of 64."""
+    if epilogue == EPI_SWIGLU:
+        return 1
+    bn = 16
+    while bn < T and bn < 256:
+        bn *= 2
+    tiles = -(-N // 128) * -(-T // bn)
+    return max(1, min(148 // tiles, -(-K // 64) // 8, 16))
+
+
+def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int, splits: Optional[int] = None) -> None:
+    """out = x @ w.T for bf16 operands on the tcgen05 tensor cores (float accumulation in
+    TMEM), with the epilogues of gemm_simt.  ``splits`` > 1 cuts K across blocks that add
+    their partial sums in a fixed order."""
+    _need(x, "x", torch.bfloat16)
+    _need(w, "w", torch.bfloat16)
+    M, K = x.shape
+    n_w = w.shape[0]
+    N = n_w // 2 if epilogue == EPI_SWIGLU else n_w
+    if w.shape[1] != K or (epilogue == EPI_SWIGLU and n_w % 2):
+        raise KernelError(f"gemm: x is {tuple(x.shape)}, w is {tuple(w.shape)}")
+    _need(out, "out", torch.float32 if epilogue in (EPI_STORE_F32, EPI_ADD_F32) else torch.bfloat16)
+    if tuple(out.shape) != (M, N):
+        raise KernelError(f"gemm: out is {tuple(out.shape)}, wanted {(M, N)}")
+    if splits is None:
+        splits = gemm_tc_splits(M, N, K, epilogue)
+    partial = counters = None
+    if splits > 1:
+        partial, counters = _tc_scratch(x.device)
+        bn = 16
+        while bn < M and bn < 256:
+            bn *= 2
+        tiles = -(-N // 128) * -(-M // bn)
+        if tiles * 128 * bn > partial.numel() or tiles * 4 > counters.numel():
+            raise KernelError(f"gemm_tc: {tiles} tiles are too many for the split-K scratch; use splits=1")
+    _call(_fn("bc_gemm_tc_bf16"), _ptr(x), _ptr(w), _ptr(out), _c_int(M), _c_int(N), _c_int(K), _c_int(epilogue), _c_int(splits),
+          _ptr(partial), _ptr(counters), _stream())
+
+
+def gemm_tc_status(reset: bool = True) -> int:
+    """Waits for the device and returns the tensor-core kernels' status word: 0, or
+    (code << 16 | block) of the first bounded wait that gave up."""
+    return int(_fn("bc_gemm_tc_status")(_c_int(1 if reset else 0)))
+
+
 # --------------------------------------------------------------------------------- attention
 
 def attention_rows(q: torch.Tensor, q_stride: int, k_cache: torch.Tensor, v_cache: torch.Tensor, page_table: torch.Tensor,

@@ -1,0 +1,79 @@
+"""The tcgen05 product against a float64 product of the same bf16 operands, at shapes that
+exercise every token tile, ragged edges in all three dimensions, split-K, and all epilogues."""
+
+from __future__ import annotations
+
+import math
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+torch = pytest.importorskip("torch")
+
+SHAPES = [
+    # T, N, K, splits
+    (1, 128, 64, 1), (16, 128, 128, 1), (5, 70, 176, 1), (37, 320, 96, 1), (64, 256, 256, 1), (100, 200, 128, 1),
+    (300, 130, 192, 1), (8, 512, 4096, 4), (33, 256, 2048, 3), (3, 100, 1024, 2), (600, 384, 512, 1),
+]
+
+
+def operands(T, N, K, seed):
+    r = np.random.default_rng(seed)
+    x = torch.from_numpy(r.standard_normal((T, K)).astype(np.float32)).cuda().to(torch.bfloat16)
+    w = torch.from_numpy((r.standard_normal((2 * N, K)) / math.sqrt(K)).astype(np.float32)).cuda().to(torch.bfloat16)
+    return x, w
+
+
+def f64(t):
+    return t.detach().float().cpu().numpy().astype(np.float64)
+
+
+@pytest.mark.parametrize("T,N,K,splits", SHAPES)
+def test_gemm_tc_all_epilogues(T, N, K, splits):
+    from borrowed_compute_b200 import ops
+
+    x, w = operands(T, N, K, T * 1000 + N)
+    full = f64(x) @ f64(w).T
+    scale = 1.0 + np.abs(full).max()
+    wn = w[:N].contiguous()
+    out32 = torch.full((T, N), 7.0, dtype=torch.float32, device="cuda")
+    ops.gemm_tc(x, wn, out32, ops.EPI_STORE_F32, splits=splits)
+    assert ops.gemm_tc_status() == 0
+    assert np.abs(f64(out32) - full[:, :N]).max() <= 2e-5 * scale, "float store"
+    again = torch.empty_like(out32)
+    ops.gemm_tc(x, wn, again, ops.EPI_STORE_F32, splits=splits)
+    assert torch.equal(out32, again), "the same launch twice must give the same bits"
+    out16 = torch.empty((T, N), dtype=torch.bfloat16, device="cuda")
+    ops.gemm_tc(x, wn, out16, ops.EPI_STORE, splits=splits)
+    assert np.abs(f64(out16) - full[:, :N]).max() <= 2.0 ** -8 * scale, "bf16 store"
+    base = torch.from_numpy(np.random.default_rng(1).standard_normal((T, N)).astype(np.float32)).cuda()
+    acc = base.clone()
+    ops.gemm_tc(x, wn, acc, ops.EPI_ADD_F32, splits=splits)
+    assert np.abs(f64(acc) - (f64(base) + full[:, :N])).max() <= 2e-5 * scale, "residual add"
+    g, u = full[:, :N], full[:, N:]
+    ref = g / (1 + np.exp(-g)) * u
+    ops.gemm_tc(x, w, out16, ops.EPI_SWIGLU)
+    assert np.abs(f64(out16) - ref).max() <= 2.0 ** -8 * (1 + np.abs(ref).max()), "SwiGLU"
+    assert ops.gemm_tc_status() == 0
+
+
+def test_gemm_tc_matches_the_cuda_core_twin():
+    from borrowed_compute_b200 import ops
+
+    x, w = operands(50, 300, 640, 3)
+    a = torch.empty((50, 300), dtype=torch.float32, device="cuda")
+    b = torch.empty_like(a)
+    ops.gemm_tc(x, w[:300].contiguous(), a, ops.EPI_STORE_F32)
+    ops.gemm_simt(x, w[:300].contiguous(), b, ops.EPI_STORE_F32)
+    assert (a - b).abs().max().item() <= 1e-5 * (1 + b.abs().max().item())
+
+
+def test_gemm_tc_refuses_what_it_cannot_do():
+    from borrowed_compute_b200 import ops
+
+    x, w = operands(4, 64, 100, 4)   # K = 100 is no multiple of 8
+    assert not ops.gemm_tc_accepts(x, w)
+    with pytest.raises(ops.KernelError, match="multiple of 8"):
+        ops.gemm_tc(x, w[:64].contiguous(), torch.empty((4, 64), dtype=torch.float32, device="cuda"), ops.EPI_STORE_F32)
