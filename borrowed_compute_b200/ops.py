@@ -210,6 +210,8 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int, 
     _need(out, "out", torch.float32 if epilogue in (EPI_STORE_F32, EPI_ADD_F32) else torch.bfloat16)
     if tuple(out.shape) != (M, N):
         raise KernelError(f"gemm: out is {tuple(out.shape)}, wanted {(M, N)}")
+    if M == 0:
+        return
     if splits is None:
         splits = gemm_tc_splits(M, N, K, epilogue)
     partial = counters = None
