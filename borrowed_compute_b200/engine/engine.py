@@ -29,6 +29,63 @@ DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.f
           torch.bfloat16: torch.bfloat16, torch.float32: torch.float32}
 
 
+class _DecodeGraph:
+    """One captured decode step for a fixed number of rows."""
+
+    def __init__(self, engine: "Engine", rows: int):
+        self.engine, self.rows = engine, rows
+        dev = engine.rt.device
+        # tokens, row_pos, row_slot, seq_rows (+1), seq_slot, seq_start, want_rows
+        self.sizes = [("tokens", rows), ("row_pos", rows), ("row_slot", rows), ("seq_rows", rows + 1), ("seq_slot", rows),
+                      ("seq_start", rows), ("want_rows", rows)]
+        total = sum(n for _, n in self.sizes)
+        self.ints = torch.zeros(total, dtype=torch.int32, device=dev)
+        self.host = torch.zeros(total, dtype=torch.int32).pin_memory()
+        self.copied: Optional[torch.cuda.Event] = None
+        self.views, at = {}, 0
+        for name, n in self.sizes:
+            self.views[name] = self.ints[at:at + n]
+            at += n
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self.scores: Optional[torch.Tensor] = None
+
+    def _fill(self, plan: StepPlan) -> None:
+        rows, n = self.rows, plan.seqs
+        seq_rows = np.full(rows + 1, plan.rows, dtype=np.int32)
+        seq_rows[: n + 1] = plan.seq_rows
+        seq_slot = np.full(rows, -1, dtype=np.int32)
+        seq_slot[:n] = plan.seq_slot
+        seq_start = np.zeros(rows, dtype=np.int32)
+        seq_start[:n] = plan.seq_start
+        packed = np.concatenate([plan.tokens, plan.row_pos, plan.row_slot, seq_rows, seq_slot, seq_start, np.arange(rows, dtype=np.int32)])
+        if self.copied is not None:
+            self.copied.synchronize()
+        self.host.copy_(torch.from_numpy(packed))
+        self.ints.copy_(self.host, non_blocking=True)
+        if self.copied is None:
+            self.copied = torch.cuda.Event()
+        self.copied.record()
+
+    def _forward(self) -> torch.Tensor:
+        v, rows = self.views, self.rows
+        ctx = StepContext(rows=rows, seqs=rows, tokens=v["tokens"], row_pos=v["row_pos"], row_slot=v["row_slot"], seq_rows=v["seq_rows"],
+                          seq_slot=v["seq_slot"], seq_start=v["seq_start"], max_new=1, max_total=self.engine.max_seq, decode=True,
+                          extras={"graph": True})
+        return self.engine.model.forward(ctx, self.engine.cache, v["want_rows"], rows)
+
+    def run(self, plan: StepPlan) -> torch.Tensor:
+        self._fill(plan)
+        if self.graph is None:
+            self._forward()   # once eagerly: first-use set-up must not happen inside a capture
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                self.scores = self._forward()
+            self.graph = graph
+        self.graph.replay()
+        return self.scores
+
+
 class Engine:
     def __init__(self, config: Mapping[str, Any], model: DecoderModel, typed_config: Any, rt: Runtime, max_tokens: int,
                  max_slots: int, max_seq: int):
@@ -40,6 +97,8 @@ class Engine:
         self._ints: Optional[torch.Tensor] = None
         self._host_ints: Optional[torch.Tensor] = None
         self._staged: Optional[torch.cuda.Event] = None
+        self._graphs: Dict[int, "_DecodeGraph"] = {}
+        self.use_graphs = True   # decode steps replay a captured CUDA graph
         self.steps_run = 0
 
     # ------------------------------------------------------------------------ construction
@@ -165,16 +224,44 @@ class Engine:
             starts.append(start)
         return starts
 
+    # ------------------------------------------------------------------------ decode graphs
+    @staticmethod
+    def _bucket(n: int) -> int:
+        """Rows a captured decode step is padded to: a power of two up to 16, then
+        multiples of 16 (the smallest token tile of the tensor-core product)."""
+        b = 1
+        while b < n and b < 16:
+            b *= 2
+        return b if n <= 16 else -(-n // 16) * 16
+
+    def _decode_graph_step(self, entries: Sequence[StepEntry], starts: Sequence[int]) -> torch.Tensor:
+        """A step of one token a sequence, replayed from a CUDA graph captured once per
+        padded batch size: the kernels, their order and their buffers are fixed, only the
+        integers that name tokens, positions and slots change."""
+        n = len(entries)
+        bucket = self._bucket(n)
+        g = self._graphs.get(bucket)
+        if g is None:
+            g = self._graphs[bucket] = _DecodeGraph(self, bucket)
+        plan = plan_step(entries, starts, pad_rows_to=bucket)
+        return g.run(plan)[:n]
+
     def step(self, entries: Sequence[StepEntry], pad_rows_to: int = 1) -> torch.Tensor:
         """Runs the given tokens of every entry as one batch from the cache and returns
         the scores [wanted, vocab] (float32, on the device) at the wanted places, in entry
         order then ``want`` order.  ``pad_rows_to`` adds rows that belong to no sequence;
         they change no result."""
         starts = self.check_entries(entries)
-        plan = plan_step(entries, starts, pad_rows_to)
         for e, start in zip(entries, starts):
             self.cache.slots.reserve(e.slot, start + len(e.tokens), rows=len(e.tokens))
         self.cache.sync_tables()
+        if self.use_graphs and pad_rows_to == 1 and all(len(e.tokens) == 1 and tuple(e.want) == (0,) for e in entries):
+            scores = self._decode_graph_step(entries, starts)
+            for e, start in zip(entries, starts):
+                self.cache.slots.commit(e.slot, start + 1)
+            self.steps_run += 1
+            return scores
+        plan = plan_step(entries, starts, pad_rows_to)
         v = self._stage(plan)
         ctx = StepContext(
             rows=plan.padded_rows, seqs=plan.seqs, tokens=v["tokens"], row_pos=v["row_pos"], row_slot=v["row_slot"],

@@ -64,7 +64,12 @@ def _suffix(dtype: torch.dtype) -> str:
     raise KernelError(f"no kernels for {dtype}: float32 and bfloat16 only")
 
 
+launches = 0   # kernels launched through this module since import (a captured graph replays them uncounted)
+
+
 def _call(fn, *args) -> None:
+    global launches
+    launches += 1
     status = fn(*args)
     if status != 0:
         msg = lib().bc_last_error()
