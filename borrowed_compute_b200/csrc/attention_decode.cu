@@ -1,0 +1,320 @@
+// Decode attention for bf16: one new row a sequence against its paged cache, the cached
+// positions split across blocks, the query heads of one kv head sharing every key and value
+// read.
+//
+// What is computed is the reference's attention (crates/bc-infer/src/model.rs:448-481;
+// online softmax as crates/bc-infer/src/gpu/kernels.h:271-324).  How: a block takes
+// (row, kv head, split).  The heads that share the kv head (H / G of them, at most 16)
+// are the 16 rows of an m16n8k16 tensor-core tile, so a 64-position page of keys is read
+// once for all of them.  Pages stream through shared memory by cp.async (three stages);
+// each of the four warps takes 16 of a page's 64 positions: S = Q K^T, a running maximum
+// and sum in float, P V accumulated in float.  The four warps' partial results are merged
+// in a fixed order; with several splits each block leaves (sum, maximum, normaliser) in
+// scratch memory and the last block to finish merges the splits, again in a fixed order,
+// so the result is the same bits whatever the scheduling.  The launch does not depend on
+// the sequence lengths (they are read on the device), so one captured graph serves every
+// step of a batch.
+#include "common.cuh"
+
+#define AD_THREADS 128
+#define AD_STAGES 3
+#define AD_MAX_GROUP 16
+
+__device__ __forceinline__ uint32_t ad_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void mma_16816(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Byte offset of 16-byte chunk c of row r in a [64][D] bf16 tile.  Rows of 128 bytes or
+// more get their chunks xor-ed with the row so that eight rows hit eight different banks.
+template <int D> __device__ __forceinline__ int tile_offset(int r, int c) {
+    constexpr int CHUNKS = D / 8;
+    constexpr int SWZ = (CHUNKS % 8 == 0) ? 7 : 0;
+    return (r * CHUNKS + (c ^ (r & SWZ))) * 16;
+}
+
+template <int D>
+__global__ void __launch_bounds__(AD_THREADS)
+attention_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
+                        const int* __restrict__ page_table, const int* __restrict__ row_pos, const int* __restrict__ row_slot,
+                        bf16* __restrict__ out, float* __restrict__ scratch, int* __restrict__ counters, int H, int G, int max_pages,
+                        int n_pages, int window, float scale_log2) {
+    constexpr int CHUNKS = D / 8;              // 16-byte chunks a row
+    constexpr int TILE_BYTES = 64 * D * 2;     // one page of one kv head
+    constexpr int KD = D / 16;                 // k-steps of Q K^T
+    constexpr int ND = D / 8;                  // 8-wide dimension blocks of the output
+    extern __shared__ __align__(128) uint8_t smem[];
+    __shared__ int is_last;
+
+    const int split = blockIdx.x, n_splits = gridDim.x, g = blockIdx.y, r = blockIdx.z;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int gq = lane >> 2, tq = lane & 3;
+    const int group = H / G;
+    const int slot = row_slot[r];
+    if (slot < 0) {
+        if (split == 0)
+            for (int i = threadIdx.x; i < group * D; i += AD_THREADS) out[((size_t)r * H + (size_t)g * group) * D + i] = __float2bfloat16_rn(0.0f);
+        return;
+    }
+    const int pos = row_pos[r];
+    const int lo = window > 0 && pos + 1 > window ? pos + 1 - window : 0;
+    const int first_tile = lo / BC_PAGE, end_tile = pos / BC_PAGE + 1;
+    const int per_split = (end_tile - first_tile + n_splits - 1) / n_splits;
+    const int t_begin = first_tile + split * per_split;
+    const int t_end = min(end_tile, t_begin + per_split);
+    const int n_tiles = max(0, t_end - t_begin);
+    const int* pages = page_table + (size_t)slot * max_pages;
+
+    // Q fragments: row i of the tile is head g * group + i (zero past the group).
+    uint32_t qf[KD][4];
+    {
+        const bf16* qr = q + (size_t)r * q_stride + (size_t)g * group * D;
+#pragma unroll
+        for (int kd = 0; kd < KD; kd++) {
+            const int d0 = kd * 16 + 2 * tq;
+            qf[kd][0] = gq < group ? *reinterpret_cast<const uint32_t*>(qr + (size_t)gq * D + d0) : 0u;
+            qf[kd][1] = gq + 8 < group ? *reinterpret_cast<const uint32_t*>(qr + (size_t)(gq + 8) * D + d0) : 0u;
+            qf[kd][2] = gq < group ? *reinterpret_cast<const uint32_t*>(qr + (size_t)gq * D + d0 + 8) : 0u;
+            qf[kd][3] = gq + 8 < group ? *reinterpret_cast<const uint32_t*>(qr + (size_t)(gq + 8) * D + d0 + 8) : 0u;
+        }
+    }
+
+    auto load_tile = [&](int tile, int stage) {
+        int page = tile < max_pages ? pages[tile] : -1;
+        if (page < 0 || page >= n_pages) page = 0;   // never read: every position of such a tile is masked below
+        const bf16* ks = k_cache + ((size_t)page * G + g) * BC_PAGE * D;
+        const bf16* vs = v_cache + ((size_t)page * G + g) * BC_PAGE * D;
+        const uint32_t kb = ad_smem(smem + (size_t)stage * 2 * TILE_BYTES), vb = kb + TILE_BYTES;
+        for (int i = threadIdx.x; i < 64 * CHUNKS; i += AD_THREADS) {
+            const int row = i / CHUNKS, c = i - row * CHUNKS;
+            cp_async16(kb + tile_offset<D>(row, c), ks + (size_t)row * D + c * 8);
+            cp_async16(vb + tile_offset<D>(row, c), vs + (size_t)row * D + c * 8);
+        }
+    };
+
+    float o[ND][4];
+#pragma unroll
+    for (int i = 0; i < ND; i++) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.0f, l1 = 0.0f;   // rows gq and gq + 8
+
+#pragma unroll
+    for (int s = 0; s < AD_STAGES - 1; s++) {
+        if (s < n_tiles) load_tile(t_begin + s, s);
+        cp_async_commit();
+    }
+    for (int it = 0; it < n_tiles; it++) {
+        cp_async_wait<AD_STAGES - 2>();
+        __syncthreads();
+        if (it + AD_STAGES - 1 < n_tiles) load_tile(t_begin + it + AD_STAGES - 1, (it + AD_STAGES - 1) % AD_STAGES);
+        cp_async_commit();
+        const int tile = t_begin + it;
+        const bool page_ok = tile < max_pages && pages[tile] >= 0 && pages[tile] < n_pages;
+        const uint32_t kb = ad_smem(smem + (size_t)(it % AD_STAGES) * 2 * TILE_BYTES), vb = kb + TILE_BYTES;
+        const int key0 = 16 * warp;   // this warp's 16 positions of the page
+
+        float s[2][4] = {};
+#pragma unroll
+        for (int kd = 0; kd < KD; kd++) {
+            uint32_t b0, b1, b2, b3;
+            const int j = lane >> 3, rr = lane & 7;
+            ldmatrix_x4(kb + tile_offset<D>(key0 + (j >> 1) * 8 + rr, kd * 2 + (j & 1)), b0, b1, b2, b3);
+            mma_16816(s[0], qf[kd], b0, b1);
+            mma_16816(s[1], qf[kd], b2, b3);
+        }
+        // Scores in the log2 domain; positions outside [lo, pos] do not exist for this row.
+        float tmax0 = -INFINITY, tmax1 = -INFINITY;
+#pragma unroll
+        for (int nb = 0; nb < 2; nb++)
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                const int t = tile * BC_PAGE + key0 + nb * 8 + 2 * tq + (e & 1);
+                const bool seen = page_ok && t >= lo && t <= pos;
+                s[nb][e] = seen ? s[nb][e] * scale_log2 : -INFINITY;
+                if (e < 2) tmax0 = fmaxf(tmax0, s[nb][e]);
+                else tmax1 = fmaxf(tmax1, s[nb][e]);
+            }
+        tmax0 = fmaxf(tmax0, __shfl_xor_sync(0xffffffffu, tmax0, 1));
+        tmax0 = fmaxf(tmax0, __shfl_xor_sync(0xffffffffu, tmax0, 2));
+        tmax1 = fmaxf(tmax1, __shfl_xor_sync(0xffffffffu, tmax1, 1));
+        tmax1 = fmaxf(tmax1, __shfl_xor_sync(0xffffffffu, tmax1, 2));
+        const float mn0 = fmaxf(m0, tmax0), mn1 = fmaxf(m1, tmax1);
+        const float c0 = mn0 == -INFINITY ? 1.0f : exp2f(m0 - mn0), c1 = mn1 == -INFINITY ? 1.0f : exp2f(m1 - mn1);
+        const float base0 = mn0 == -INFINITY ? 0.0f : mn0, base1 = mn1 == -INFINITY ? 0.0f : mn1;
+        float p[2][4];
+#pragma unroll
+        for (int nb = 0; nb < 2; nb++) {
+            p[nb][0] = exp2f(s[nb][0] - base0);
+            p[nb][1] = exp2f(s[nb][1] - base0);
+            p[nb][2] = exp2f(s[nb][2] - base1);
+            p[nb][3] = exp2f(s[nb][3] - base1);
+        }
+        l0 = l0 * c0 + (p[0][0] + p[0][1] + p[1][0] + p[1][1]);
+        l1 = l1 * c1 + (p[0][2] + p[0][3] + p[1][2] + p[1][3]);
+        m0 = mn0;
+        m1 = mn1;
+        uint32_t pf[4] = {pack_bf16(p[0][0], p[0][1]), pack_bf16(p[0][2], p[0][3]), pack_bf16(p[1][0], p[1][1]), pack_bf16(p[1][2], p[1][3])};
+#pragma unroll
+        for (int nd = 0; nd < ND; nd += 2) {
+            o[nd][0] *= c0; o[nd][1] *= c0; o[nd][2] *= c1; o[nd][3] *= c1;
+            o[nd + 1][0] *= c0; o[nd + 1][1] *= c0; o[nd + 1][2] *= c1; o[nd + 1][3] *= c1;
+            uint32_t b0, b1, b2, b3;
+            const int j = lane >> 3, rr = lane & 7;
+            ldmatrix_x4_trans(vb + tile_offset<D>(key0 + (j & 1) * 8 + rr, nd + (j >> 1)), b0, b1, b2, b3);
+            mma_16816(o[nd], pf, b0, b1);
+            mma_16816(o[nd + 1], pf, b2, b3);
+        }
+    }
+    cp_async_wait<0>();
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    __syncthreads();
+
+    // Merge the four warps (each saw other positions) in the order 0, 1, 2, 3.
+    float* wm = reinterpret_cast<float*>(smem);              // [4][16] maxima
+    float* wl = wm + 4 * 16;                                 // [4][16] sums
+    float* wo = wl + 4 * 16;                                 // [4][16][D] weighted values
+    if (tq == 0) {
+        wm[warp * 16 + gq] = m0;
+        wm[warp * 16 + gq + 8] = m1;
+        wl[warp * 16 + gq] = l0;
+        wl[warp * 16 + gq + 8] = l1;
+    }
+#pragma unroll
+    for (int nd = 0; nd < ND; nd++) {
+        float* base = wo + (size_t)warp * 16 * D + nd * 8 + 2 * tq;
+        base[(size_t)gq * D] = o[nd][0];
+        base[(size_t)gq * D + 1] = o[nd][1];
+        base[(size_t)(gq + 8) * D] = o[nd][2];
+        base[(size_t)(gq + 8) * D + 1] = o[nd][3];
+    }
+    __syncthreads();
+    // scratch: [row][head][split][D + 2]: the un-normalised sum, then maximum and normaliser.
+    const int stride = D + 2;
+    for (int i = threadIdx.x; i < group * D; i += AD_THREADS) {
+        const int hr = i / D, d = i - hr * D;
+        float M = -INFINITY;
+        for (int w = 0; w < 4; w++) M = fmaxf(M, wm[w * 16 + hr]);
+        float L = 0.0f, O = 0.0f;
+        for (int w = 0; w < 4; w++) {
+            const float mw = wm[w * 16 + hr];
+            const float f = mw == -INFINITY ? 0.0f : exp2f(mw - M);
+            L += wl[w * 16 + hr] * f;
+            O += wo[((size_t)w * 16 + hr) * D + d] * f;
+        }
+        const int h = g * group + hr;
+        if (n_splits == 1) {
+            out[((size_t)r * H + h) * D + d] = __float2bfloat16_rn(L > 0.0f ? O / L : 0.0f);
+        } else {
+            float* dst = scratch + (((size_t)r * H + h) * n_splits + split) * stride;
+            __stcg(dst + d, O);
+            if (d == 0) {
+                __stcg(dst + D, M);
+                __stcg(dst + D + 1, L);
+            }
+        }
+    }
+    if (n_splits == 1) return;
+
+    // The last block of this (row, kv head) to arrive merges the splits in order.
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const int arrived = atomicAdd(&counters[r * G + g], 1);
+        is_last = arrived == n_splits - 1;
+        if (is_last) counters[r * G + g] = 0;   // ready for the next launch
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    for (int i = threadIdx.x; i < group * D; i += AD_THREADS) {
+        const int hr = i / D, d = i - hr * D;
+        const int h = g * group + hr;
+        const float* src = scratch + ((size_t)r * H + h) * n_splits * stride;
+        float M = -INFINITY;
+        for (int sp = 0; sp < n_splits; sp++) M = fmaxf(M, __ldcg(src + (size_t)sp * stride + D));
+        float L = 0.0f, O = 0.0f;
+        for (int sp = 0; sp < n_splits; sp++) {
+            const float ms = __ldcg(src + (size_t)sp * stride + D);
+            const float f = ms == -INFINITY ? 0.0f : exp2f(ms - M);
+            L += __ldcg(src + (size_t)sp * stride + D + 1) * f;
+            O += __ldcg(src + (size_t)sp * stride + d) * f;
+        }
+        out[((size_t)r * H + h) * D + d] = __float2bfloat16_rn(L > 0.0f ? O / L : 0.0f);
+    }
+}
+
+template <int D>
+static int launch(const void* q, int q_stride, const void* k_cache, const void* v_cache, const int* page_table, const int* row_pos,
+                  const int* row_slot, void* out, float* scratch, int* counters, int rows, int H, int G, int max_pages, int n_pages,
+                  int window, float scale, int n_splits, cudaStream_t s) {
+    constexpr int TILE_BYTES = 64 * D * 2;
+    constexpr int MERGE_BYTES = (2 * 4 * 16 + 4 * 16 * D) * 4;
+    constexpr int SMEM = AD_STAGES * 2 * TILE_BYTES > MERGE_BYTES ? AD_STAGES * 2 * TILE_BYTES : MERGE_BYTES;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+        if (e != cudaSuccess) {
+            bc_set_error("attention_decode: cannot set shared memory to %d: %s", SMEM, cudaGetErrorString(e));
+            return (int)e;
+        }
+        configured = true;
+    }
+    dim3 grid(n_splits, G, rows);
+    attention_decode_kernel<D><<<grid, AD_THREADS, SMEM, s>>>((const bf16*)q, q_stride, (const bf16*)k_cache, (const bf16*)v_cache, page_table,
+                                                             row_pos, row_slot, (bf16*)out, scratch, counters, H, G, max_pages, n_pages, window,
+                                                             scale * 1.4426950408889634f);
+    BC_LAUNCH_STATUS();
+}
+
+// Whether this kernel takes the sizes (else the caller uses the one-warp-a-row kernel).
+extern "C" int bc_attention_decode_accepts(int H, int G, int D) {
+    return G > 0 && H % G == 0 && H / G <= AD_MAX_GROUP && D % 16 == 0 && D >= 16 && D <= 128;
+}
+
+// Floats of scratch and ints of counters for `rows` rows cut into `n_splits`.
+extern "C" int bc_attention_decode_workspace(int rows, int H, int G, int D, int n_splits, long long* floats, long long* ints) {
+    *floats = n_splits > 1 ? (long long)rows * H * n_splits * (D + 2) : 0;
+    *ints = n_splits > 1 ? (long long)rows * G : 0;
+    return BC_OK;
+}
+
+// q: row r's head h at q + r * q_stride + h * D.  scratch / counters: see above; counters
+// zero before the first launch (every launch leaves them zero).  Rows must be <= 65535.
+extern "C" int bc_attention_decode_bf16(const void* q, int q_stride, const void* k_cache, const void* v_cache, const int* page_table,
+                                        const int* row_pos, const int* row_slot, void* out, float* scratch, int* counters, int rows, int H,
+                                        int G, int D, int max_pages, int n_pages, int window, float scale, int n_splits, cudaStream_t s) {
+    BC_CHECK_ARG(rows >= 0 && rows <= 65535, "attention_decode: %d rows (at most 65535)", rows);
+    BC_CHECK_ARG(bc_attention_decode_accepts(H, G, D), "attention_decode: H=%d G=%d D=%d is outside what this kernel takes "
+                 "(at most %d heads a kv head, head size a multiple of 16 up to 128)", H, G, D, AD_MAX_GROUP);
+    BC_CHECK_ARG(n_splits >= 1 && n_splits <= 65535 && G <= 65535, "attention_decode: bad split count %d", n_splits);
+    BC_CHECK_ARG(n_splits == 1 || (scratch && counters), "attention_decode: splits need scratch memory");
+    BC_CHECK_ARG(q_stride % 2 == 0 && ((uintptr_t)q % 4 == 0), "attention_decode: q must be 4-byte aligned with an even stride");
+    if (rows == 0) return BC_OK;
+#define AD_CASE(DD) \
+    case DD: return launch<DD>(q, q_stride, k_cache, v_cache, page_table, row_pos, row_slot, out, scratch, counters, rows, H, G, max_pages, n_pages, window, scale, n_splits, s);
+    switch (D) {
+        AD_CASE(16) AD_CASE(32) AD_CASE(48) AD_CASE(64) AD_CASE(80) AD_CASE(96) AD_CASE(112) AD_CASE(128)
+    }
+#undef AD_CASE
+    bc_set_error("attention_decode: no kernel for head size %d", D);
+    return BC_ERR_ARG;
+}

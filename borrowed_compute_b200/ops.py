@@ -263,6 +263,66 @@ def attention_rows(q: torch.Tensor, q_stride: int, k_cache: torch.Tensor, v_cach
           _c_int(page_table.shape[1]), _c_int(k_cache.shape[0]), _c_int(window), _c_float(scale), _stream())
 
 
+_decode_scratch = {}
+
+
+def attention_decode_accepts(heads: int, kv_heads: int, head_dim: int, dtype: torch.dtype) -> bool:
+    """Whether the split decode kernel takes these sizes (bf16; at most 16 heads a kv head;
+    head size a multiple of 16 up to 128).  Otherwise attention_rows serves."""
+    return dtype == torch.bfloat16 and bool(_fn("bc_attention_decode_accepts")(_c_int(heads), _c_int(kv_heads), _c_int(head_dim)))
+
+
+def attention_decode_splits(rows: int, kv_heads: int, max_pages: int) -> int:
+    """Splits of the cached positions so that rows * kv_heads * splits blocks fill the
+    device about twice over; never more than a sequence can have pages."""
+    return max(1, min(-(-296 // max(1, rows * kv_heads)), max_pages, 64))
+
+
+def _decode_workspace(device: torch.device, floats: int, ints: int):
+    """Scratch of the split decode kernel, one a device, grown outside of any capture and
+    never freed (a captured graph keeps pointing at the buffer it saw)."""
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    held = _decode_scratch.setdefault(key, [])
+    for f, c in held:
+        if f.numel() >= floats and c.numel() >= ints:
+            return f, c
+    if torch.cuda.is_current_stream_capturing():
+        raise KernelError("attention_decode: scratch memory must exist before a graph is captured (run the step once eagerly)")
+    f = torch.empty(max(floats, 1 << 20), dtype=torch.float32, device=device)
+    c = torch.zeros(max(ints, 1 << 14), dtype=torch.int32, device=device)
+    held.append((f, c))
+    return f, c
+
+
+def attention_decode(q: torch.Tensor, q_stride: int, k_cache: torch.Tensor, v_cache: torch.Tensor, page_table: torch.Tensor,
+                     row_pos: torch.Tensor, row_slot: torch.Tensor, out: torch.Tensor, heads: int, kv_heads: int, head_dim: int,
+                     window: int = 0, scale: Optional[float] = None, splits: Optional[int] = None) -> None:
+    """Attention of one new row a sequence (bf16): the cached positions are split across
+    blocks and the heads of a kv head share each read; results are merged in a fixed order."""
+    _need(q, "q", torch.bfloat16)
+    _need(k_cache, "k_cache", torch.bfloat16)
+    _need(v_cache, "v_cache", torch.bfloat16)
+    _need(page_table, "page_table", torch.int32)
+    _need(row_pos, "row_pos", torch.int32)
+    _need(row_slot, "row_slot", torch.int32)
+    _need(out, "out", torch.bfloat16)
+    rows = out.shape[0]
+    if out.shape[1] != heads * head_dim:
+        raise KernelError(f"attention: out width {out.shape[1]} is not heads * head_dim")
+    if tuple(k_cache.shape[1:]) != (kv_heads, PAGE, head_dim) or k_cache.shape != v_cache.shape:
+        raise KernelError(f"attention: cache is {tuple(k_cache.shape)}, wanted [pages, {kv_heads}, {PAGE}, {head_dim}]")
+    if scale is None:
+        scale = 1.0 / float(head_dim) ** 0.5
+    if splits is None:
+        splits = attention_decode_splits(rows, kv_heads, page_table.shape[1])
+    scratch = counters = None
+    if splits > 1:
+        scratch, counters = _decode_workspace(q.device, rows * heads * splits * (head_dim + 2), rows * kv_heads)
+    _call(_fn("bc_attention_decode_bf16"), _ptr(q), _c_int(q_stride), _ptr(k_cache), _ptr(v_cache), _ptr(page_table), _ptr(row_pos),
+          _ptr(row_slot), _ptr(out), _ptr(scratch), _ptr(counters), _c_int(rows), _c_int(heads), _c_int(kv_heads), _c_int(head_dim),
+          _c_int(page_table.shape[1]), _c_int(k_cache.shape[0]), _c_int(window), _c_float(scale), _c_int(splits), _stream())
+
+
 # ---------------------------------------------------------------------------------- sampling
 
 def argmax(scores: torch.Tensor, out: torch.Tensor) -> None:

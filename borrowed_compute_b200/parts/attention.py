@@ -66,5 +66,9 @@ class GroupedQueryAttention(Mixer):
 
     def attend(self, qkv: torch.Tensor, out: torch.Tensor, ctx: StepContext, mem: RunMemory) -> None:
         H, G, D = self.heads, self.kv_heads, self.head_dim
+        if ctx.decode and ops.attention_decode_accepts(H, G, D, qkv.dtype):
+            ops.attention_decode(qkv, (H + 2 * G) * D, mem.k_pages, mem.v_pages, mem.page_table, ctx.row_pos, ctx.row_slot, out,
+                                 H, G, D, window=self.window, scale=self.scale)
+            return
         ops.attention_rows(qkv, (H + 2 * G) * D, mem.k_pages, mem.v_pages, mem.page_table, ctx.row_pos, ctx.row_slot, out,
                            H, G, D, window=self.window, scale=self.scale)

@@ -238,6 +238,52 @@ def test_attention_finds_one_far_key(dtype):
             assert np.abs(f64(out).reshape(H, D) - want).max() > 0.05, f"window {outside} must not see position {far}"
 
 
+@pytest.mark.parametrize("H,G,D", [(6, 3, 48), (4, 4, 16), (16, 1, 32), (32, 8, 128), (8, 2, 64)])
+@pytest.mark.parametrize("splits", [1, 3, 8])
+@pytest.mark.parametrize("window", [0, 70])
+def test_attention_decode(H, G, D, splits, window):
+    """The split bf16 decode kernel against the float64 formula and its one-warp twin, for
+    lengths around page and tile edges, scattered pages, padding rows."""
+    from borrowed_compute_b200 import ops
+
+    n_pages = 24
+    lengths = [1, 17, 64, 65, 200, 700]
+    r = rng(H * 100 + D)
+    free = list(r.permutation(n_pages))
+    table = np.full((len(lengths), 12), -1, dtype=np.int32)
+    kp = np.zeros((n_pages, G, 64, D), dtype=np.float32)
+    vp = np.zeros_like(kp)
+    ks, vs = [], []
+    for s, n in enumerate(lengths):
+        pages = [int(free.pop()) for _ in range((n + 63) // 64)]
+        table[s, :len(pages)] = pages
+        k, v = r.standard_normal((n, G, D)).astype(np.float32), r.standard_normal((n, G, D)).astype(np.float32)
+        ks.append(k), vs.append(v)
+        kp += paged(k, pages, G, D, n_pages, torch.bfloat16)
+        vp += paged(v, pages, G, D, n_pages, torch.bfloat16)
+    row_slot = np.array([0, 1, -1, 2, 3, 4, 5], dtype=np.int32)
+    row_pos = np.array([n - 1 for n in lengths[:2]] + [0] + [n - 1 for n in lengths[2:]], dtype=np.int32)
+    q = (r.standard_normal((7, H * D)) * 1.5).astype(np.float32)
+    args = (dev(q, torch.bfloat16), H * D, dev(kp, torch.bfloat16), dev(vp, torch.bfloat16), dev(table), dev(row_pos), dev(row_slot))
+    out = torch.full((7, H * D), 9.0, dtype=torch.bfloat16, device="cuda")
+    twin = torch.empty_like(out)
+    ops.attention_decode(*args, out, H, G, D, window=window, splits=splits)
+    ops.attention_rows(*args, twin, H, G, D, window=window)
+    again = torch.empty_like(out)
+    ops.attention_decode(*args, again, H, G, D, window=window, splits=splits)
+    assert torch.equal(out, again), "the same launch twice must give the same bits"
+    got, qs = f64(out), stored(q, torch.bfloat16)
+    for i in range(7):
+        if row_slot[i] < 0:
+            assert np.all(got[i] == 0.0)
+            continue
+        s, p = row_slot[i], row_pos[i]
+        ref = attention_reference(qs[i].reshape(H, D), stored(ks[s][:p + 1], torch.bfloat16), stored(vs[s][:p + 1], torch.bfloat16), window)
+        # Probabilities are rounded to bf16 before they weigh the values: 2^-8 of the largest value.
+        assert np.abs(got[i].reshape(H, D) - ref).max() <= 2.0 ** -7 * (1 + np.abs(ref).max()), f"row {i}"
+    assert (out.float() - twin.float()).abs().max().item() <= 2.0 ** -6
+
+
 def test_argmax_first_largest_wins():
     from borrowed_compute_b200 import ops
 
