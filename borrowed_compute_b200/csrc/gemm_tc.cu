@@ -20,8 +20,8 @@
 //     epilogue: store bf16, store float (scores), add into the float residual stream, or
 //     SwiGLU over a weight that stacks gate rows on up rows (two accumulators, one B tile).
 //   - With split-K (grid z > 1, for products with few weight tiles and a long K) every
-//     split adds its partial into a float workspace tile in a fixed order: split s waits
-//     for a tile counter to reach s, so the sum's order never changes from run to run.
+//     split leaves its partial tile in scratch memory and the block that arrives last adds
+//     them in the order of the splits, so the sum's order never changes from run to run.
 //
 // Every wait is bounded: after about a second without progress a thread records where it
 // gave up in a status word, stops waiting, and the block frees its TMEM and returns.
@@ -131,7 +131,7 @@ __device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.0f +
 // ---------------------------------------------------------------------------------- kernel
 struct TcParams {
     void* out;          // bf16 [T, N] (store, swiglu) or float [T, N] (store_f32, add_f32)
-    float* partial;     // split-K: float [tiles, BN, TC_BM] workspace (contents need not be zero)
+    float* partial;     // split-K: float [tiles, splits, BN, TC_BM] scratch (contents need not be zero)
     int* counters;      // split-K: four a tile, zero before the first launch (a launch leaves them zero)
     int T, N, K;
     int up_row_offset;  // SwiGLU: rows of the up half start here in W
@@ -214,48 +214,65 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         const int q = warp & 3;
         const int n = n0 + 32 * q + lane;
         const bool split = gridDim.z > 1;
-        const bool last = blockIdx.z == gridDim.z - 1;
         const int tile = blockIdx.y * gridDim.x + blockIdx.x;
-        // Split-K: the four row quarters of a tile each have a counter; split z adds its
-        // partial to the quarter's workspace once the counter says z, so the order of the
-        // sum is fixed.  Workspace layout [column][row]: a warp touches 32 consecutive floats.
-        float* part = split ? p.partial + (size_t)tile * TC_BM * BN + 32 * q + lane : nullptr;
+        // Split-K: every split leaves its partial tile in scratch memory; the four row
+        // quarters of a tile each have a counter, and the warp that arrives last adds the
+        // splits' partials in the order 0, 1, 2 .., so the sum never depends on timing.
+        // Scratch layout [tile][split][column][row]: a warp touches 32 consecutive floats.
+        const size_t part_tile = (size_t)TC_BM * BN;
+        float* part = split ? p.partial + ((size_t)tile * gridDim.z + blockIdx.z) * part_tile + 32 * q + lane : nullptr;
         int* counter = split ? p.counters + (size_t)tile * 4 + q : nullptr;
         bool ok = true;
-        if (lane == 0) {
-            ok = mbar_wait(acc_bar, 0, 3);
-            if (ok && split && blockIdx.z > 0) {
-                const long long start = clock64();
-                while (atomicAdd(counter, 0) != (int)blockIdx.z) {
-                    if (clock64() - start > TC_WAIT_CYCLES) {
-                        atomicCAS(&g_tc_status, 0, (4 << 16) | (int)(blockIdx.x & 0xffff));
-                        ok = false;
-                        break;
-                    }
+        if (lane == 0) ok = mbar_wait(acc_bar, 0, 3);
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        tc_fence_after();
+        const uint32_t taddr = tmem + ((uint32_t)(32 * q) << 16);
+        bool finish = !split;   // this warp writes the output
+        if (split) {
+            if (ok) {
+#pragma unroll 1
+                for (int c0 = 0; c0 < BN; c0 += 16) {
+                    uint32_t v[16];
+                    tmem_load16(taddr + c0, v);
+                    tmem_load_wait();
+#pragma unroll
+                    for (int j = 0; j < 16; j++) __stcg(part + (size_t)(c0 + j) * TC_BM, __uint_as_float(v[j]));
                 }
             }
+            __threadfence();
+            __syncwarp();
+            int arrived = 0;
+            if (lane == 0) arrived = atomicAdd(counter, 1);
+            arrived = __shfl_sync(0xffffffffu, arrived, 0);
+            finish = arrived == (int)gridDim.z - 1;
+            if (finish) {
+                __threadfence();
+                if (lane == 0) *counter = 0;   // ready for the next launch
+            }
         }
-        ok = __shfl_sync(0xffffffffu, ok, 0);
-        __threadfence();
-        tc_fence_after();
-        if (ok) {
-            const uint32_t taddr = tmem + ((uint32_t)(32 * q) << 16);
+        if (finish && ok) {
+            const float* all = split ? p.partial + (size_t)tile * gridDim.z * part_tile + 32 * q + lane : nullptr;
 #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += 16) {
                 uint32_t v[16], u[16];
-                tmem_load16(taddr + c0, v);
-                if (EPI == EPI_SWIGLU) tmem_load16(taddr + BN + c0, u);
-                tmem_load_wait();
+                if (!split) {
+                    tmem_load16(taddr + c0, v);
+                    if (EPI == EPI_SWIGLU) tmem_load16(taddr + BN + c0, u);
+                    tmem_load_wait();
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 16; j++) v[j] = 0u;
+                    for (int z = 0; z < (int)gridDim.z; z++) {
+#pragma unroll
+                        for (int j = 0; j < 16; j++)
+                            v[j] = __float_as_uint(__uint_as_float(v[j]) + __ldcg(all + (size_t)z * part_tile + (size_t)(c0 + j) * TC_BM));
+                    }
+                }
 #pragma unroll
                 for (int j = 0; j < 16; j++) {
                     const int t = t0 + c0 + j;
-                    float val = __uint_as_float(v[j]);
-                    if (split) {
-                        float* w = part + (size_t)(c0 + j) * TC_BM;
-                        if (blockIdx.z > 0) val += __ldcg(w);
-                        if (!last) __stcg(w, val);
-                    }
-                    if (last && t < p.T && n < p.N) {
+                    const float val = __uint_as_float(v[j]);
+                    if (t < p.T && n < p.N) {
                         const size_t o = (size_t)t * p.N + n;
                         if (EPI == EPI_STORE) ((bf16*)p.out)[o] = __float2bfloat16_rn(val);
                         if (EPI == EPI_STORE_F32) ((float*)p.out)[o] = val;
@@ -263,16 +280,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                         if (EPI == EPI_SWIGLU) ((bf16*)p.out)[o] = __float2bfloat16_rn(silu_mul(val, __uint_as_float(u[j])));
                     }
                 }
-            }
-        }
-        if (split) {
-            // Hand the quarter to the next split (or, from the last, back to zero for the
-            // next launch) only after this warp's sums are visible.
-            __threadfence();
-            __syncwarp();
-            if (lane == 0) {
-                if (last) atomicExch(counter, 0);
-                else if (ok) atomicAdd(counter, 1);
             }
         }
     }
@@ -401,7 +408,7 @@ extern "C" int bc_gemm_tc_token_tile(int T, int epilogue) {
 extern "C" int bc_gemm_tc_workspace(int T, int N, int epilogue, int splits, long long* floats, long long* ints) {
     const int bn = bc_gemm_tc_token_tile(T, epilogue);
     const long long tiles = (long long)((N + TC_BM - 1) / TC_BM) * ((T + bn - 1) / bn);
-    *floats = splits > 1 ? tiles * TC_BM * bn : 0;
+    *floats = splits > 1 ? tiles * splits * TC_BM * bn : 0;
     *ints = splits > 1 ? tiles * 4 : 0;
     return BC_OK;
 }

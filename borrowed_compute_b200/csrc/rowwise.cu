@@ -15,6 +15,23 @@ __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict_
     const bool ok = t >= 0 && t < V;
     const T* src = table + (size_t)(ok ? t : 0) * E;
     float* dst = out + (size_t)r * E;
+    if (E % 4 == 0) {
+        // Four elements a thread a turn: rows start 16-byte aligned when E is a multiple of 4 (float) or 8 (bf16).
+        for (int c = 4 * threadIdx.x; c < E; c += 4 * blockDim.x) {
+            float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            if (ok) {
+                if (sizeof(T) == 4) {
+                    v = *reinterpret_cast<const float4*>(src + c);
+                } else {
+                    const uint2 raw = *reinterpret_cast<const uint2*>(src + c);
+                    v = make_float4(__uint_as_float(raw.x << 16), __uint_as_float(raw.x & 0xffff0000u), __uint_as_float(raw.y << 16),
+                                    __uint_as_float(raw.y & 0xffff0000u));
+                }
+            }
+            *reinterpret_cast<float4*>(dst + c) = v;
+        }
+        return;
+    }
     for (int c = threadIdx.x; c < E; c += blockDim.x) dst[c] = ok ? to_f32(src[c]) : 0.0f;
 }
 
@@ -22,6 +39,20 @@ __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict_
 // out[i, c] = x[row(i), c] * rsqrt(mean_c(x^2) + eps) * w[c]; eps inside the root, the
 // weight applied after the scale (model.rs:381-389; gpu/kernels.h:226-233).  `gather`
 // (may be null) picks the rows to normalise, so the head runs on wanted rows only.
+template <class T> __device__ __forceinline__ void store4(T* p, float a, float b, float c, float d);
+template <> __device__ __forceinline__ void store4<float>(float* p, float a, float b, float c, float d) {
+    *reinterpret_cast<float4*>(p) = make_float4(a, b, c, d);
+}
+template <> __device__ __forceinline__ void store4<bf16>(bf16* p, float a, float b, float c, float d) {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+    uint2 raw;
+    raw.x = *reinterpret_cast<uint32_t*>(&lo);
+    raw.y = *reinterpret_cast<uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(p) = raw;
+}
+
+// A thread's share of the sum of squares is taken in ascending column order and the
+// shares are added in a fixed tree, so a row's statistic is the same bits in any batch.
 template <class T>
 __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w, T* __restrict__ out,
                                const int* __restrict__ gather, int E, float eps) {
@@ -29,14 +60,28 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
     const int i = blockIdx.x;
     const int r = gather ? gather[i] : i;
     const float* xr = x + (size_t)r * E;
+    T* o = out + (size_t)i * E;
     float s = 0.0f;
+    if (E % 4 == 0) {
+        for (int c = 4 * threadIdx.x; c < E; c += 4 * blockDim.x) {
+            const float4 v = *reinterpret_cast<const float4*>(xr + c);
+            s += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+        }
+        s = block_sum(s, scratch);
+        const float scale = 1.0f / sqrtf(s / (float)E + eps);
+        for (int c = 4 * threadIdx.x; c < E; c += 4 * blockDim.x) {
+            const float4 v = *reinterpret_cast<const float4*>(xr + c);
+            const float4 g = *reinterpret_cast<const float4*>(w + c);
+            store4<T>(o + c, v.x * scale * g.x, v.y * scale * g.y, v.z * scale * g.z, v.w * scale * g.w);
+        }
+        return;
+    }
     for (int c = threadIdx.x; c < E; c += blockDim.x) {
         float v = xr[c];
         s += v * v;
     }
     s = block_sum(s, scratch);
     const float scale = 1.0f / sqrtf(s / (float)E + eps);
-    T* o = out + (size_t)i * E;
     for (int c = threadIdx.x; c < E; c += blockDim.x) o[c] = from_f32<T>(xr[c] * scale * w[c]);
 }
 
@@ -68,52 +113,44 @@ template <class T>
 __global__ void rope_append_kernel(T* __restrict__ qkv, const float2* __restrict__ cos_sin, const int* __restrict__ row_pos,
                                    const int* __restrict__ row_slot, const int* __restrict__ page_table, T* __restrict__ k_cache,
                                    T* __restrict__ v_cache, int H, int G, int D, int pairing, int max_pages, int n_pages, int write_cache) {
-    const int r = blockIdx.x;
+    // One block a (row, head of the fused projection): q heads, then k heads, then v heads.
+    const int r = blockIdx.x, h = blockIdx.y;
     const int slot = row_slot[r];
     if (slot < 0) return;
     const int pos = row_pos[r];
     const int half = D / 2;
-    T* row = qkv + (size_t)r * (H + 2 * G) * D;
+    T* head = qkv + ((size_t)r * (H + 2 * G) + h) * D;
     int page = -1;
-    if (write_cache && pos / BC_PAGE < max_pages) page = page_table[(size_t)slot * max_pages + pos / BC_PAGE];
+    if (h >= H && write_cache && pos / BC_PAGE < max_pages) page = page_table[(size_t)slot * max_pages + pos / BC_PAGE];
     const bool can_write = page >= 0 && page < n_pages;
     const int in_page = pos % BC_PAGE;
+    if (h >= H + G) {
+        if (!can_write) return;
+        T* dst = v_cache + (((size_t)page * G + (h - H - G)) * BC_PAGE + in_page) * D;
+        for (int d = threadIdx.x; d < D; d += blockDim.x) dst[d] = head[d];
+        return;
+    }
     const float2* cs = cos_sin ? cos_sin + (size_t)pos * half : nullptr;
-
-    const int rot_pairs = (H + G) * half;
-    for (int idx = threadIdx.x; idx < rot_pairs; idx += blockDim.x) {
-        const int h = idx / half, i = idx - h * half;
+    T* dst = h < H ? head : (can_write ? k_cache + (((size_t)page * G + (h - H)) * BC_PAGE + in_page) * D : nullptr);
+    if (!dst) return;
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
         const int a = pairing ? 2 * i : i, b = pairing ? 2 * i + 1 : i + half;
-        T* head = row + (size_t)h * D;
-        float x0 = to_f32(head[a]), x1 = to_f32(head[b]);
+        const float x0 = to_f32(head[a]), x1 = to_f32(head[b]);
         float y0 = x0, y1 = x1;
         if (cs) {
             const float2 c = cs[i];
             y0 = x0 * c.x - x1 * c.y;
             y1 = x0 * c.y + x1 * c.x;
         }
-        if (h < H) {
-            head[a] = from_f32<T>(y0);
-            head[b] = from_f32<T>(y1);
-        } else if (can_write) {
-            T* dst = k_cache + (((size_t)page * G + (h - H)) * BC_PAGE + in_page) * D;
-            dst[a] = from_f32<T>(y0);
-            dst[b] = from_f32<T>(y1);
-        }
-    }
-    if (can_write) {
-        const T* v = row + (size_t)(H + G) * D;
-        for (int idx = threadIdx.x; idx < G * D; idx += blockDim.x) {
-            const int g = idx / D, d = idx - g * D;
-            v_cache[(((size_t)page * G + g) * BC_PAGE + in_page) * D + d] = v[idx];
-        }
+        dst[a] = from_f32<T>(y0);
+        dst[b] = from_f32<T>(y1);
     }
 }
 
 // ------------------------------------------------------------------------------ launchers
-static int pick_threads(int n) {
+static int pick_threads(int n, int cap = 256) {
     int t = 32;
-    while (t < n && t < 256) t <<= 1;
+    while (t < n && t < cap) t <<= 1;
     return t;
 }
 
@@ -121,14 +158,14 @@ static int pick_threads(int n) {
     extern "C" int bc_embed_##SUFFIX(const void* table, const int* tokens, float* out, int rows, int E, int V, cudaStream_t s) { \
         BC_CHECK_ARG(rows >= 0 && E > 0 && V > 0, "embed: bad sizes rows=%d E=%d V=%d", rows, E, V);                             \
         if (rows == 0) return BC_OK;                                                                                             \
-        embed_kernel<T><<<rows, pick_threads(E), 0, s>>>((const T*)table, tokens, out, E, V);                                    \
+        embed_kernel<T><<<rows, pick_threads(E % 4 == 0 ? E / 4 : E, 1024), 0, s>>>((const T*)table, tokens, out, E, V);                                    \
         BC_LAUNCH_STATUS();                                                                                                      \
     }                                                                                                                            \
     extern "C" int bc_rmsnorm_##SUFFIX(const float* x, const float* w, void* out, const int* gather, int rows, int E, float eps, \
                                        cudaStream_t s) {                                                                         \
         BC_CHECK_ARG(rows >= 0 && E > 0 && eps > 0.0f, "rmsnorm: bad sizes rows=%d E=%d eps=%g", rows, E, (double)eps);          \
         if (rows == 0) return BC_OK;                                                                                             \
-        rmsnorm_kernel<T><<<rows, pick_threads(E), 0, s>>>(x, w, (T*)out, gather, E, eps);                                       \
+        rmsnorm_kernel<T><<<rows, pick_threads(E % 4 == 0 ? E / 4 : E, 1024), 0, s>>>(x, w, (T*)out, gather, E, eps);                                       \
         BC_LAUNCH_STATUS();                                                                                                      \
     }                                                                                                                            \
     extern "C" int bc_swiglu_##SUFFIX(const void* gu, void* out, int rows, int F, cudaStream_t s) {                              \
@@ -145,7 +182,8 @@ static int pick_threads(int n) {
                      H, G, D);                                                                                                   \
         BC_CHECK_ARG(pairing == 0 || pairing == 1, "rope_append: pairing %d is neither 0 (half) nor 1 (adjacent)", pairing);     \
         if (rows == 0) return BC_OK;                                                                                             \
-        rope_append_kernel<T><<<rows, 256, 0, s>>>((T*)qkv, (const float2*)cos_sin, row_pos, row_slot, page_table, (T*)k_cache,  \
+        BC_CHECK_ARG(H + 2 * G <= 65535, "rope_append: too many heads (%d)", H + 2 * G);                                          \
+        rope_append_kernel<T><<<dim3(rows, H + 2 * G), pick_threads(D / 2, 128), 0, s>>>((T*)qkv, (const float2*)cos_sin, row_pos, row_slot, page_table, (T*)k_cache,  \
                                                    (T*)v_cache, H, G, D, pairing, max_pages, n_pages, write_cache);              \
         BC_LAUNCH_STATUS();                                                                                                      \
     }

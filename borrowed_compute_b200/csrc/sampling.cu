@@ -212,11 +212,50 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(const float* __r
     if (threadIdx.x == 0) out[r] = pick;
 }
 
-__global__ void __launch_bounds__(SAMPLE_THREADS) argmax_kernel(const float* __restrict__ scores, int V, int* __restrict__ out) {
-    __shared__ ArgBest best_scratch[SAMPLE_WARPS];
-    const int top = block_argmax(scores + (size_t)blockIdx.x * V, V, best_scratch, nullptr);
-    if (threadIdx.x == 0) out[blockIdx.x] = top;
+// Greedy picks for a batch in two short launches: blocks scan chunks of a row and fold
+// their best into one 64-bit word a row (score bits made sortable in the high half, the
+// inverted index in the low half, so the largest word is the largest score and, among
+// equals, the smallest index); a second launch unpacks the words and clears them.
+#define ARGMAX_CHUNK 4096
+
+__device__ __forceinline__ unsigned long long argmax_key(float v, int i) {
+    unsigned u = __float_as_uint(v);
+    u = (u & 0x80000000u) ? ~u : (u | 0x80000000u);     // larger float -> larger unsigned
+    if (v != v) u = 0u;                                  // a NaN never wins
+    return ((unsigned long long)u << 32) | (unsigned long long)(0xffffffffu - (unsigned)i);
 }
+
+__global__ void __launch_bounds__(256) argmax_partial_kernel(const float* __restrict__ scores, int V, unsigned long long* __restrict__ best) {
+    __shared__ unsigned long long part[8];
+    const int r = blockIdx.y, c0 = blockIdx.x * ARGMAX_CHUNK;
+    const float* row = scores + (size_t)r * V;
+    unsigned long long mine = 0ull;
+    for (int i = c0 + threadIdx.x; i < min(V, c0 + ARGMAX_CHUNK); i += blockDim.x) {
+        const unsigned long long k = argmax_key(row[i], i);
+        mine = k > mine ? k : mine;
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+        const unsigned long long other = __shfl_xor_sync(0xffffffffu, mine, o);
+        mine = other > mine ? other : mine;
+    }
+    if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = mine;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < 8; w++) mine = part[w] > mine ? part[w] : mine;
+        atomicMax(&best[r], mine);
+    }
+}
+
+__global__ void argmax_finish_kernel(unsigned long long* __restrict__ best, int* __restrict__ out, int rows) {
+    const int r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r >= rows) return;
+    const unsigned long long k = best[r];
+    out[r] = k == 0ull ? 0 : (int)(0xffffffffu - (unsigned)(k & 0xffffffffull));
+    best[r] = 0ull;
+}
+
+#define ARGMAX_MAX_ROWS 4096
+__device__ unsigned long long g_argmax_best[ARGMAX_MAX_ROWS];   // zero between launches
 
 // scores [rows, V] float; temperature, top_p, seed (64-bit), step (the position of the row
 // sampled) one a row; out [rows] token ids.
@@ -230,7 +269,18 @@ extern "C" int bc_sample(const float* scores, int rows, int V, const float* temp
 
 extern "C" int bc_argmax(const float* scores, int rows, int V, int* out, cudaStream_t s) {
     BC_CHECK_ARG(rows >= 0 && V > 0, "argmax: bad sizes rows=%d V=%d", rows, V);
+    BC_CHECK_ARG(rows <= ARGMAX_MAX_ROWS, "argmax: %d rows are more than %d", rows, ARGMAX_MAX_ROWS);
     if (rows == 0) return BC_OK;
-    argmax_kernel<<<rows, SAMPLE_THREADS, 0, s>>>(scores, V, out);
+    static unsigned long long* best = nullptr;
+    if (!best) {
+        cudaError_t e = cudaGetSymbolAddress((void**)&best, g_argmax_best);
+        if (e != cudaSuccess) {
+            bc_set_error("argmax: %s", cudaGetErrorString(e));
+            return (int)e;
+        }
+    }
+    dim3 grid((V + ARGMAX_CHUNK - 1) / ARGMAX_CHUNK, rows);
+    argmax_partial_kernel<<<grid, 256, 0, s>>>(scores, V, best);
+    argmax_finish_kernel<<<(rows + 127) / 128, 128, 0, s>>>(best, out, rows);
     BC_LAUNCH_STATUS();
 }

@@ -226,7 +226,7 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int, 
         while bn < M and bn < 256:
             bn *= 2
         tiles = -(-N // 128) * -(-M // bn)
-        if tiles * 128 * bn > partial.numel() or tiles * 4 > counters.numel():
+        if tiles * splits * 128 * bn > partial.numel() or tiles * 4 > counters.numel():
             raise KernelError(f"gemm_tc: {tiles} tiles are too many for the split-K scratch; use splits=1")
     _call(_fn("bc_gemm_tc_bf16"), _ptr(x), _ptr(w), _ptr(out), _c_int(M), _c_int(N), _c_int(K), _c_int(epilogue), _c_int(splits),
           _ptr(partial), _ptr(counters), _stream())
