@@ -63,6 +63,8 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ int is_last;
 
+    pdl_launch_dependents();
+    pdl_wait();
     const int split = blockIdx.x, n_splits = gridDim.x, g = blockIdx.y, r = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int gq = lane >> 2, tq = lane & 3;
@@ -279,9 +281,9 @@ static int launch(const void* q, int q_stride, const void* k_cache, const void* 
         configured = true;
     }
     dim3 grid(n_splits, G, rows);
-    attention_decode_kernel<D><<<grid, AD_THREADS, SMEM, s>>>((const bf16*)q, q_stride, (const bf16*)k_cache, (const bf16*)v_cache, page_table,
-                                                             row_pos, row_slot, (bf16*)out, scratch, counters, H, G, max_pages, n_pages, window,
-                                                             scale * 1.4426950408889634f);
+    bc_launch(attention_decode_kernel<D>, grid, dim3(AD_THREADS), (size_t)SMEM, s, (const bf16*)q, q_stride, (const bf16*)k_cache,
+              (const bf16*)v_cache, page_table, row_pos, row_slot, (bf16*)out, scratch, counters, H, G, max_pages, n_pages, window,
+              scale * 1.4426950408889634f);
     BC_LAUNCH_STATUS();
 }
 

@@ -55,6 +55,8 @@ __global__ void __launch_bounds__(WARPS * 32) attention_rows_kernel(const T* __r
                                                                    T* __restrict__ out, int H, int G, int D, int max_pages, int n_pages,
                                                                    int window, float scale) {
     __shared__ __align__(16) float qs[WARPS][MAX_D];
+    pdl_launch_dependents();
+    pdl_wait();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int r = blockIdx.x, h = blockIdx.y * WARPS + warp;
     if (h >= H) return;
@@ -123,8 +125,8 @@ static int launch(const void* q, int q_stride, const void* k_cache, const void* 
     BC_CHECK_ARG(rows <= 2147483647 && (H + WARPS - 1) / WARPS <= 65535, "attention_rows: too many heads (%d)", H);
     if (rows == 0) return BC_OK;
     dim3 grid(rows, (H + WARPS - 1) / WARPS);
-    attention_rows_kernel<T><<<grid, WARPS * 32, 0, s>>>((const T*)q, q_stride, (const T*)k_cache, (const T*)v_cache, page_table, row_pos,
-                                                         row_slot, (T*)out, H, G, D, max_pages, n_pages, window, scale);
+    bc_launch(attention_rows_kernel<T>, grid, dim3(WARPS * 32), 0, s, (const T*)q, q_stride, (const T*)k_cache, (const T*)v_cache, page_table,
+              row_pos, row_slot, (T*)out, H, G, D, max_pages, n_pages, window, scale);
     BC_LAUNCH_STATUS();
 }
 

@@ -38,6 +38,31 @@ void bc_set_error(const char* fmt, ...);
 
 typedef __nv_bfloat16 bf16;
 
+// Programmatic dependent launch: a kernel launched with the attribute may start while its
+// predecessor in the stream is still draining.  Everything before pdl_wait() (set-up, and
+// loads of weights, which no kernel writes) then overlaps the predecessor's tail; pdl_wait()
+// returns once the predecessor has completed and its writes are visible.  Every kernel of
+// this library waits before it touches anything another kernel produced or still reads.
+// Without the attribute both calls do nothing.
+extern int g_bc_pdl;
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <class... KArgs, class... Args>
+static inline cudaError_t bc_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_bc_pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 __device__ __forceinline__ float to_f32(float v) { return v; }
 __device__ __forceinline__ float to_f32(bf16 v) { return __bfloat162float(v); }
 template <class T> __device__ __forceinline__ T from_f32(float v);

@@ -57,13 +57,15 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(const T* __restrict__ X,
     __shared__ float As[BK][BM + 4];
     __shared__ float Bs[BK][BN + 4];
     __shared__ float Cs[EPI == EPI_SWIGLU ? BK : 1][BN + 4];
+    pdl_launch_dependents();
+    pdl_wait();
     const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
     const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
     float acc[4][4] = {};
     float acc2[EPI == EPI_SWIGLU ? 4 : 1][4] = {};
     for (int k0 = 0; k0 < K; k0 += BK) {
         load_tile<T, VEC>(X, M, K, m0, k0, As);
-        load_tile<T, VEC>(W, EPI == EPI_SWIGLU ? N : N, K, n0, k0, Bs);
+        load_tile<T, VEC>(W, N, K, n0, k0, Bs);
         if (EPI == EPI_SWIGLU) load_tile<T, VEC>(W + (size_t)N * K, N, K, n0, k0, Cs);
         __syncthreads();
 #pragma unroll
@@ -116,9 +118,9 @@ static int launch(const void* X, const void* W, void* out, int M, int N, int K, 
     T* oa = (EPI == EPI_STORE || EPI == EPI_SWIGLU) ? (T*)out : nullptr;
     float* of = (EPI == EPI_STORE_F32 || EPI == EPI_ADD_F32) ? (float*)out : nullptr;
     if (vec)
-        gemm_simt_kernel<T, EPI, true><<<grid, 256, 0, s>>>((const T*)X, (const T*)W, oa, of, M, N, K);
+        bc_launch(gemm_simt_kernel<T, EPI, true>, grid, dim3(256), 0, s, (const T*)X, (const T*)W, oa, of, M, N, K);
     else
-        gemm_simt_kernel<T, EPI, false><<<grid, 256, 0, s>>>((const T*)X, (const T*)W, oa, of, M, N, K);
+        bc_launch(gemm_simt_kernel<T, EPI, false>, grid, dim3(256), 0, s, (const T*)X, (const T*)W, oa, of, M, N, K);
     BC_LAUNCH_STATUS();
 }
 

@@ -175,9 +175,25 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     tc_fence_after();
     const uint32_t tmem = tmem_slot;
 
+    pdl_launch_dependents();
     if (warp == 0) {
         if (lane == 0) {
-            for (int i = 0; i < k_iters; i++) {
+            // Weights are written by no kernel, so the first ring of weight tiles is asked
+            // for before the wait on the preceding kernel; activations only after it.
+            const int ahead = min(stages, k_iters);
+            for (int i = 0; i < ahead; i++) {
+                const uint32_t a = smem_u32(smem + (size_t)i * STAGE_BYTES);
+                mbar_expect_tx(full0 + 8 * i, STAGE_BYTES);
+                const int k = (k_first + i) * TC_BK;
+                tma_load_2d(a, &map_w, full0 + 8 * i, k, n0);
+                if (EPI == EPI_SWIGLU) tma_load_2d(a + A_BYTES, &map_w, full0 + 8 * i, k, p.up_row_offset + n0);
+            }
+            pdl_wait();
+            for (int i = 0; i < ahead; i++) {
+                const uint32_t a = smem_u32(smem + (size_t)i * STAGE_BYTES);
+                tma_load_2d(a + N_ACC * A_BYTES, &map_x, full0 + 8 * i, (k_first + i) * TC_BK, t0);
+            }
+            for (int i = ahead; i < k_iters; i++) {
                 const int s = i % stages;
                 if (!mbar_wait(empty0 + 8 * s, ((i / stages) & 1) ^ 1, 1)) break;
                 const uint32_t a = smem_u32(smem + (size_t)s * STAGE_BYTES);
@@ -223,6 +239,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         float* part = split ? p.partial + ((size_t)tile * gridDim.z + blockIdx.z) * part_tile + 32 * q + lane : nullptr;
         int* counter = split ? p.counters + (size_t)tile * 4 + q : nullptr;
         bool ok = true;
+        pdl_wait();   // the output, the scratch and the counters may still be in use by the preceding kernel
         if (lane == 0) ok = mbar_wait(acc_bar, 0, 3);
         ok = __shfl_sync(0xffffffffu, ok, 0);
         tc_fence_after();
@@ -377,7 +394,11 @@ static int launch(const CUtensorMap& mw, const CUtensorMap& mx, TcParams p, int 
         configured = true;
     }
     dim3 grid((p.N + TC_BM - 1) / TC_BM, (p.T + BN - 1) / BN, splits);
-    gemm_tc_kernel<BN, EPI><<<grid, TC_THREADS, smem, s>>>(mw, mx, p);
+    cudaError_t e = bc_launch(gemm_tc_kernel<BN, EPI>, grid, dim3(TC_THREADS), (size_t)smem, s, mw, mx, p);
+    if (e != cudaSuccess) {
+        bc_set_error("gemm_tc: launch failed: %s", cudaGetErrorString(e));
+        return (int)e;
+    }
     BC_LAUNCH_STATUS();
 }
 

@@ -10,6 +10,8 @@
 // table (the host rejects those before launch) yields a row of zeros, never a wild read.
 template <class T>
 __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ tokens, float* __restrict__ out, int E, int V) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int r = blockIdx.x;
     const int t = tokens[r];
     const bool ok = t >= 0 && t < V;
@@ -57,6 +59,8 @@ template <class T>
 __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w, T* __restrict__ out,
                                const int* __restrict__ gather, int E, float eps) {
     __shared__ float scratch[32];
+    pdl_launch_dependents();
+    pdl_wait();
     const int i = blockIdx.x;
     const int r = gather ? gather[i] : i;
     const float* xr = x + (size_t)r * E;
@@ -90,6 +94,8 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
 // kernels.h:330).  The stand-alone form; the serving GEMM fuses it into its epilogue.
 template <class T>
 __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int F, size_t total) {
+    pdl_launch_dependents();
+    pdl_wait();
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= total) return;
     size_t r = i / F;
@@ -114,6 +120,8 @@ __global__ void rope_append_kernel(T* __restrict__ qkv, const float2* __restrict
                                    const int* __restrict__ row_slot, const int* __restrict__ page_table, T* __restrict__ k_cache,
                                    T* __restrict__ v_cache, int H, int G, int D, int pairing, int max_pages, int n_pages, int write_cache) {
     // One block a (row, head of the fused projection): q heads, then k heads, then v heads.
+    pdl_launch_dependents();
+    pdl_wait();
     const int r = blockIdx.x, h = blockIdx.y;
     const int slot = row_slot[r];
     if (slot < 0) return;
@@ -158,21 +166,21 @@ static int pick_threads(int n, int cap = 256) {
     extern "C" int bc_embed_##SUFFIX(const void* table, const int* tokens, float* out, int rows, int E, int V, cudaStream_t s) { \
         BC_CHECK_ARG(rows >= 0 && E > 0 && V > 0, "embed: bad sizes rows=%d E=%d V=%d", rows, E, V);                             \
         if (rows == 0) return BC_OK;                                                                                             \
-        embed_kernel<T><<<rows, pick_threads(E % 4 == 0 ? E / 4 : E, 1024), 0, s>>>((const T*)table, tokens, out, E, V);                                    \
+        bc_launch(embed_kernel<T>, dim3(rows), dim3(pick_threads(E % 4 == 0 ? E / 4 : E, 1024)), 0, s, (const T*)table, tokens, out, E, V);                                    \
         BC_LAUNCH_STATUS();                                                                                                      \
     }                                                                                                                            \
     extern "C" int bc_rmsnorm_##SUFFIX(const float* x, const float* w, void* out, const int* gather, int rows, int E, float eps, \
                                        cudaStream_t s) {                                                                         \
         BC_CHECK_ARG(rows >= 0 && E > 0 && eps > 0.0f, "rmsnorm: bad sizes rows=%d E=%d eps=%g", rows, E, (double)eps);          \
         if (rows == 0) return BC_OK;                                                                                             \
-        rmsnorm_kernel<T><<<rows, pick_threads(E % 4 == 0 ? E / 4 : E, 1024), 0, s>>>(x, w, (T*)out, gather, E, eps);                                       \
+        bc_launch(rmsnorm_kernel<T>, dim3(rows), dim3(pick_threads(E % 4 == 0 ? E / 4 : E, 1024)), 0, s, x, w, (T*)out, gather, E, eps);                                       \
         BC_LAUNCH_STATUS();                                                                                                      \
     }                                                                                                                            \
     extern "C" int bc_swiglu_##SUFFIX(const void* gu, void* out, int rows, int F, cudaStream_t s) {                              \
         BC_CHECK_ARG(rows >= 0 && F > 0, "swiglu: bad sizes rows=%d F=%d", rows, F);                                             \
         size_t total = (size_t)rows * F;                                                                                         \
         if (total == 0) return BC_OK;                                                                                            \
-        swiglu_kernel<T><<<(unsigned)((total + 255) / 256), 256, 0, s>>>((const T*)gu, (T*)out, F, total);                       \
+        bc_launch(swiglu_kernel<T>, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, s, (const T*)gu, (T*)out, F, total);                       \
         BC_LAUNCH_STATUS();                                                                                                      \
     }                                                                                                                            \
     extern "C" int bc_rope_append_##SUFFIX(void* qkv, const float* cos_sin, const int* row_pos, const int* row_slot,             \
@@ -183,8 +191,9 @@ static int pick_threads(int n, int cap = 256) {
         BC_CHECK_ARG(pairing == 0 || pairing == 1, "rope_append: pairing %d is neither 0 (half) nor 1 (adjacent)", pairing);     \
         if (rows == 0) return BC_OK;                                                                                             \
         BC_CHECK_ARG(H + 2 * G <= 65535, "rope_append: too many heads (%d)", H + 2 * G);                                          \
-        rope_append_kernel<T><<<dim3(rows, H + 2 * G), pick_threads(D / 2, 128), 0, s>>>((T*)qkv, (const float2*)cos_sin, row_pos, row_slot, page_table, (T*)k_cache,  \
-                                                   (T*)v_cache, H, G, D, pairing, max_pages, n_pages, write_cache);              \
+        bc_launch(rope_append_kernel<T>, dim3(rows, H + 2 * G), dim3(pick_threads(D / 2, 128)), 0, s, (T*)qkv,                 \
+                  (const float2*)cos_sin, row_pos, row_slot, page_table, (T*)k_cache, (T*)v_cache, H, G, D, pairing, max_pages,  \
+                  n_pages, write_cache);                                                                                         \
         BC_LAUNCH_STATUS();                                                                                                      \
     }
 

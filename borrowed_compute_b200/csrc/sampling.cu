@@ -167,6 +167,8 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(const float* __r
     __shared__ float tot[16];
     __shared__ float red[32];
     __shared__ int counts[SAMPLE_THREADS];
+    pdl_launch_dependents();
+    pdl_wait();
     const int r = blockIdx.x;
     const float* row = scores + (size_t)r * V;
     float max_score;
@@ -227,6 +229,8 @@ __device__ __forceinline__ unsigned long long argmax_key(float v, int i) {
 
 __global__ void __launch_bounds__(256) argmax_partial_kernel(const float* __restrict__ scores, int V, unsigned long long* __restrict__ best) {
     __shared__ unsigned long long part[8];
+    pdl_launch_dependents();
+    pdl_wait();
     const int r = blockIdx.y, c0 = blockIdx.x * ARGMAX_CHUNK;
     const float* row = scores + (size_t)r * V;
     unsigned long long mine = 0ull;
@@ -247,6 +251,8 @@ __global__ void __launch_bounds__(256) argmax_partial_kernel(const float* __rest
 }
 
 __global__ void argmax_finish_kernel(unsigned long long* __restrict__ best, int* __restrict__ out, int rows) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int r = blockIdx.x * blockDim.x + threadIdx.x;
     if (r >= rows) return;
     const unsigned long long k = best[r];
@@ -263,7 +269,7 @@ extern "C" int bc_sample(const float* scores, int rows, int V, const float* temp
                          const unsigned long long* seed, const int* step, int* out, cudaStream_t s) {
     BC_CHECK_ARG(rows >= 0 && V > 0, "sample: bad sizes rows=%d V=%d", rows, V);
     if (rows == 0) return BC_OK;
-    sample_kernel<<<rows, SAMPLE_THREADS, 0, s>>>(scores, V, temperature, top_p, seed, step, out);
+    bc_launch(sample_kernel, dim3(rows), dim3(SAMPLE_THREADS), 0, s, scores, V, temperature, top_p, seed, step, out);
     BC_LAUNCH_STATUS();
 }
 
@@ -280,7 +286,7 @@ extern "C" int bc_argmax(const float* scores, int rows, int V, int* out, cudaStr
         }
     }
     dim3 grid((V + ARGMAX_CHUNK - 1) / ARGMAX_CHUNK, rows);
-    argmax_partial_kernel<<<grid, 256, 0, s>>>(scores, V, best);
-    argmax_finish_kernel<<<(rows + 127) / 128, 128, 0, s>>>(best, out, rows);
+    bc_launch(argmax_partial_kernel, grid, dim3(256), 0, s, scores, V, best);
+    bc_launch(argmax_finish_kernel, dim3((rows + 127) / 128), dim3(128), 0, s, best, out, rows);
     BC_LAUNCH_STATUS();
 }

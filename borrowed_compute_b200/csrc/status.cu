@@ -13,6 +13,11 @@ void bc_set_error(const char* fmt, ...) {
     va_end(ap);
 }
 
+// Whether launches ask for programmatic dependent launch (see common.cuh).
+int g_bc_pdl = 1;
+extern "C" void bc_set_pdl(int on) { g_bc_pdl = on ? 1 : 0; }
+extern "C" int bc_get_pdl() { return g_bc_pdl; }
+
 extern "C" const char* bc_last_error() { return g_error; }
 
 // Bumped when an exported signature changes, so a stale build is never called.

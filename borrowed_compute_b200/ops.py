@@ -8,6 +8,7 @@ device, or a kernel library that cannot be loaded, raises.
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Optional
 
 import torch
@@ -36,7 +37,15 @@ def lib() -> ctypes.CDLL:
         if handle.bc_page_size() != PAGE:
             raise KernelError(f"the kernel library pages {handle.bc_page_size()} tokens, the package {PAGE}")
         _checked_page = True
+        if os.environ.get("BC_B200_PDL", "1") == "0":
+            handle.bc_set_pdl(_c_int(0))
     return handle
+
+
+def set_pdl(on: bool) -> None:
+    """Whether kernels ask for programmatic dependent launch (overlap of a kernel's set-up
+    and weight prefetch with the preceding kernel's tail).  On by default."""
+    lib().bc_set_pdl(_c_int(1 if on else 0))
 
 
 def _stream() -> _c_void_p:
@@ -273,9 +282,10 @@ def attention_decode_accepts(heads: int, kv_heads: int, head_dim: int, dtype: to
 
 
 def attention_decode_splits(rows: int, kv_heads: int, max_pages: int) -> int:
-    """Splits of the cached positions so that rows * kv_heads * splits blocks fill the
-    device about twice over; never more than a sequence can have pages."""
-    return max(1, min(-(-296 // max(1, rows * kv_heads)), max_pages, 64))
+    """Splits of the cached positions so that rows * kv_heads * splits blocks come close to,
+    and stay within, one wave of two blocks on each of 148 SMs; never more than a sequence
+    can have pages."""
+    return max(1, min(296 // max(1, rows * kv_heads), max_pages, 64))
 
 
 def _decode_workspace(device: torch.device, floats: int, ints: int):
