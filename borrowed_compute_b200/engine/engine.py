@@ -98,7 +98,8 @@ class Engine:
         self._host_ints: Optional[torch.Tensor] = None
         self._staged: Optional[torch.cuda.Event] = None
         self._graphs: Dict[int, "_DecodeGraph"] = {}
-        self.use_graphs = True   # decode steps replay a captured CUDA graph
+        # Decode steps replay a captured CUDA graph unless a part plans on the host.
+        self.use_graphs = all(part.graph_safe for _, part in model._named_parts())
         self.steps_run = 0
 
     # ------------------------------------------------------------------------ construction

@@ -209,6 +209,10 @@ class Part:
     which tensors it wants, and receives them (already on the device, already in the type
     their role asks for) in :meth:`load`."""
 
+    # False for a part whose forward plans on the host from this step's lengths (ctx.host_*):
+    # the engine then runs every step eagerly instead of replaying a captured graph.
+    graph_safe = True
+
     def __init__(self, **params: Any):
         self.params = params
 
