@@ -333,6 +333,38 @@ def attention_decode(q: torch.Tensor, q_stride: int, k_cache: torch.Tensor, v_ca
           _c_int(page_table.shape[1]), _c_int(k_cache.shape[0]), _c_int(window), _c_float(scale), _c_int(splits), _stream())
 
 
+def attention_prefill_accepts(heads: int, kv_heads: int, head_dim: int, dtype: torch.dtype) -> bool:
+    """Whether the tiled prompt kernel takes these sizes (bf16; at most 64 heads a kv head;
+    head size a multiple of 16 up to 128).  Otherwise attention_rows serves."""
+    return dtype == torch.bfloat16 and bool(_fn("bc_attention_prefill_accepts")(_c_int(heads), _c_int(kv_heads), _c_int(head_dim)))
+
+
+def attention_prefill(q: torch.Tensor, q_stride: int, k_cache: torch.Tensor, v_cache: torch.Tensor, page_table: torch.Tensor,
+                      seq_rows: torch.Tensor, seq_slot: torch.Tensor, seq_start: torch.Tensor, out: torch.Tensor, seqs: int, max_new: int,
+                      heads: int, kv_heads: int, head_dim: int, window: int = 0, scale: Optional[float] = None) -> None:
+    """Causal attention of every sequence's new rows against its cached positions (which
+    include the new rows' own keys and values), 64 query rows a block (bf16)."""
+    _need(q, "q", torch.bfloat16)
+    _need(k_cache, "k_cache", torch.bfloat16)
+    _need(v_cache, "v_cache", torch.bfloat16)
+    _need(page_table, "page_table", torch.int32)
+    _need(seq_rows, "seq_rows", torch.int32)
+    _need(seq_slot, "seq_slot", torch.int32)
+    _need(seq_start, "seq_start", torch.int32)
+    _need(out, "out", torch.bfloat16)
+    if out.shape[1] != heads * head_dim:
+        raise KernelError(f"attention: out width {out.shape[1]} is not heads * head_dim")
+    if tuple(k_cache.shape[1:]) != (kv_heads, PAGE, head_dim) or k_cache.shape != v_cache.shape:
+        raise KernelError(f"attention: cache is {tuple(k_cache.shape)}, wanted [pages, {kv_heads}, {PAGE}, {head_dim}]")
+    if seq_rows.numel() < seqs + 1 or seq_slot.numel() < seqs or seq_start.numel() < seqs:
+        raise KernelError("attention_prefill: fewer sequence entries than sequences")
+    if scale is None:
+        scale = 1.0 / float(head_dim) ** 0.5
+    _call(_fn("bc_attention_prefill_bf16"), _ptr(q), _c_int(q_stride), _ptr(k_cache), _ptr(v_cache), _ptr(page_table), _ptr(seq_rows),
+          _ptr(seq_slot), _ptr(seq_start), _ptr(out), _c_int(seqs), _c_int(max_new), _c_int(heads), _c_int(kv_heads), _c_int(head_dim),
+          _c_int(page_table.shape[1]), _c_int(k_cache.shape[0]), _c_int(window), _c_float(scale), _stream())
+
+
 # ---------------------------------------------------------------------------------- sampling
 
 def argmax(scores: torch.Tensor, out: torch.Tensor) -> None:

@@ -70,5 +70,9 @@ class GroupedQueryAttention(Mixer):
             ops.attention_decode(qkv, (H + 2 * G) * D, mem.k_pages, mem.v_pages, mem.page_table, ctx.row_pos, ctx.row_slot, out,
                                  H, G, D, window=self.window, scale=self.scale)
             return
+        if not ctx.decode and ops.attention_prefill_accepts(H, G, D, qkv.dtype):
+            ops.attention_prefill(qkv, (H + 2 * G) * D, mem.k_pages, mem.v_pages, mem.page_table, ctx.seq_rows, ctx.seq_slot,
+                                  ctx.seq_start, out, ctx.seqs, ctx.max_new, H, G, D, window=self.window, scale=self.scale)
+            return
         ops.attention_rows(qkv, (H + 2 * G) * D, mem.k_pages, mem.v_pages, mem.page_table, ctx.row_pos, ctx.row_slot, out,
                            H, G, D, window=self.window, scale=self.scale)

@@ -284,6 +284,68 @@ def test_attention_decode(H, G, D, splits, window):
     assert (out.float() - twin.float()).abs().max().item() <= 2.0 ** -6
 
 
+@pytest.mark.parametrize("H,G,D", [(6, 2, 48), (4, 4, 16), (8, 1, 32), (32, 8, 128), (8, 2, 64)])
+@pytest.mark.parametrize("window", [0, 70])
+def test_attention_prefill(H, G, D, window):
+    """The tiled bf16 prompt kernel against the float64 formula: sequences of ragged
+    lengths in one launch, some continuing from cached positions, a padding sequence, head
+    groups that do and do not divide the 64-row tile."""
+    from borrowed_compute_b200 import ops
+
+    n_pages = 24
+    cached = [0, 0, 100, 64, 0]            # positions already in the cache before this step
+    new = [1, 130, 30, 65, 300]            # rows this step brings
+    r = rng(H * 100 + D + 1)
+    free = list(r.permutation(n_pages))
+    table = np.full((len(new), 8), -1, dtype=np.int32)
+    kp = np.zeros((n_pages, G, 64, D), dtype=np.float32)
+    vp = np.zeros_like(kp)
+    ks, vs, qs_ = [], [], []
+    for s, (c, n) in enumerate(zip(cached, new)):
+        pages = [int(free.pop()) for _ in range((c + n + 63) // 64)]
+        table[s, :len(pages)] = pages
+        k, v = r.standard_normal((c + n, G, D)).astype(np.float32), r.standard_normal((c + n, G, D)).astype(np.float32)
+        ks.append(k), vs.append(v)
+        kp += paged(k, pages, G, D, n_pages, torch.bfloat16)
+        vp += paged(v, pages, G, D, n_pages, torch.bfloat16)
+        qs_.append((r.standard_normal((n, H * D)) * 1.5).astype(np.float32))
+    # sequence order in the step: 0, 1, a padding sequence, 2, 3, 4
+    order = [0, 1, -1, 2, 3, 4]
+    seq_rows, seq_slot, seq_start, rows = [0], [], [], []
+    for s in order:
+        n = 0 if s < 0 else new[s]
+        seq_rows.append(seq_rows[-1] + n)
+        seq_slot.append(s)
+        seq_start.append(0 if s < 0 else cached[s])
+        if s >= 0:
+            rows.append(qs_[s])
+    q = np.concatenate(rows)
+    total = q.shape[0]
+    out = torch.full((total, H * D), 9.0, dtype=torch.bfloat16, device="cuda")
+    ops.attention_prefill(dev(q, torch.bfloat16), H * D, dev(kp, torch.bfloat16), dev(vp, torch.bfloat16), dev(table),
+                          dev(np.array(seq_rows, dtype=np.int32)), dev(np.array(seq_slot, dtype=np.int32)),
+                          dev(np.array(seq_start, dtype=np.int32)), out, len(order), max(new), H, G, D, window=window)
+    got, qst = f64(out), stored(q, torch.bfloat16)
+    at = 0
+    for s in order:
+        if s < 0:
+            continue
+        for i in range(new[s]):
+            p = cached[s] + i
+            if i in (0, 1, new[s] // 2, new[s] - 2, new[s] - 1) or (p % 64) in (0, 63):
+                ref = attention_reference(qst[at + i].reshape(H, D), stored(ks[s][:p + 1], torch.bfloat16),
+                                          stored(vs[s][:p + 1], torch.bfloat16), window)
+                assert np.abs(got[at + i].reshape(H, D) - ref).max() <= 2.0 ** -7 * (1 + np.abs(ref).max()), f"sequence {s} row {i}"
+        at += new[s]
+    # and every row against the one-warp-a-row twin
+    row_slot = np.concatenate([np.full(new[s], s, dtype=np.int32) for s in order if s >= 0])
+    row_pos = np.concatenate([np.arange(cached[s], cached[s] + new[s], dtype=np.int32) for s in order if s >= 0])
+    twin = torch.empty_like(out)
+    ops.attention_rows(dev(q, torch.bfloat16), H * D, dev(kp, torch.bfloat16), dev(vp, torch.bfloat16), dev(table), dev(row_pos),
+                       dev(row_slot), twin, H, G, D, window=window)
+    assert (out.float() - twin.float()).abs().max().item() <= 2.0 ** -5
+
+
 def test_argmax_first_largest_wins():
     from borrowed_compute_b200 import ops
 
