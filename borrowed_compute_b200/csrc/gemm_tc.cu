@@ -372,6 +372,10 @@ static int weight_map(CUtensorMap* out, const void* base, int rows, int K) {
     return BC_OK;
 }
 
+// A tuning knob for measurements: 0 lets the launcher choose the ring depth, n > 0 caps it.
+static int g_tc_stage_cap = 0;
+extern "C" void bc_gemm_tc_set_stage_cap(int n) { g_tc_stage_cap = n < 0 ? 0 : n; }
+
 template <int BN, int EPI>
 static int launch(const CUtensorMap& mw, const CUtensorMap& mx, TcParams p, int splits, cudaStream_t s) {
     constexpr int N_ACC = EPI == EPI_SWIGLU ? 2 : 1;
@@ -381,6 +385,11 @@ static int launch(const CUtensorMap& mw, const CUtensorMap& mx, TcParams p, int 
     splits = (total_k_iters + p.k_iters_per_split - 1) / p.k_iters_per_split;
     int stages = (TC_SMEM_LIMIT - 1024) / STAGE_BYTES;
     if (stages > 12) stages = 12;
+    // Few tokens (decoding): the product streams weights and the next product's blocks should
+    // be able to sit beside this one's on an SM, prefetching their weights while these drain.
+    // Half the shared memory still keeps ~100 KB of loads in flight a block.
+    if (g_tc_stage_cap == 0 && BN <= 64 && stages * STAGE_BYTES > (TC_SMEM_LIMIT / 2 - 2048)) stages = (TC_SMEM_LIMIT / 2 - 2048) / STAGE_BYTES;
+    if (g_tc_stage_cap > 0 && stages > g_tc_stage_cap) stages = g_tc_stage_cap;
     if (stages > p.k_iters_per_split) stages = p.k_iters_per_split < 2 ? 2 : p.k_iters_per_split;
     p.stages = stages;
     const int smem = stages * STAGE_BYTES + 1024;

@@ -119,10 +119,12 @@ template <class T>
 __global__ void rope_append_kernel(T* __restrict__ qkv, const float2* __restrict__ cos_sin, const int* __restrict__ row_pos,
                                    const int* __restrict__ row_slot, const int* __restrict__ page_table, T* __restrict__ k_cache,
                                    T* __restrict__ v_cache, int H, int G, int D, int pairing, int max_pages, int n_pages, int write_cache) {
-    // One block a (row, head of the fused projection): q heads, then k heads, then v heads.
+    // threadIdx.y picks one (row, head of the fused projection) of the block's: q heads, then
+    // k heads, then v heads.  Nothing below synchronises, so threads may leave early.
     pdl_launch_dependents();
     pdl_wait();
-    const int r = blockIdx.x, h = blockIdx.y;
+    const int r = blockIdx.x, h = blockIdx.y * blockDim.y + threadIdx.y;
+    if (h >= H + 2 * G) return;
     const int slot = row_slot[r];
     if (slot < 0) return;
     const int pos = row_pos[r];
@@ -191,7 +193,9 @@ static int pick_threads(int n, int cap = 256) {
         BC_CHECK_ARG(pairing == 0 || pairing == 1, "rope_append: pairing %d is neither 0 (half) nor 1 (adjacent)", pairing);     \
         if (rows == 0) return BC_OK;                                                                                             \
         BC_CHECK_ARG(H + 2 * G <= 65535, "rope_append: too many heads (%d)", H + 2 * G);                                          \
-        bc_launch(rope_append_kernel<T>, dim3(rows, H + 2 * G), dim3(pick_threads(D / 2, 128)), 0, s, (T*)qkv,                 \
+        /* few rows (decoding): a block a head, for the shortest critical path; many rows: eight heads a block */                \
+        const int tx = pick_threads(D / 2, 128), ty = rows <= 64 ? 1 : (tx <= 64 ? 8 : 4);                                         \
+        bc_launch(rope_append_kernel<T>, dim3(rows, (H + 2 * G + ty - 1) / ty), dim3(tx, ty), 0, s, (T*)qkv,                       \
                   (const float2*)cos_sin, row_pos, row_slot, page_table, (T*)k_cache, (T*)v_cache, H, G, D, pairing, max_pages,  \
                   n_pages, write_cache);                                                                                         \
         BC_LAUNCH_STATUS();                                                                                                      \

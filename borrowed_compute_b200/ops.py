@@ -207,6 +207,12 @@ def gemm_tc_splits(T: int, N: int, K: int, epilogue: int) -> int:
     while bn < T and bn < 256:
         bn *= 2
     tiles = -(-N // 128) * -(-T // bn)
+    if tiles == 0:
+        return 1
+    if bn <= 64:
+        # Few tokens: the product streams weights, two blocks fit an SM, and measured rates keep
+        # rising up to about two blocks an SM as long as a split still has 8 k-steps of 64.
+        return max(1, min(296 // tiles, -(-K // 64) // 8, 16))
     return max(1, min(148 // tiles, -(-K // 64) // 8, 16))
 
 
