@@ -291,3 +291,104 @@ extern "C" int bc_attention_decode_bf16(const void* q, int q_stride, const void*
     bc_set_error("attention_decode: no kernel for head size %d", D);
     return BC_ERR_ARG;
 }
+
+// ------------------------------------------------- the variant that brings its own scratch
+// See attention_decode_static.h for who needs this and what it costs.  The array below is
+// part of the library's device image: in host code its name is only a stand-in, so the
+// device address is asked for once per device and handed to the kernel like any pointer.
+#include <mutex>
+
+#include "attention_decode_static.h"
+
+static __device__ __align__(256) unsigned char g_static_scratch[BC_STATIC_SCRATCH_BYTES];
+
+#define BC_STATIC_MAX_DEVICES 64
+static void* g_static_scratch_addr[BC_STATIC_MAX_DEVICES];        // per device, null until looked up
+static unsigned g_static_configured[BC_STATIC_MAX_DEVICES];       // per device, bit D / 16: that head size's kernel is set up
+static std::mutex g_static_mutex;
+
+template <int D>
+static int launch_static(float* scratch, int* counters, const void* q, int q_stride, const void* k_cache, const void* v_cache,
+                         const int* page_table, const int* row_pos, const int* row_slot, void* out, int rows, int H, int G, int max_pages,
+                         int n_pages, int window, float scale, int n_splits, int device, cudaStream_t s) {
+    constexpr int TILE_BYTES = 64 * D * 2;
+    constexpr int MERGE_BYTES = (2 * 4 * 16 + 4 * 16 * D) * 4;
+    constexpr int SMEM = AD_STAGES * 2 * TILE_BYTES > MERGE_BYTES ? AD_STAGES * 2 * TILE_BYTES : MERGE_BYTES;
+    {
+        // First call for this head size on this device: let the kernel use the shared memory it needs.
+        std::lock_guard<std::mutex> lock(g_static_mutex);
+        if (!(g_static_configured[device] & (1u << (D / 16)))) {
+            cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+            if (e != cudaSuccess) {
+                bc_set_error("attention_decode_static: cannot set shared memory to %d: %s", SMEM, cudaGetErrorString(e));
+                return (int)e;
+            }
+            g_static_configured[device] |= 1u << (D / 16);
+        }
+    }
+    bc_launch(attention_decode_kernel<D>, dim3(n_splits, G, rows), dim3(AD_THREADS), (size_t)SMEM, s, (const bf16*)q, q_stride,
+              (const bf16*)k_cache, (const bf16*)v_cache, page_table, row_pos, row_slot, (bf16*)out, scratch, counters, H, G, max_pages,
+              n_pages, window, scale * 1.4426950408889634f);
+    BC_LAUNCH_STATUS();
+}
+
+extern "C" int bc_attention_decode_static_bf16(const void* q, int q_stride, const void* k_cache, const void* v_cache, const int* page_table,
+                                               const int* row_pos, const int* row_slot, void* out, int rows, int heads, int kv_heads,
+                                               int head_dim, int max_pages, int n_pages, int window, float scale, int n_splits,
+                                               cudaStream_t stream) {
+    BC_CHECK_ARG(rows >= 0 && rows <= 65535, "attention_decode_static: %d rows (at most 65535)", rows);
+    BC_CHECK_ARG(bc_attention_decode_accepts(heads, kv_heads, head_dim), "attention_decode_static: heads=%d kv_heads=%d head_dim=%d is "
+                 "outside what the kernel takes (at most %d heads a kv head, head size a multiple of 16 up to 128)", heads, kv_heads,
+                 head_dim, AD_MAX_GROUP);
+    BC_CHECK_ARG(n_splits >= 1 && n_splits <= 65535 && kv_heads <= 65535, "attention_decode_static: bad split count %d", n_splits);
+    BC_CHECK_ARG(q_stride % 2 == 0 && ((uintptr_t)q % 4 == 0), "attention_decode_static: q must be 4-byte aligned with an even stride");
+    const long long floats = n_splits > 1 ? (long long)rows * heads * n_splits * (head_dim + 2) : 0;
+    const long long ints = n_splits > 1 ? (long long)rows * kv_heads : 0;
+    if (floats > BC_STATIC_SCRATCH_FLOATS || ints > BC_STATIC_SCRATCH_COUNTERS) {
+        bc_set_error("attention_decode_static: rows=%d heads=%d splits=%d head_dim=%d needs %lld floats and %lld counters of scratch; the "
+                     "built-in array holds %d and %d.  Use fewer splits or rows, or bc_attention_decode_bf16 with scratch of your own",
+                     rows, heads, n_splits, head_dim, floats, ints, BC_STATIC_SCRATCH_FLOATS, BC_STATIC_SCRATCH_COUNTERS);
+        return BC_ERR_LIMIT;
+    }
+    if (rows == 0) return BC_OK;
+
+    // Once per device, with that device current: the array's address on this device.
+    int device = -1;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess || device < 0 || device >= BC_STATIC_MAX_DEVICES) {
+        bc_set_error("attention_decode_static: no usable current device (%s)", cudaGetErrorString(e));
+        return e != cudaSuccess ? (int)e : BC_ERR_ARG;
+    }
+    void* base = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(g_static_mutex);
+        if (!g_static_scratch_addr[device]) {
+            void* p = nullptr;
+            e = cudaGetSymbolAddress(&p, g_static_scratch);
+            if (e != cudaSuccess || !p) {
+                bc_set_error("attention_decode_static: cannot find the scratch array on device %d: %s", device, cudaGetErrorString(e));
+                return e != cudaSuccess ? (int)e : BC_ERR_DRIVER;
+            }
+            g_static_scratch_addr[device] = p;
+        }
+        base = g_static_scratch_addr[device];
+    }
+    float* scratch = reinterpret_cast<float*>(base);
+    int* counters = reinterpret_cast<int*>(static_cast<unsigned char*>(base) + (size_t)BC_STATIC_SCRATCH_FLOATS * 4);
+    if (ints > 0) {
+        // The array keeps what the last call left; the counters of this launch start at zero.
+        e = cudaMemsetAsync(counters, 0, (size_t)ints * sizeof(int), stream);
+        if (e != cudaSuccess) {
+            bc_set_error("attention_decode_static: clearing the counters failed: %s", cudaGetErrorString(e));
+            return (int)e;
+        }
+    }
+#define ADS_CASE(DD) \
+    case DD: return launch_static<DD>(scratch, counters, q, q_stride, k_cache, v_cache, page_table, row_pos, row_slot, out, rows, heads, kv_heads, max_pages, n_pages, window, scale, n_splits, device, stream);
+    switch (head_dim) {
+        ADS_CASE(16) ADS_CASE(32) ADS_CASE(48) ADS_CASE(64) ADS_CASE(80) ADS_CASE(96) ADS_CASE(112) ADS_CASE(128)
+    }
+#undef ADS_CASE
+    bc_set_error("attention_decode_static: no kernel for head size %d", head_dim);
+    return BC_ERR_ARG;
+}
