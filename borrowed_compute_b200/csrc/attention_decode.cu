@@ -26,7 +26,8 @@ __global__ void __launch_bounds__(AD_THREADS)
 attention_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
                         const int* __restrict__ page_table, const int* __restrict__ row_pos, const int* __restrict__ row_slot,
                         bf16* __restrict__ out, float* __restrict__ scratch, int* __restrict__ counters, int H, int G, int max_pages,
-                        int n_pages, int window, float scale_log2) {
+                        int n_pages, int window, float scale_log2, const float2* __restrict__ cos_sin, int pairing, int fuse,
+                        int k_off, int v_off, bf16* __restrict__ k_write, bf16* __restrict__ v_write) {
     constexpr int CHUNKS = D / 8;              // 16-byte chunks a row
     constexpr int TILE_BYTES = 64 * D * 2;     // one page of one kv head
     constexpr int KD = D / 16;                 // k-steps of Q K^T
@@ -67,6 +68,70 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __
             qf[kd][2] = gq < group ? *reinterpret_cast<const uint32_t*>(qr + (size_t)gq * D + d0 + 8) : 0u;
             qf[kd][3] = gq + 8 < group ? *reinterpret_cast<const uint32_t*>(qr + (size_t)(gq + 8) * D + d0 + 8) : 0u;
         }
+    }
+
+    // Fused mode (fuse > 0): q arrives unrotated inside the fused projection
+    // [q heads | k heads | v heads]; it is rotated here, in registers, by the row's position.
+    // A thread's register (kd, hi) holds dimensions base, base + 1 with base = 16 kd + 8 hi +
+    // 2 tq, and the partner of dimension d (d + D/2, or d + 1) sits in the same thread, so no
+    // data moves between threads.  Same formulas and roundings as rope_append_kernel.
+    if (fuse > 0 && cos_sin != nullptr) {
+        const float2* cs = cos_sin + (size_t)pos * (D / 2);
+        if (pairing == 1) {
+#pragma unroll
+            for (int kd = 0; kd < KD; kd++)
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const int base = kd * 16 + 8 * (j >> 1) + 2 * tq;
+                    const float2 c = cs[base / 2];
+                    const __nv_bfloat162 x = *reinterpret_cast<__nv_bfloat162*>(&qf[kd][j]);
+                    const float x0 = __low2float(x), x1 = __high2float(x);
+                    qf[kd][j] = pack_bf16(__fsub_rn(__fmul_rn(x0, c.x), __fmul_rn(x1, c.y)), __fadd_rn(__fmul_rn(x0, c.y), __fmul_rn(x1, c.x)));
+                }
+        } else {
+#pragma unroll
+            for (int u = 0; u < D / 16; u++)      // units of 8 dimensions in the first half of the head
+#pragma unroll
+                for (int rs = 0; rs < 2; rs++) {
+                    const int u2 = u + D / 16;
+                    const int base = u * 8 + 2 * tq;
+                    const float4 c = *reinterpret_cast<const float4*>(cs + base);   // (cos, sin) of pairs base and base + 1
+                    uint32_t& lo_reg = qf[u >> 1][rs + 2 * (u & 1)];
+                    uint32_t& hi_reg = qf[u2 >> 1][rs + 2 * (u2 & 1)];
+                    const __nv_bfloat162 a = *reinterpret_cast<__nv_bfloat162*>(&lo_reg), b = *reinterpret_cast<__nv_bfloat162*>(&hi_reg);
+                    const float a0 = __low2float(a), a1 = __high2float(a), b0 = __low2float(b), b1 = __high2float(b);
+                    lo_reg = pack_bf16(__fsub_rn(__fmul_rn(a0, c.x), __fmul_rn(b0, c.y)), __fsub_rn(__fmul_rn(a1, c.z), __fmul_rn(b1, c.w)));
+                    hi_reg = pack_bf16(__fadd_rn(__fmul_rn(a0, c.y), __fmul_rn(b0, c.x)), __fadd_rn(__fmul_rn(a1, c.w), __fmul_rn(b1, c.z)));
+                }
+        }
+    }
+    // The block whose split holds the row's own position also appends the row's key (rotated)
+    // and value to the cache, before it starts reading pages.
+    if (fuse == 2 && n_tiles > 0 && t_end == end_tile) {
+        const int pi = pos / BC_PAGE;
+        const int page = pi < max_pages ? pages[pi] : -1;
+        if (page >= 0 && page < n_pages) {
+            const bf16* kr = q + (size_t)r * q_stride + k_off + (size_t)g * D;
+            const bf16* vr = q + (size_t)r * q_stride + v_off + (size_t)g * D;
+            bf16* kd_ = k_write + (((size_t)page * G + g) * BC_PAGE + pos % BC_PAGE) * D;
+            bf16* vd_ = v_write + (((size_t)page * G + g) * BC_PAGE + pos % BC_PAGE) * D;
+            const float2* cs = cos_sin ? cos_sin + (size_t)pos * (D / 2) : nullptr;
+            for (int i = threadIdx.x; i < D / 2; i += AD_THREADS) {
+                const int a = pairing ? 2 * i : i, b = pairing ? 2 * i + 1 : i + D / 2;
+                const float x0 = __bfloat162float(kr[a]), x1 = __bfloat162float(kr[b]);
+                float y0 = x0, y1 = x1;
+                if (cs) {
+                    const float2 c = cs[i];
+                    y0 = __fsub_rn(__fmul_rn(x0, c.x), __fmul_rn(x1, c.y));
+                    y1 = __fadd_rn(__fmul_rn(x0, c.y), __fmul_rn(x1, c.x));
+                }
+                kd_[a] = __float2bfloat16_rn(y0);
+                kd_[b] = __float2bfloat16_rn(y1);
+            }
+            for (int d = threadIdx.x; d < D; d += AD_THREADS) vd_[d] = vr[d];
+        }
+        __threadfence();
+        __syncthreads();
     }
 
     auto load_tile = [&](int tile, int stage) {
@@ -235,10 +300,17 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __
     }
 }
 
+struct FusedRope {
+    const float* cos_sin;   // null: no rotation
+    int pairing;
+    int fuse;               // 0: q is already rotated and the cache already holds the row; 1: rotate q; 2: rotate q and append k, v
+    int k_off, v_off;       // where a row's k and v heads start inside the fused projection, in elements
+};
+
 template <int D>
 static int launch(const void* q, int q_stride, const void* k_cache, const void* v_cache, const int* page_table, const int* row_pos,
                   const int* row_slot, void* out, float* scratch, int* counters, int rows, int H, int G, int max_pages, int n_pages,
-                  int window, float scale, int n_splits, cudaStream_t s) {
+                  int window, float scale, int n_splits, FusedRope fr, cudaStream_t s) {
     constexpr int TILE_BYTES = 64 * D * 2;
     constexpr int MERGE_BYTES = (2 * 4 * 16 + 4 * 16 * D) * 4;
     constexpr int SMEM = AD_STAGES * 2 * TILE_BYTES > MERGE_BYTES ? AD_STAGES * 2 * TILE_BYTES : MERGE_BYTES;
@@ -254,7 +326,8 @@ static int launch(const void* q, int q_stride, const void* k_cache, const void* 
     dim3 grid(n_splits, G, rows);
     bc_launch(attention_decode_kernel<D>, grid, dim3(AD_THREADS), (size_t)SMEM, s, (const bf16*)q, q_stride, (const bf16*)k_cache,
               (const bf16*)v_cache, page_table, row_pos, row_slot, (bf16*)out, scratch, counters, H, G, max_pages, n_pages, window,
-              scale * 1.4426950408889634f);
+              scale * 1.4426950408889634f, (const float2*)fr.cos_sin, fr.pairing, fr.fuse, fr.k_off, fr.v_off, (bf16*)k_cache,
+              (bf16*)v_cache);
     BC_LAUNCH_STATUS();
 }
 
@@ -270,6 +343,37 @@ extern "C" int bc_attention_decode_workspace(int rows, int H, int G, int D, int 
     return BC_OK;
 }
 
+// The same with rotary encoding and the cache append fused in (the reference does these as
+// k_rope and k_copy launches, crates/bc-infer/src/gpu/mod.rs:464-475): `q` is then the
+// fused projection [rows, (H + 2 G) D] as the product left it, unrotated; fuse = 1 rotates
+// q on the fly, fuse = 2 also writes the row's rotated key and its value to the cache
+// before attending; fuse = 0 is the plain kernel.  cos_sin [positions, D/2, 2] float, or
+// null for no rotation.
+extern "C" int bc_attention_decode_fused_bf16(const void* q, int q_stride, const void* k_cache, const void* v_cache, const int* page_table,
+                                              const int* row_pos, const int* row_slot, void* out, float* scratch, int* counters, int rows,
+                                              int H, int G, int D, int max_pages, int n_pages, int window, float scale, int n_splits,
+                                              const float* cos_sin, int pairing, int fuse, cudaStream_t s) {
+    BC_CHECK_ARG(rows >= 0 && rows <= 65535, "attention_decode: %d rows (at most 65535)", rows);
+    BC_CHECK_ARG(bc_attention_decode_accepts(H, G, D), "attention_decode: H=%d G=%d D=%d is outside what this kernel takes "
+                 "(at most %d heads a kv head, head size a multiple of 16 up to 128)", H, G, D, AD_MAX_GROUP);
+    BC_CHECK_ARG(n_splits >= 1 && n_splits <= 65535 && G <= 65535, "attention_decode: bad split count %d", n_splits);
+    BC_CHECK_ARG(n_splits == 1 || (scratch && counters), "attention_decode: splits need scratch memory");
+    BC_CHECK_ARG(q_stride % 2 == 0 && ((uintptr_t)q % 4 == 0), "attention_decode: q must be 4-byte aligned with an even stride");
+    BC_CHECK_ARG(fuse >= 0 && fuse <= 2 && (pairing == 0 || pairing == 1), "attention_decode: bad fuse %d or pairing %d", fuse, pairing);
+    BC_CHECK_ARG(fuse == 0 || q_stride == (H + 2 * G) * D, "attention_decode: fused mode wants the fused projection, stride %d", (H + 2 * G) * D);
+    BC_CHECK_ARG(fuse == 0 || cos_sin == nullptr || (uintptr_t)cos_sin % 16 == 0, "attention_decode: the rotary table must be 16-byte aligned");
+    if (rows == 0) return BC_OK;
+    FusedRope fr{cos_sin, pairing, fuse, H * D, (H + G) * D};
+#define AD_CASE(DD) \
+    case DD: return launch<DD>(q, q_stride, k_cache, v_cache, page_table, row_pos, row_slot, out, scratch, counters, rows, H, G, max_pages, n_pages, window, scale, n_splits, fr, s);
+    switch (D) {
+        AD_CASE(16) AD_CASE(32) AD_CASE(48) AD_CASE(64) AD_CASE(80) AD_CASE(96) AD_CASE(112) AD_CASE(128)
+    }
+#undef AD_CASE
+    bc_set_error("attention_decode: no kernel for head size %d", D);
+    return BC_ERR_ARG;
+}
+
 // q: row r's head h at q + r * q_stride + h * D.  scratch / counters: see above; counters
 // zero before the first launch (every launch leaves them zero).  Rows must be <= 65535.
 extern "C" int bc_attention_decode_bf16(const void* q, int q_stride, const void* k_cache, const void* v_cache, const int* page_table,
@@ -282,14 +386,8 @@ extern "C" int bc_attention_decode_bf16(const void* q, int q_stride, const void*
     BC_CHECK_ARG(n_splits == 1 || (scratch && counters), "attention_decode: splits need scratch memory");
     BC_CHECK_ARG(q_stride % 2 == 0 && ((uintptr_t)q % 4 == 0), "attention_decode: q must be 4-byte aligned with an even stride");
     if (rows == 0) return BC_OK;
-#define AD_CASE(DD) \
-    case DD: return launch<DD>(q, q_stride, k_cache, v_cache, page_table, row_pos, row_slot, out, scratch, counters, rows, H, G, max_pages, n_pages, window, scale, n_splits, s);
-    switch (D) {
-        AD_CASE(16) AD_CASE(32) AD_CASE(48) AD_CASE(64) AD_CASE(80) AD_CASE(96) AD_CASE(112) AD_CASE(128)
-    }
-#undef AD_CASE
-    bc_set_error("attention_decode: no kernel for head size %d", D);
-    return BC_ERR_ARG;
+    return bc_attention_decode_fused_bf16(q, q_stride, k_cache, v_cache, page_table, row_pos, row_slot, out, scratch, counters, rows, H, G,
+                                          D, max_pages, n_pages, window, scale, n_splits, nullptr, 0, 0, s);
 }
 
 // ------------------------------------------------- the variant that brings its own scratch
@@ -328,7 +426,7 @@ static int launch_static(float* scratch, int* counters, const void* q, int q_str
     }
     bc_launch(attention_decode_kernel<D>, dim3(n_splits, G, rows), dim3(AD_THREADS), (size_t)SMEM, s, (const bf16*)q, q_stride,
               (const bf16*)k_cache, (const bf16*)v_cache, page_table, row_pos, row_slot, (bf16*)out, scratch, counters, H, G, max_pages,
-              n_pages, window, scale * 1.4426950408889634f);
+              n_pages, window, scale * 1.4426950408889634f, (const float2*)nullptr, 0, 0, 0, 0, (bf16*)nullptr, (bf16*)nullptr);
     BC_LAUNCH_STATUS();
 }
 

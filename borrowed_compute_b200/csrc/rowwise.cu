@@ -149,8 +149,10 @@ __global__ void rope_append_kernel(T* __restrict__ qkv, const float2* __restrict
         float y0 = x0, y1 = x1;
         if (cs) {
             const float2 c = cs[i];
-            y0 = x0 * c.x - x1 * c.y;
-            y1 = x0 * c.y + x1 * c.x;
+            // Each product and the sum rounded on its own (no fused multiply-add): the decode
+            // attention kernel rotates with the same four roundings and must give the same bits.
+            y0 = __fsub_rn(__fmul_rn(x0, c.x), __fmul_rn(x1, c.y));
+            y1 = __fadd_rn(__fmul_rn(x0, c.y), __fmul_rn(x1, c.x));
         }
         dst[a] = from_f32<T>(y0);
         dst[b] = from_f32<T>(y1);

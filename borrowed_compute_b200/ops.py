@@ -312,9 +312,13 @@ def _decode_workspace(device: torch.device, floats: int, ints: int):
 
 def attention_decode(q: torch.Tensor, q_stride: int, k_cache: torch.Tensor, v_cache: torch.Tensor, page_table: torch.Tensor,
                      row_pos: torch.Tensor, row_slot: torch.Tensor, out: torch.Tensor, heads: int, kv_heads: int, head_dim: int,
-                     window: int = 0, scale: Optional[float] = None, splits: Optional[int] = None) -> None:
+                     window: int = 0, scale: Optional[float] = None, splits: Optional[int] = None, fuse: int = 0,
+                     cos_sin: Optional[torch.Tensor] = None, pairing: int = 0) -> None:
     """Attention of one new row a sequence (bf16): the cached positions are split across
-    blocks and the heads of a kv head share each read; results are merged in a fixed order."""
+    blocks and the heads of a kv head share each read; results are merged in a fixed order.
+    ``fuse`` 1 or 2: ``q`` is the fused projection as the product left it; q is rotated on
+    the fly by ``cos_sin`` (None: no rotation), and with 2 the row's rotated key and its
+    value are appended to the cache first (what rope_append would have done)."""
     _need(q, "q", torch.bfloat16)
     _need(k_cache, "k_cache", torch.bfloat16)
     _need(v_cache, "v_cache", torch.bfloat16)
@@ -334,9 +338,14 @@ def attention_decode(q: torch.Tensor, q_stride: int, k_cache: torch.Tensor, v_ca
     scratch = counters = None
     if splits > 1:
         scratch, counters = _decode_workspace(q.device, rows * heads * splits * (head_dim + 2), rows * kv_heads)
-    _call(_fn("bc_attention_decode_bf16"), _ptr(q), _c_int(q_stride), _ptr(k_cache), _ptr(v_cache), _ptr(page_table), _ptr(row_pos),
+    if cos_sin is not None:
+        _need(cos_sin, "cos_sin", torch.float32)
+        if tuple(cos_sin.shape[1:]) != (head_dim // 2, 2):
+            raise KernelError(f"attention_decode: cos_sin is {tuple(cos_sin.shape)}, wanted [positions, {head_dim // 2}, 2]")
+    _call(_fn("bc_attention_decode_fused_bf16"), _ptr(q), _c_int(q_stride), _ptr(k_cache), _ptr(v_cache), _ptr(page_table), _ptr(row_pos),
           _ptr(row_slot), _ptr(out), _ptr(scratch), _ptr(counters), _c_int(rows), _c_int(heads), _c_int(kv_heads), _c_int(head_dim),
-          _c_int(page_table.shape[1]), _c_int(k_cache.shape[0]), _c_int(window), _c_float(scale), _c_int(splits), _stream())
+          _c_int(page_table.shape[1]), _c_int(k_cache.shape[0]), _c_int(window), _c_float(scale), _c_int(splits), _ptr(cos_sin),
+          _c_int(pairing), _c_int(fuse), _stream())
 
 
 def attention_prefill_accepts(heads: int, kv_heads: int, head_dim: int, dtype: torch.dtype) -> bool:

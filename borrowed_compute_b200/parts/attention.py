@@ -58,18 +58,20 @@ class GroupedQueryAttention(Mixer):
         qkv = torch.empty((rows, (H + 2 * G) * D), dtype=x.dtype, device=x.device)
         products.linear(x, self.w_qkv, qkv, products.EPI_STORE)
         table = self.position.rotary()
-        ops.rope_append(qkv, None if table is None else table.cos_sin, ctx.row_pos, ctx.row_slot, mem.page_table,
-                        mem.k_pages, mem.v_pages, H, G, D, 0 if table is None else table.pairing, write_cache=mem.writes)
         att = torch.empty((rows, H * D), dtype=x.dtype, device=x.device)
-        self.attend(qkv, att, ctx, mem)
+        if ctx.decode and ops.attention_decode_accepts(H, G, D, qkv.dtype):
+            # One token a sequence: rotation and the cache append ride inside the attention kernel.
+            ops.attention_decode(qkv, (H + 2 * G) * D, mem.k_pages, mem.v_pages, mem.page_table, ctx.row_pos, ctx.row_slot, att,
+                                 H, G, D, window=self.window, scale=self.scale, fuse=2 if mem.writes else 1,
+                                 cos_sin=None if table is None else table.cos_sin, pairing=0 if table is None else table.pairing)
+        else:
+            ops.rope_append(qkv, None if table is None else table.cos_sin, ctx.row_pos, ctx.row_slot, mem.page_table,
+                            mem.k_pages, mem.v_pages, H, G, D, 0 if table is None else table.pairing, write_cache=mem.writes)
+            self.attend(qkv, att, ctx, mem)
         products.linear(att, self.w_o, residual, products.EPI_ADD_F32)
 
     def attend(self, qkv: torch.Tensor, out: torch.Tensor, ctx: StepContext, mem: RunMemory) -> None:
         H, G, D = self.heads, self.kv_heads, self.head_dim
-        if ctx.decode and ops.attention_decode_accepts(H, G, D, qkv.dtype):
-            ops.attention_decode(qkv, (H + 2 * G) * D, mem.k_pages, mem.v_pages, mem.page_table, ctx.row_pos, ctx.row_slot, out,
-                                 H, G, D, window=self.window, scale=self.scale)
-            return
         if not ctx.decode and ops.attention_prefill_accepts(H, G, D, qkv.dtype):
             ops.attention_prefill(qkv, (H + 2 * G) * D, mem.k_pages, mem.v_pages, mem.page_table, ctx.seq_rows, ctx.seq_slot,
                                   ctx.seq_start, out, ctx.seqs, ctx.max_new, H, G, D, window=self.window, scale=self.scale)

@@ -346,6 +346,49 @@ def test_attention_prefill(H, G, D, window):
     assert (out.float() - twin.float()).abs().max().item() <= 2.0 ** -5
 
 
+@pytest.mark.parametrize("H,G,D", [(6, 3, 48), (4, 4, 16), (16, 1, 32), (32, 8, 128), (8, 2, 64)])
+@pytest.mark.parametrize("pairing", [0, 1])
+def test_attention_decode_with_rotation_and_append_fused(H, G, D, pairing):
+    """fuse=2 on the raw projection must leave the same cache and give the same output,
+    to the bit, as rope_append followed by the plain decode kernel."""
+    from borrowed_compute_b200 import ops
+    from borrowed_compute_b200.parts.rope import inverse_frequencies, rotary_table
+
+    r = rng(H + D + pairing)
+    n_pages, lengths = 20, [1, 64, 65, 130, 400]
+    free = list(r.permutation(n_pages))
+    table = np.full((len(lengths), 8), -1, dtype=np.int32)
+    for s, n in enumerate(lengths):
+        for i in range(-(-n // 64)):
+            table[s, i] = int(free.pop())
+    kp = dev((r.standard_normal((n_pages, G, 64, D)) * 0.7).astype(np.float32), torch.bfloat16)
+    vp = dev((r.standard_normal((n_pages, G, 64, D)) * 0.7).astype(np.float32), torch.bfloat16)
+    rows = len(lengths) + 1
+    row_slot = dev(np.array(list(range(len(lengths))) + [-1], dtype=np.int32))
+    row_pos = dev(np.array([n - 1 for n in lengths] + [3], dtype=np.int32))
+    qkv = dev((r.standard_normal((rows, (H + 2 * G) * D)) * 1.2).astype(np.float32), torch.bfloat16)
+    cos_sin = rotary_table(inverse_frequencies(D, 10000.0, None), 512).cuda()
+    tab = dev(table)
+    # the two-kernel way
+    q1, k1, v1 = qkv.clone(), kp.clone(), vp.clone()
+    ops.rope_append(q1, cos_sin, row_pos, row_slot, tab, k1, v1, H, G, D, pairing)
+    want = torch.empty((rows, H * D), dtype=torch.bfloat16, device="cuda")
+    ops.attention_decode(q1, (H + 2 * G) * D, k1, v1, tab, row_pos, row_slot, want, H, G, D, splits=3)
+    # fused
+    q2, k2, v2 = qkv.clone(), kp.clone(), vp.clone()
+    got = torch.empty_like(want)
+    ops.attention_decode(q2, (H + 2 * G) * D, k2, v2, tab, row_pos, row_slot, got, H, G, D, splits=3, fuse=2, cos_sin=cos_sin, pairing=pairing)
+    assert torch.equal(k1, k2) and torch.equal(v1, v2), "the fused append left another cache"
+    assert torch.equal(q2, qkv), "the fused kernel must not write the projection"
+    assert torch.equal(got, want)
+    # fuse=1 rotates but leaves the cache alone (a run that reads another run's cache)
+    k3, v3 = k1.clone(), v1.clone()
+    ops.attention_decode(qkv.clone(), (H + 2 * G) * D, k3, v3, tab, row_pos, row_slot, got, H, G, D, splits=2, fuse=1, cos_sin=cos_sin, pairing=pairing)
+    assert torch.equal(k3, k1) and torch.equal(v3, v1)
+    ops.attention_decode(q1, (H + 2 * G) * D, k1, v1, tab, row_pos, row_slot, want, H, G, D, splits=2)
+    assert torch.equal(got, want)
+
+
 def test_argmax_first_largest_wins():
     from borrowed_compute_b200 import ops
 
