@@ -144,7 +144,12 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, const TcParams p) {
     constexpr int A_BYTES = TC_BM * TC_BK * 2;
     constexpr int B_BYTES = BN * TC_BK * 2;
-    constexpr int N_ACC = EPI == EPI_SWIGLU ? 2 : 1;
+    // Two accumulators share one activation tile: gate and up rows for SwiGLU, or, with the
+    // widest token tile, two stacked weight tiles (256 output rows a block), which cuts the
+    // bytes an SM must fetch per multiply-accumulate by a third.
+    constexpr bool TWO_TILES = EPI != EPI_SWIGLU && BN == 256;
+    constexpr int N_ACC = (EPI == EPI_SWIGLU || TWO_TILES) ? 2 : 1;
+    constexpr int OUT_TILES = TWO_TILES ? 2 : 1;
     constexpr int STAGE_BYTES = N_ACC * A_BYTES + B_BYTES;
     constexpr int TMEM_COLS = N_ACC * BN < 32 ? 32 : N_ACC * BN;
     extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -155,7 +160,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int stages = p.stages;
-    const int n0 = blockIdx.x * TC_BM, t0 = blockIdx.y * BN;
+    const int n0 = blockIdx.x * (OUT_TILES * TC_BM), t0 = blockIdx.y * BN;
+    const int second_row = EPI == EPI_SWIGLU ? p.up_row_offset + n0 : n0 + TC_BM;   // where the second accumulator's weight rows start
     const int total_k_iters = (p.K + TC_BK - 1) / TC_BK;
     const int k_first = blockIdx.z * p.k_iters_per_split;
     const int k_iters = min(p.k_iters_per_split, total_k_iters - k_first);
@@ -186,7 +192,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 mbar_expect_tx(full0 + 8 * i, STAGE_BYTES);
                 const int k = (k_first + i) * TC_BK;
                 tma_load_2d(a, &map_w, full0 + 8 * i, k, n0);
-                if (EPI == EPI_SWIGLU) tma_load_2d(a + A_BYTES, &map_w, full0 + 8 * i, k, p.up_row_offset + n0);
+                if (N_ACC == 2) tma_load_2d(a + A_BYTES, &map_w, full0 + 8 * i, k, second_row);
             }
             pdl_wait();
             for (int i = 0; i < ahead; i++) {
@@ -200,7 +206,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
                 const int k = (k_first + i) * TC_BK;
                 tma_load_2d(a, &map_w, full0 + 8 * s, k, n0);
-                if (EPI == EPI_SWIGLU) tma_load_2d(a + A_BYTES, &map_w, full0 + 8 * s, k, p.up_row_offset + n0);
+                if (N_ACC == 2) tma_load_2d(a + A_BYTES, &map_w, full0 + 8 * s, k, second_row);
                 tma_load_2d(a + N_ACC * A_BYTES, &map_x, full0 + 8 * s, k, t0);
             }
         }
@@ -219,7 +225,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 for (int kk = 0; kk < TC_BK / 16; kk++) {
                     const uint32_t acc = (i | kk) != 0;
                     mma_bf16(tmem, da + 2 * kk, db + 2 * kk, idesc, acc);
-                    if (EPI == EPI_SWIGLU) mma_bf16(tmem + BN, smem_desc(a + A_BYTES) + 2 * kk, db + 2 * kk, idesc, acc);
+                    if (N_ACC == 2) mma_bf16(tmem + BN, smem_desc(a + A_BYTES) + 2 * kk, db + 2 * kk, idesc, acc);
                 }
                 mma_commit(empty0 + 8 * s);
             }
@@ -228,14 +234,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     } else {
         // Epilogue: this warp reads TMEM lanes 32 q .. 32 q + 31, i.e. weight rows n0 + 32 q + lane.
         const int q = warp & 3;
-        const int n = n0 + 32 * q + lane;
+        const int n_first = n0 + 32 * q + lane;
         const bool split = gridDim.z > 1;
         const int tile = blockIdx.y * gridDim.x + blockIdx.x;
         // Split-K: every split leaves its partial tile in scratch memory; the four row
         // quarters of a tile each have a counter, and the warp that arrives last adds the
         // splits' partials in the order 0, 1, 2 .., so the sum never depends on timing.
         // Scratch layout [tile][split][column][row]: a warp touches 32 consecutive floats.
-        const size_t part_tile = (size_t)TC_BM * BN;
+        const size_t part_tile = (size_t)OUT_TILES * TC_BM * BN;   // [accumulator][column][row]
         float* part = split ? p.partial + ((size_t)tile * gridDim.z + blockIdx.z) * part_tile + 32 * q + lane : nullptr;
         int* counter = split ? p.counters + (size_t)tile * 4 + q : nullptr;
         bool ok = true;
@@ -248,7 +254,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         if (split) {
             if (ok) {
 #pragma unroll 1
-                for (int c0 = 0; c0 < BN; c0 += 16) {
+                for (int c0 = 0; c0 < OUT_TILES * BN; c0 += 16) {   // the second accumulator follows the first in TMEM and in scratch
                     uint32_t v[16];
                     tmem_load16(taddr + c0, v);
                     tmem_load_wait();
@@ -270,10 +276,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         if (finish && ok) {
             const float* all = split ? p.partial + (size_t)tile * gridDim.z * part_tile + 32 * q + lane : nullptr;
 #pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 16) {
+            for (int cc = 0; cc < OUT_TILES * BN; cc += 16) {
+                const int acc_i = cc / BN, c0 = cc - acc_i * BN;     // which accumulator (stacked weight tile), which token column
+                const int n = n_first + TC_BM * acc_i;
                 uint32_t v[16], u[16];
                 if (!split) {
-                    tmem_load16(taddr + c0, v);
+                    tmem_load16(taddr + cc, v);
                     if (EPI == EPI_SWIGLU) tmem_load16(taddr + BN + c0, u);
                     tmem_load_wait();
                 } else {
@@ -282,7 +290,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                     for (int z = 0; z < (int)gridDim.z; z++) {
 #pragma unroll
                         for (int j = 0; j < 16; j++)
-                            v[j] = __float_as_uint(__uint_as_float(v[j]) + __ldcg(all + (size_t)z * part_tile + (size_t)(c0 + j) * TC_BM));
+                            v[j] = __float_as_uint(__uint_as_float(v[j]) + __ldcg(all + (size_t)z * part_tile + (size_t)(cc + j) * TC_BM));
                     }
                 }
 #pragma unroll
@@ -293,7 +301,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                         const size_t o = (size_t)t * p.N + n;
                         if (EPI == EPI_STORE) ((bf16*)p.out)[o] = __float2bfloat16_rn(val);
                         if (EPI == EPI_STORE_F32) ((float*)p.out)[o] = val;
-                        if (EPI == EPI_ADD_F32) ((float*)p.out)[o] += val;
+                        // One thread owns each element, so a fire-and-forget reduction gives the same
+                        // sum as a load, add and store, without waiting for the load.
+                        if (EPI == EPI_ADD_F32) atomicAdd(&((float*)p.out)[o], val);
                         if (EPI == EPI_SWIGLU) ((bf16*)p.out)[o] = __float2bfloat16_rn(silu_mul(val, __uint_as_float(u[j])));
                     }
                 }
@@ -378,7 +388,8 @@ extern "C" void bc_gemm_tc_set_stage_cap(int n) { g_tc_stage_cap = n < 0 ? 0 : n
 
 template <int BN, int EPI>
 static int launch(const CUtensorMap& mw, const CUtensorMap& mx, TcParams p, int splits, cudaStream_t s) {
-    constexpr int N_ACC = EPI == EPI_SWIGLU ? 2 : 1;
+    constexpr bool TWO_TILES = EPI != EPI_SWIGLU && BN == 256;
+    constexpr int N_ACC = (EPI == EPI_SWIGLU || TWO_TILES) ? 2 : 1;
     constexpr int STAGE_BYTES = N_ACC * TC_BM * TC_BK * 2 + BN * TC_BK * 2;
     const int total_k_iters = (p.K + TC_BK - 1) / TC_BK;
     p.k_iters_per_split = (total_k_iters + splits - 1) / splits;
@@ -402,7 +413,8 @@ static int launch(const CUtensorMap& mw, const CUtensorMap& mx, TcParams p, int 
         }
         configured = true;
     }
-    dim3 grid((p.N + TC_BM - 1) / TC_BM, (p.T + BN - 1) / BN, splits);
+    constexpr int ROWS = TWO_TILES ? 2 * TC_BM : TC_BM;   // output rows a block
+    dim3 grid((p.N + ROWS - 1) / ROWS, (p.T + BN - 1) / BN, splits);
     cudaError_t e = bc_launch(gemm_tc_kernel<BN, EPI>, grid, dim3(TC_THREADS), (size_t)smem, s, mw, mx, p);
     if (e != cudaSuccess) {
         bc_set_error("gemm_tc: launch failed: %s", cudaGetErrorString(e));
@@ -424,21 +436,27 @@ static int launch_bn(int bn, const CUtensorMap& mw, const CUtensorMap& mx, const
     return BC_ERR_ARG;
 }
 
-// Token tile for T tokens: the smallest that covers them, up to 256 (128 for SwiGLU, whose
-// two accumulators would otherwise fill all of TMEM).
+// Token tile for T tokens: the smallest that covers them, up to 256.
 extern "C" int bc_gemm_tc_token_tile(int T, int epilogue) {
-    const int cap = epilogue == EPI_SWIGLU ? 128 : 256;
+    (void)epilogue;
     int bn = 16;
-    while (bn < T && bn < cap) bn <<= 1;
+    while (bn < T && bn < 256) bn <<= 1;
     return bn;
+}
+
+// Output rows one block covers: 128, or 256 with the widest token tile (two stacked weight
+// tiles; SwiGLU's two accumulators are gate and up of the same 128 outputs instead).
+extern "C" int bc_gemm_tc_rows_per_block(int T, int epilogue) {
+    return (bc_gemm_tc_token_tile(T, epilogue) == 256 && epilogue != EPI_SWIGLU) ? 2 * TC_BM : TC_BM;
 }
 
 // Floats of workspace and ints of counters a split-K launch needs.  The counters are zero
 // before the first launch and every launch leaves them zero; the floats may hold anything.
 extern "C" int bc_gemm_tc_workspace(int T, int N, int epilogue, int splits, long long* floats, long long* ints) {
     const int bn = bc_gemm_tc_token_tile(T, epilogue);
-    const long long tiles = (long long)((N + TC_BM - 1) / TC_BM) * ((T + bn - 1) / bn);
-    *floats = splits > 1 ? tiles * splits * TC_BM * bn : 0;
+    const int rows = bc_gemm_tc_rows_per_block(T, epilogue);
+    const long long tiles = (long long)((N + rows - 1) / rows) * ((T + bn - 1) / bn);
+    *floats = splits > 1 ? tiles * splits * rows * bn : 0;
     *ints = splits > 1 ? tiles * 4 : 0;
     return BC_OK;
 }

@@ -198,15 +198,21 @@ def gemm_tc_accepts(x: torch.Tensor, w: torch.Tensor) -> bool:
     return x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[-1] % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
 
 
+def _tc_tiling(T: int, N: int, epilogue: int):
+    """(token tile, output rows a block, blocks) the tensor-core product uses; mirrors the launcher."""
+    bn = 16
+    while bn < T and bn < 256:
+        bn *= 2
+    rows = 256 if (bn == 256 and epilogue != EPI_SWIGLU) else 128
+    return bn, rows, -(-N // rows) * -(-T // bn)
+
+
 def gemm_tc_splits(T: int, N: int, K: int, epilogue: int) -> int:
     """How many ways to split K so that a product with few weight tiles still fills the
     device's 148 SMs: as many as fit, each at least 8 k-steps of 64."""
     if epilogue == EPI_SWIGLU:
         return 1
-    bn = 16
-    while bn < T and bn < 256:
-        bn *= 2
-    tiles = -(-N // 128) * -(-T // bn)
+    bn, _, tiles = _tc_tiling(T, N, epilogue)
     if tiles == 0:
         return 1
     if bn <= 64:
@@ -237,11 +243,8 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int, 
     partial = counters = None
     if splits > 1:
         partial, counters = _tc_scratch(x.device)
-        bn = 16
-        while bn < M and bn < 256:
-            bn *= 2
-        tiles = -(-N // 128) * -(-M // bn)
-        if tiles * splits * 128 * bn > partial.numel() or tiles * 4 > counters.numel():
+        bn, rows, tiles = _tc_tiling(M, N, epilogue)
+        if tiles * splits * rows * bn > partial.numel() or tiles * 4 > counters.numel():
             raise KernelError(f"gemm_tc: {tiles} tiles are too many for the split-K scratch; use splits=1")
     _call(_fn("bc_gemm_tc_bf16"), _ptr(x), _ptr(w), _ptr(out), _c_int(M), _c_int(N), _c_int(K), _c_int(epilogue), _c_int(splits),
           _ptr(partial), _ptr(counters), _stream())
