@@ -126,7 +126,9 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
 // both k-major (bits 15, 16 clear), N / 8 at bit 17, M / 16 at bit 24.
 __host__ __device__ constexpr uint32_t instr_desc(int n) { return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24); }
 
-__device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.0f + expf(-g)) * u; }
+// The gate of the bf16 path: hardware exponential and division (errors of a few float ulp,
+// far below the bf16 rounding that follows).
+__device__ __forceinline__ float silu_mul(float g, float u) { return __fdividef(g, 1.0f + __expf(-g)) * u; }
 
 // ---------------------------------------------------------------------------------- kernel
 struct TcParams {
@@ -139,7 +141,7 @@ struct TcParams {
     int k_iters_per_split;
 };
 
-template <int BN, int EPI>
+template <int BN, int EPI, bool STACK>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, const TcParams p) {
     constexpr int A_BYTES = TC_BM * TC_BK * 2;
@@ -147,7 +149,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     // Two accumulators share one activation tile: gate and up rows for SwiGLU, or, with the
     // widest token tile, two stacked weight tiles (256 output rows a block), which cuts the
     // bytes an SM must fetch per multiply-accumulate by a third.
-    constexpr bool TWO_TILES = EPI != EPI_SWIGLU && BN == 256;
+    constexpr bool TWO_TILES = EPI != EPI_SWIGLU && BN == 256 && STACK;
     constexpr int N_ACC = (EPI == EPI_SWIGLU || TWO_TILES) ? 2 : 1;
     constexpr int OUT_TILES = TWO_TILES ? 2 : 1;
     constexpr int STAGE_BYTES = N_ACC * A_BYTES + B_BYTES;
@@ -386,9 +388,9 @@ static int weight_map(CUtensorMap* out, const void* base, int rows, int K) {
 static int g_tc_stage_cap = 0;
 extern "C" void bc_gemm_tc_set_stage_cap(int n) { g_tc_stage_cap = n < 0 ? 0 : n; }
 
-template <int BN, int EPI>
+template <int BN, int EPI, bool STACK>
 static int launch(const CUtensorMap& mw, const CUtensorMap& mx, TcParams p, int splits, cudaStream_t s) {
-    constexpr bool TWO_TILES = EPI != EPI_SWIGLU && BN == 256;
+    constexpr bool TWO_TILES = EPI != EPI_SWIGLU && BN == 256 && STACK;
     constexpr int N_ACC = (EPI == EPI_SWIGLU || TWO_TILES) ? 2 : 1;
     constexpr int STAGE_BYTES = N_ACC * TC_BM * TC_BK * 2 + BN * TC_BK * 2;
     const int total_k_iters = (p.K + TC_BK - 1) / TC_BK;
@@ -398,15 +400,17 @@ static int launch(const CUtensorMap& mw, const CUtensorMap& mx, TcParams p, int 
     if (stages > 12) stages = 12;
     // Few tokens (decoding): the product streams weights and the next product's blocks should
     // be able to sit beside this one's on an SM, prefetching their weights while these drain.
-    // Half the shared memory still keeps ~100 KB of loads in flight a block.
-    if (g_tc_stage_cap == 0 && BN <= 64 && stages * STAGE_BYTES > (TC_SMEM_LIMIT / 2 - 2048)) stages = (TC_SMEM_LIMIT / 2 - 2048) / STAGE_BYTES;
+    // Half the shared memory still keeps ~100 KB of loads in flight a block; where that would
+    // leave fewer than four stages (SwiGLU's double weight tile) the block takes the whole SM.
+    if (g_tc_stage_cap == 0 && BN <= 64 && (TC_SMEM_LIMIT / 2 - 2048) / STAGE_BYTES >= 4 && stages * STAGE_BYTES > (TC_SMEM_LIMIT / 2 - 2048))
+        stages = (TC_SMEM_LIMIT / 2 - 2048) / STAGE_BYTES;
     if (g_tc_stage_cap > 0 && stages > g_tc_stage_cap) stages = g_tc_stage_cap;
     if (stages > p.k_iters_per_split) stages = p.k_iters_per_split < 2 ? 2 : p.k_iters_per_split;
     p.stages = stages;
     const int smem = stages * STAGE_BYTES + 1024;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_LIMIT);
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, EPI, STACK>, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_LIMIT);
         if (e != cudaSuccess) {
             bc_set_error("gemm_tc: cannot raise the shared memory limit: %s", cudaGetErrorString(e));
             return (int)e;
@@ -415,7 +419,7 @@ static int launch(const CUtensorMap& mw, const CUtensorMap& mx, TcParams p, int 
     }
     constexpr int ROWS = TWO_TILES ? 2 * TC_BM : TC_BM;   // output rows a block
     dim3 grid((p.N + ROWS - 1) / ROWS, (p.T + BN - 1) / BN, splits);
-    cudaError_t e = bc_launch(gemm_tc_kernel<BN, EPI>, grid, dim3(TC_THREADS), (size_t)smem, s, mw, mx, p);
+    cudaError_t e = bc_launch(gemm_tc_kernel<BN, EPI, STACK>, grid, dim3(TC_THREADS), (size_t)smem, s, mw, mx, p);
     if (e != cudaSuccess) {
         bc_set_error("gemm_tc: launch failed: %s", cudaGetErrorString(e));
         return (int)e;
@@ -424,13 +428,13 @@ static int launch(const CUtensorMap& mw, const CUtensorMap& mx, TcParams p, int 
 }
 
 template <int EPI>
-static int launch_bn(int bn, const CUtensorMap& mw, const CUtensorMap& mx, const TcParams& p, int splits, cudaStream_t s) {
+static int launch_bn(int bn, bool stack, const CUtensorMap& mw, const CUtensorMap& mx, const TcParams& p, int splits, cudaStream_t s) {
     switch (bn) {
-        case 16: return launch<16, EPI>(mw, mx, p, splits, s);
-        case 32: return launch<32, EPI>(mw, mx, p, splits, s);
-        case 64: return launch<64, EPI>(mw, mx, p, splits, s);
-        case 128: return launch<128, EPI>(mw, mx, p, splits, s);
-        case 256: return launch<256, EPI>(mw, mx, p, splits, s);
+        case 16: return launch<16, EPI, false>(mw, mx, p, splits, s);
+        case 32: return launch<32, EPI, false>(mw, mx, p, splits, s);
+        case 64: return launch<64, EPI, false>(mw, mx, p, splits, s);
+        case 128: return launch<128, EPI, false>(mw, mx, p, splits, s);
+        case 256: return stack ? launch<256, EPI, true>(mw, mx, p, splits, s) : launch<256, EPI, false>(mw, mx, p, splits, s);
     }
     bc_set_error("gemm_tc: no kernel for a token tile of %d", bn);
     return BC_ERR_ARG;
@@ -444,17 +448,27 @@ extern "C" int bc_gemm_tc_token_tile(int T, int epilogue) {
     return bn;
 }
 
-// Output rows one block covers: 128, or 256 with the widest token tile (two stacked weight
-// tiles; SwiGLU's two accumulators are gate and up of the same 128 outputs instead).
-extern "C" int bc_gemm_tc_rows_per_block(int T, int epilogue) {
-    return (bc_gemm_tc_token_tile(T, epilogue) == 256 && epilogue != EPI_SWIGLU) ? 2 * TC_BM : TC_BM;
+// Output rows one block covers: 128, or 256 when, with the widest token tile, two weight
+// tiles are stacked (SwiGLU's two accumulators are gate and up of the same 128 outputs
+// instead).  Stacking cuts shared-memory traffic per multiply by a third but halves the
+// number of blocks; it is used unless that leaves the last wave of blocks much emptier.
+static int g_tc_stack = -1;   // tuning knob for measurements: -1 decide here, 0 never, 1 always
+extern "C" void bc_gemm_tc_set_stack(int mode) { g_tc_stack = mode; }
+static double wave_fill(long long blocks) { return (double)blocks / (double)(((blocks + 147) / 148) * 148); }
+extern "C" int bc_gemm_tc_rows_per_block(int T, int N, int epilogue) {
+    const int bn = bc_gemm_tc_token_tile(T, epilogue);
+    if (bn != 256 || epilogue == EPI_SWIGLU || g_tc_stack == 0) return TC_BM;
+    if (g_tc_stack == 1) return 2 * TC_BM;
+    const long long t_tiles = (T + bn - 1) / bn;
+    const long long stacked = (long long)((N + 2 * TC_BM - 1) / (2 * TC_BM)) * t_tiles, single = (long long)((N + TC_BM - 1) / TC_BM) * t_tiles;
+    return wave_fill(stacked) >= 0.9 * wave_fill(single) ? 2 * TC_BM : TC_BM;
 }
 
 // Floats of workspace and ints of counters a split-K launch needs.  The counters are zero
 // before the first launch and every launch leaves them zero; the floats may hold anything.
 extern "C" int bc_gemm_tc_workspace(int T, int N, int epilogue, int splits, long long* floats, long long* ints) {
     const int bn = bc_gemm_tc_token_tile(T, epilogue);
-    const int rows = bc_gemm_tc_rows_per_block(T, epilogue);
+    const int rows = bc_gemm_tc_rows_per_block(T, N, epilogue);
     const long long tiles = (long long)((N + rows - 1) / rows) * ((T + bn - 1) / bn);
     *floats = splits > 1 ? tiles * splits * rows * bn : 0;
     *ints = splits > 1 ? tiles * 4 : 0;
@@ -475,6 +489,7 @@ extern "C" int bc_gemm_tc_bf16(const void* X, const void* W, void* out, int T, i
     if (T == 0) return BC_OK;
     const int bn = bc_gemm_tc_token_tile(T, epilogue);
     BC_CHECK_ARG((T + bn - 1) / bn <= 65535, "gemm_tc: %d tokens are too many token tiles", T);
+    const bool stack = bc_gemm_tc_rows_per_block(T, N, epilogue) == 2 * TC_BM;
     const int w_rows = epilogue == EPI_SWIGLU ? 2 * N : N;
     CUtensorMap mw, mx;
     int st = weight_map(&mw, W, w_rows, K);
@@ -492,10 +507,10 @@ extern "C" int bc_gemm_tc_bf16(const void* X, const void* W, void* out, int T, i
     p.stages = 0;
     p.k_iters_per_split = 0;
     switch (epilogue) {
-        case EPI_STORE: return launch_bn<EPI_STORE>(bn, mw, mx, p, splits, s);
-        case EPI_STORE_F32: return launch_bn<EPI_STORE_F32>(bn, mw, mx, p, splits, s);
-        case EPI_ADD_F32: return launch_bn<EPI_ADD_F32>(bn, mw, mx, p, splits, s);
-        case EPI_SWIGLU: return launch_bn<EPI_SWIGLU>(bn, mw, mx, p, 1, s);
+        case EPI_STORE: return launch_bn<EPI_STORE>(bn, stack, mw, mx, p, splits, s);
+        case EPI_STORE_F32: return launch_bn<EPI_STORE_F32>(bn, stack, mw, mx, p, splits, s);
+        case EPI_ADD_F32: return launch_bn<EPI_ADD_F32>(bn, stack, mw, mx, p, splits, s);
+        case EPI_SWIGLU: return launch_bn<EPI_SWIGLU>(bn, false, mw, mx, p, 1, s);
     }
     return BC_ERR_ARG;
 }

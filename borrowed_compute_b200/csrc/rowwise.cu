@@ -137,25 +137,57 @@ __global__ void rope_append_kernel(T* __restrict__ qkv, const float2* __restrict
     if (h >= H + G) {
         if (!can_write) return;
         T* dst = v_cache + (((size_t)page * G + (h - H - G)) * BC_PAGE + in_page) * D;
-        for (int d = threadIdx.x; d < D; d += blockDim.x) dst[d] = head[d];
+        // D is a multiple of 16, so a head is whole 16-byte pieces in either type.
+        constexpr int PER = 16 / sizeof(T);
+        for (int d = threadIdx.x * PER; d < D; d += blockDim.x * PER)
+            *reinterpret_cast<uint4*>(dst + d) = *reinterpret_cast<const uint4*>(head + d);
         return;
     }
     const float2* cs = cos_sin ? cos_sin + (size_t)pos * half : nullptr;
     T* dst = h < H ? head : (can_write ? k_cache + (((size_t)page * G + (h - H)) * BC_PAGE + in_page) * D : nullptr);
     if (!dst) return;
-    for (int i = threadIdx.x; i < half; i += blockDim.x) {
-        const int a = pairing ? 2 * i : i, b = pairing ? 2 * i + 1 : i + half;
-        const float x0 = to_f32(head[a]), x1 = to_f32(head[b]);
-        float y0 = x0, y1 = x1;
-        if (cs) {
-            const float2 c = cs[i];
-            // Each product and the sum rounded on its own (no fused multiply-add): the decode
-            // attention kernel rotates with the same four roundings and must give the same bits.
-            y0 = __fsub_rn(__fmul_rn(x0, c.x), __fmul_rn(x1, c.y));
-            y1 = __fadd_rn(__fmul_rn(x0, c.y), __fmul_rn(x1, c.x));
+    // Four pairs a thread a turn (D/2 is a multiple of 8): both pairings then read and write
+    // whole 8- or 16-byte pieces.  Each product and sum is rounded on its own (no fused
+    // multiply-add): the decode attention kernel rotates with the same four roundings and
+    // must give the same bits.
+    for (int i = 4 * threadIdx.x; i < half; i += 4 * blockDim.x) {
+        float x0[4], x1[4], y0[4], y1[4];
+        if (pairing) {
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                x0[j] = to_f32(head[2 * (i + j)]);
+                x1[j] = to_f32(head[2 * (i + j) + 1]);
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                x0[j] = to_f32(head[i + j]);
+                x1[j] = to_f32(head[i + j + half]);
+            }
         }
-        dst[a] = from_f32<T>(y0);
-        dst[b] = from_f32<T>(y1);
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            y0[j] = x0[j];
+            y1[j] = x1[j];
+            if (cs) {
+                const float2 c = cs[i + j];
+                y0[j] = __fsub_rn(__fmul_rn(x0[j], c.x), __fmul_rn(x1[j], c.y));
+                y1[j] = __fadd_rn(__fmul_rn(x0[j], c.y), __fmul_rn(x1[j], c.x));
+            }
+        }
+        if (pairing) {
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                dst[2 * (i + j)] = from_f32<T>(y0[j]);
+                dst[2 * (i + j) + 1] = from_f32<T>(y1[j]);
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                dst[i + j] = from_f32<T>(y0[j]);
+                dst[i + j + half] = from_f32<T>(y1[j]);
+            }
+        }
     }
 }
 
@@ -196,7 +228,7 @@ static int pick_threads(int n, int cap = 256) {
         if (rows == 0) return BC_OK;                                                                                             \
         BC_CHECK_ARG(H + 2 * G <= 65535, "rope_append: too many heads (%d)", H + 2 * G);                                          \
         /* few rows (decoding): a block a head, for the shortest critical path; many rows: eight heads a block */                \
-        const int tx = pick_threads(D / 2, 128), ty = rows <= 64 ? 1 : (tx <= 64 ? 8 : 4);                                         \
+        const int tx = pick_threads(D / 8, 32), ty = rows <= 64 ? 1 : 8;                                         \
         bc_launch(rope_append_kernel<T>, dim3(rows, (H + 2 * G + ty - 1) / ty), dim3(tx, ty), 0, s, (T*)qkv,                       \
                   (const float2*)cos_sin, row_pos, row_slot, page_table, (T*)k_cache, (T*)v_cache, H, G, D, pairing, max_pages,  \
                   n_pages, write_cache);                                                                                         \

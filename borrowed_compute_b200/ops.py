@@ -181,6 +181,7 @@ def gemm_simt(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int
 
 
 _tc_workspace = {}
+TC_SCRATCH_FLOATS = 148 * 256 * 256   # split-K partial tiles: room for one 256 x 256 tile a block on every SM
 
 
 def _tc_scratch(device: torch.device):
@@ -188,7 +189,7 @@ def _tc_scratch(device: torch.device):
     float partial tiles (any contents) and int counters (zero between launches)."""
     key = device.index if device.index is not None else torch.cuda.current_device()
     if key not in _tc_workspace:
-        _tc_workspace[key] = (torch.empty(148 * 128 * 256, dtype=torch.float32, device=device),
+        _tc_workspace[key] = (torch.empty(TC_SCRATCH_FLOATS, dtype=torch.float32, device=device),
                               torch.zeros(4096, dtype=torch.int32, device=device))
     return _tc_workspace[key]
 
@@ -200,10 +201,8 @@ def gemm_tc_accepts(x: torch.Tensor, w: torch.Tensor) -> bool:
 
 def _tc_tiling(T: int, N: int, epilogue: int):
     """(token tile, output rows a block, blocks) the tensor-core product uses; mirrors the launcher."""
-    bn = 16
-    while bn < T and bn < 256:
-        bn *= 2
-    rows = 256 if (bn == 256 and epilogue != EPI_SWIGLU) else 128
+    bn = int(_fn("bc_gemm_tc_token_tile")(_c_int(T), _c_int(epilogue)))
+    rows = int(_fn("bc_gemm_tc_rows_per_block")(_c_int(T), _c_int(N), _c_int(epilogue)))
     return bn, rows, -(-N // rows) * -(-T // bn)
 
 
@@ -212,14 +211,15 @@ def gemm_tc_splits(T: int, N: int, K: int, epilogue: int) -> int:
     device's 148 SMs: as many as fit, each at least 8 k-steps of 64."""
     if epilogue == EPI_SWIGLU:
         return 1
-    bn, _, tiles = _tc_tiling(T, N, epilogue)
+    bn, rows, tiles = _tc_tiling(T, N, epilogue)
     if tiles == 0:
         return 1
+    fits = TC_SCRATCH_FLOATS // (tiles * rows * bn)      # splits whose partial tiles fit the scratch
     if bn <= 64:
         # Few tokens: the product streams weights, two blocks fit an SM, and measured rates keep
         # rising up to about two blocks an SM as long as a split still has 8 k-steps of 64.
-        return max(1, min(296 // tiles, -(-K // 64) // 8, 16))
-    return max(1, min(148 // tiles, -(-K // 64) // 8, 16))
+        return max(1, min(296 // tiles, -(-K // 64) // 8, 16, fits))
+    return max(1, min(148 // tiles, -(-K // 64) // 8, 16, fits))
 
 
 def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int, splits: Optional[int] = None) -> None:
