@@ -129,6 +129,7 @@ class EngineBackend(Backend):
         self._sampling = {}
         self._live_key = None
         self._steps = torch.zeros(self.max_batch, dtype=torch.int32, device=engine.rt.device)
+        self._host_steps = torch.zeros(self.max_batch, dtype=torch.int32).pin_memory()
 
     def _set_rows(self, indices: Sequence[int]) -> None:
         key = tuple(indices)
@@ -137,9 +138,11 @@ class EngineBackend(Backend):
             self._live_key = key
 
     def _sample(self, scores: torch.Tensor, positions: Sequence[int]) -> List[int]:
-        n = len(positions)
-        self._steps[:n].copy_(torch.tensor(positions, dtype=torch.int32))
-        return self.sampler.sample(scores, self._steps).cpu().tolist()
+        if not self.sampler.all_greedy:      # only a draw needs to know the position it is for
+            n = len(positions)
+            self._host_steps[:n] = torch.tensor(positions, dtype=torch.int32)
+            self._steps[:n].copy_(self._host_steps[:n], non_blocking=True)
+        return self.sampler.sample(scores, self._steps).tolist()
 
     def start(self, indices, prompts, samplings) -> List[int]:
         entries = []
