@@ -277,24 +277,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         }
         if (finish && ok) {
             const float* all = split ? p.partial + (size_t)tile * gridDim.z * part_tile + 32 * q + lane : nullptr;
-#pragma unroll 1
-            for (int cc = 0; cc < OUT_TILES * BN; cc += 16) {
+            // 16 token columns of one accumulator: apply the epilogue and write.
+            auto emit = [&](const uint32_t* v, const uint32_t* u, int cc) {
                 const int acc_i = cc / BN, c0 = cc - acc_i * BN;     // which accumulator (stacked weight tile), which token column
                 const int n = n_first + TC_BM * acc_i;
-                uint32_t v[16], u[16];
-                if (!split) {
-                    tmem_load16(taddr + cc, v);
-                    if (EPI == EPI_SWIGLU) tmem_load16(taddr + BN + c0, u);
-                    tmem_load_wait();
-                } else {
-#pragma unroll
-                    for (int j = 0; j < 16; j++) v[j] = 0u;
-                    for (int z = 0; z < (int)gridDim.z; z++) {
-#pragma unroll
-                        for (int j = 0; j < 16; j++)
-                            v[j] = __float_as_uint(__uint_as_float(v[j]) + __ldcg(all + (size_t)z * part_tile + (size_t)(cc + j) * TC_BM));
-                    }
-                }
 #pragma unroll
                 for (int j = 0; j < 16; j++) {
                     const int t = t0 + c0 + j;
@@ -308,6 +294,44 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                         if (EPI == EPI_ADD_F32) atomicAdd(&((float*)p.out)[o], val);
                         if (EPI == EPI_SWIGLU) ((bf16*)p.out)[o] = __float2bfloat16_rn(silu_mul(val, __uint_as_float(u[j])));
                     }
+                }
+            };
+            constexpr int TOTAL = OUT_TILES * BN;
+            if (!split) {
+                // The accumulator comes out of TMEM 16 columns at a time, the next piece on its way
+                // while this one is written, so the round trip to TMEM is paid once, not per piece.
+                uint32_t va[16], vb[16], ua[16], ub[16];
+                tmem_load16(taddr, va);
+                if (EPI == EPI_SWIGLU) tmem_load16(taddr + BN, ua);
+#pragma unroll 1
+                for (int cc = 0; cc < TOTAL; cc += 32) {
+                    tmem_load_wait();
+                    if (cc + 16 < TOTAL) {
+                        tmem_load16(taddr + cc + 16, vb);
+                        if (EPI == EPI_SWIGLU) tmem_load16(taddr + BN + cc + 16, ub);
+                    }
+                    emit(va, ua, cc);
+                    if (cc + 16 < TOTAL) {
+                        tmem_load_wait();
+                        if (cc + 32 < TOTAL) {
+                            tmem_load16(taddr + cc + 32, va);
+                            if (EPI == EPI_SWIGLU) tmem_load16(taddr + BN + cc + 32, ua);
+                        }
+                        emit(vb, ub, cc + 16);
+                    }
+                }
+            } else {
+#pragma unroll 1
+                for (int cc = 0; cc < TOTAL; cc += 16) {
+                    uint32_t v[16];
+#pragma unroll
+                    for (int j = 0; j < 16; j++) v[j] = 0u;
+                    for (int z = 0; z < (int)gridDim.z; z++) {
+#pragma unroll
+                        for (int j = 0; j < 16; j++)
+                            v[j] = __float_as_uint(__uint_as_float(v[j]) + __ldcg(all + (size_t)z * part_tile + (size_t)(cc + j) * TC_BM));
+                    }
+                    emit(v, v, cc);
                 }
             }
         }
