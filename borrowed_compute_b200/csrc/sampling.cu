@@ -13,42 +13,17 @@
 // crosses a target is found by descending four key bits a pass, 16 bucket sums a pass kept
 // in registers and added across the block in a fixed order (no atomics: the same bits every
 // run).  Two such walks give the nucleus cut and the draw; tokens of equal weight are told
-// apart by id with an ordered count.  One block a row; any vocabulary size.
+// apart by id with an ordered count.  A cluster of eight blocks shares a row (each owns a
+// span of ids and they exchange sums through distributed shared memory); any vocabulary size.
+#include <cooperative_groups.h>
+
 #include "common.cuh"
 
-#define SAMPLE_THREADS 1024
-#define SAMPLE_WARPS (SAMPLE_THREADS / 32)
+namespace cg = cooperative_groups;
 
-struct ArgBest {
-    float v;
-    int i;
-};
-
-__device__ __forceinline__ ArgBest better(ArgBest a, ArgBest b) {
-    // The earlier index wins a tie; a NaN never beats a number (sample.rs:27 compares with >).
-    if (b.i >= 0 && (a.i < 0 || b.v > a.v || (b.v == a.v && b.i < a.i))) return b;
-    return a;
-}
-
-__device__ int block_argmax(const float* __restrict__ row, int V, ArgBest* scratch, float* max_out) {
-    ArgBest best = {-INFINITY, -1};
-    for (int i = threadIdx.x; i < V; i += blockDim.x) {
-        const float v = row[i];
-        if (best.i < 0 || v > best.v) best = {v, i};
-    }
-    for (int o = 16; o > 0; o >>= 1) {
-        ArgBest other = {__shfl_xor_sync(0xffffffffu, best.v, o), __shfl_xor_sync(0xffffffffu, best.i, o)};
-        best = better(best, other);
-    }
-    __syncthreads();
-    if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = best;
-    __syncthreads();
-    ArgBest b = scratch[0];
-    const int warps = (blockDim.x + 31) >> 5;
-    for (int w = 1; w < warps; w++) b = better(b, scratch[w]);
-    if (max_out) *max_out = b.v;
-    return b.i < 0 ? 0 : b.i;
-}
+#define SMP_THREADS 512
+#define SMP_WARPS (SMP_THREADS / 32)
+#define SMP_CLUSTER 8      // blocks that share a row (the portable cluster size)
 
 // splitmix64's finaliser; the top 24 bits over 2^24 (sample.rs:64-71).
 __device__ __forceinline__ float uniform_from(uint64_t seed) {
@@ -59,50 +34,81 @@ __device__ __forceinline__ float uniform_from(uint64_t seed) {
     return (float)(z >> 40) / 16777216.0f;
 }
 
+__device__ __forceinline__ unsigned long long argmax_key(float v, int i) {
+    unsigned u = __float_as_uint(v);
+    u = (u & 0x80000000u) ? ~u : (u | 0x80000000u);     // larger float -> larger unsigned
+    if (v != v) u = 0u;                                  // a NaN never wins (sample.rs:27 compares with >)
+    return ((unsigned long long)u << 32) | (unsigned long long)(0xffffffffu - (unsigned)i);
+}
+__device__ __forceinline__ float argmax_key_value(unsigned long long k) {
+    unsigned u = (unsigned)(k >> 32);
+    u = (u & 0x80000000u) ? (u & 0x7fffffffu) : ~u;
+    return __uint_as_float(u);
+}
+
+// What one block of a row's cluster leaves for its peers to read through distributed
+// shared memory.  Each slot is written once, or alternates between two copies, so that one
+// cluster barrier a step is enough.
+struct SampleShared {
+    unsigned long long best;     // this block's best (score, index) word
+    float sum;                   // this block's sum of weights
+    float tot[2][16];            // this block's bucket sums of the current descent level (two copies in turn)
+    int count[2];                // this block's number of tokens with the cut key / the hit key
+    float all[16];               // bucket sums over the whole row (local copy)
+    int warp_counts[SMP_WARPS];
+};
+
 struct Walk {
     unsigned key;   // float bits of the weight at which the running sum reaches the target
     float above;    // sum of all weights with larger bits
 };
 
-// Where, going down the weights in descending order, the running sum first reaches
-// `target`.  If rounding keeps the sum below the target to the end, the smallest weight
-// that occurs stands.
-__device__ Walk walk_down(const float* __restrict__ row, int V, float max_score, float inv_t, float target, float (*part)[16], float* tot) {
+// A row is spread over the blocks of a cluster: block c owns ids [c * chunk, (c + 1) * chunk).
+struct RowView {
+    const float* row;
+    int lo, hi;          // this block's ids
+    float max_score, inv_t;
+    __device__ __forceinline__ float weight(int i) const { return expf((row[i] - max_score) * inv_t); }
+};
+
+// Where, going down the weights of the whole row in descending order, the running sum first
+// reaches `target` (if rounding keeps it below to the end, the smallest weight stands).
+// Four key bits a level: every thread sums the weights of its elements into 16 buckets of
+// its own in shared memory, a warp a bucket adds the threads' sums in a fixed order, and
+// the blocks' sums are added in rank order, so every block takes the same decision and
+// the result is the same bits on every run.
+__device__ Walk walk_down(cg::cluster_group& cl, SampleShared& sh, float* hist, const RowView& rv, float target, int& turn) {
     unsigned prefix = 0, mask = 0;
     float above = 0.0f;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     for (int shift = 28; shift >= 0; shift -= 4) {
-        float b[16];
 #pragma unroll
-        for (int j = 0; j < 16; j++) b[j] = 0.0f;
-        for (int i = threadIdx.x; i < V; i += blockDim.x) {
-            const float w = expf((row[i] - max_score) * inv_t);
+        for (int j = 0; j < 16; j++) hist[j * SMP_THREADS + threadIdx.x] = 0.0f;
+        for (int i = rv.lo + threadIdx.x; i < rv.hi; i += SMP_THREADS) {
+            const float w = rv.weight(i);
             const unsigned key = __float_as_uint(w);
-            if ((key & mask) == prefix) {
-                const unsigned d = (key >> shift) & 15u;
-#pragma unroll
-                for (int j = 0; j < 16; j++) b[j] += d == (unsigned)j ? w : 0.0f;
-            }
-        }
-#pragma unroll
-        for (int j = 0; j < 16; j++) b[j] = warp_sum(b[j]);
-        __syncthreads();
-        if (lane == 0) {
-#pragma unroll
-            for (int j = 0; j < 16; j++) part[warp][j] = b[j];
+            if ((key & mask) == prefix) hist[((key >> shift) & 15u) * SMP_THREADS + threadIdx.x] += w;
         }
         __syncthreads();
+        {   // warp j adds bucket j over the threads
+            float s = 0.0f;
+            for (int k = 0; k < SMP_THREADS / 32; k++) s += hist[warp * SMP_THREADS + lane + 32 * k];
+            s = warp_sum(s);
+            if (lane == 0) sh.tot[turn][warp] = s;
+        }
+        cl.sync();
         if (threadIdx.x < 16) {
             float s = 0.0f;
-            for (int w = 0; w < SAMPLE_WARPS; w++) s += part[w][threadIdx.x];
-            tot[threadIdx.x] = s;
+            for (unsigned r = 0; r < cl.num_blocks(); r++) s += cl.map_shared_rank(&sh, r)->tot[turn][threadIdx.x];
+            sh.all[threadIdx.x] = s;
         }
+        turn ^= 1;
         __syncthreads();
         float running = above;
         int chosen = -1, lowest = -1;
         float above_lowest = above;
         for (int j = 15; j >= 0; j--) {
-            const float t = tot[j];
+            const float t = sh.all[j];
             if (t > 0.0f) {
                 if (chosen < 0 && running + t >= target) chosen = j;
                 lowest = j;
@@ -117,101 +123,138 @@ __device__ Walk walk_down(const float* __restrict__ row, int V, float max_score,
         above = running;
         prefix |= (unsigned)chosen << shift;
         mask |= 15u << shift;
+        __syncthreads();   // sh.all is rewritten at the next level
     }
     return {prefix, above};
 }
 
-// The id of the n-th (1-based, clamped to what exists) token whose weight has bits `key`,
-// counting by ascending id, and how many such tokens there are.
-__device__ int nth_with_key(const float* __restrict__ row, int V, float max_score, float inv_t, unsigned key, int n, int* counts, int* total_out) {
-    const int chunk = (V + blockDim.x - 1) / blockDim.x;
-    const int lo = min(V, (int)threadIdx.x * chunk), hi = min(V, lo + chunk);
-    int mine = 0;
-    for (int i = lo; i < hi; i++) mine += __float_as_uint(expf((row[i] - max_score) * inv_t)) == key;
-    __syncthreads();
-    counts[threadIdx.x] = mine;
-    __syncthreads();
-    // Threads own ascending id ranges, so a serial prefix over their counts is the order.
-    __shared__ int found, total;
-    if (threadIdx.x == 0) {
-        int sum = 0;
-        for (int t = 0; t < (int)blockDim.x; t++) sum += counts[t];
-        total = sum;
-        int want = max(1, min(n, sum)), before = 0, owner = 0;
-        for (int t = 0; t < (int)blockDim.x; t++) {
-            if (before + counts[t] >= want) { owner = t; break; }
-            before += counts[t];
-        }
-        counts[0] = owner;
-        counts[1] = want - before;
-        found = -1;
+// Counts, by ascending id, the tokens whose weight has bits `key`.  Returns the row's total;
+// `before` gets how many of them have smaller ids than this thread's own span of ids
+// [t_lo, t_hi), `mine` how many lie inside it.
+__device__ int count_with_key(cg::cluster_group& cl, SampleShared& sh, const RowView& rv, unsigned key, int which, int& before, int& mine,
+                              int& t_lo, int& t_hi) {
+    const int span = (rv.hi - rv.lo + SMP_THREADS - 1) / SMP_THREADS;
+    t_lo = min(rv.hi, rv.lo + (int)threadIdx.x * span);
+    t_hi = min(rv.hi, t_lo + span);
+    mine = 0;
+    for (int i = t_lo; i < t_hi; i++) mine += __float_as_uint(rv.weight(i)) == key;
+    // exclusive prefix over the block's threads (ascending ids)
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    int incl = mine;
+    for (int o = 1; o < 32; o <<= 1) {
+        const int v = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += v;
     }
+    if (lane == 31) sh.warp_counts[warp] = incl;
     __syncthreads();
-    const int owner = counts[0], rank = counts[1];
-    if ((int)threadIdx.x == owner) {
-        int seen = 0;
-        for (int i = lo; i < hi; i++) {
-            if (__float_as_uint(expf((row[i] - max_score) * inv_t)) == key && ++seen == rank) { found = i; break; }
-        }
+    int warp_before = 0, block_total = 0;
+    for (int w = 0; w < SMP_WARPS; w++) {
+        if (w < warp) warp_before += sh.warp_counts[w];
+        block_total += sh.warp_counts[w];
     }
-    __syncthreads();
-    if (total_out) *total_out = total;
-    return found;
+    if (threadIdx.x == 0) sh.count[which] = block_total;
+    cl.sync();
+    int blocks_before = 0, total = 0;
+    for (unsigned r = 0; r < cl.num_blocks(); r++) {
+        const int c = cl.map_shared_rank(&sh, r)->count[which];
+        if (r < cl.block_rank()) blocks_before += c;
+        total += c;
+    }
+    before = blocks_before + warp_before + incl - mine;
+    return total;
 }
 
-__global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(const float* __restrict__ scores, int V, const float* __restrict__ temperature,
-                                                                const float* __restrict__ top_p, const unsigned long long* __restrict__ seed,
-                                                                const int* __restrict__ step, int* __restrict__ out) {
-    __shared__ ArgBest best_scratch[SAMPLE_WARPS];
-    __shared__ float part[SAMPLE_WARPS][16];
-    __shared__ float tot[16];
+__global__ void __launch_bounds__(SMP_THREADS) sample_kernel(const float* __restrict__ scores, int V, const float* __restrict__ temperature,
+                                                             const float* __restrict__ top_p, const unsigned long long* __restrict__ seed,
+                                                             const int* __restrict__ step, int* __restrict__ out) {
+    extern __shared__ float hist[];          // [16][SMP_THREADS]: every thread's own bucket sums
+    __shared__ SampleShared sh;
+    __shared__ unsigned long long warp_best[SMP_WARPS];
     __shared__ float red[32];
-    __shared__ int counts[SAMPLE_THREADS];
+    cg::cluster_group cl = cg::this_cluster();
     pdl_launch_dependents();
     pdl_wait();
-    const int r = blockIdx.x;
-    const float* row = scores + (size_t)r * V;
-    float max_score;
-    const int top = block_argmax(row, V, best_scratch, &max_score);
+    const int r = blockIdx.y;
+    const int chunk = (V + (int)cl.num_blocks() - 1) / (int)cl.num_blocks();
+    RowView rv;
+    rv.row = scores + (size_t)r * V;
+    rv.lo = min(V, (int)cl.block_rank() * chunk);
+    rv.hi = min(V, rv.lo + chunk);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+
+    // The largest score and its first index, over the cluster.
+    unsigned long long best = 0ull;
+    for (int i = rv.lo + threadIdx.x; i < rv.hi; i += SMP_THREADS) {
+        const unsigned long long k = argmax_key(rv.row[i], i);
+        best = k > best ? k : best;
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+        const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o);
+        best = other > best ? other : best;
+    }
+    if (lane == 0) warp_best[warp] = best;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < SMP_WARPS; w++) best = warp_best[w] > best ? warp_best[w] : best;
+        sh.best = best;
+    }
+    cl.sync();
+    best = 0ull;
+    for (unsigned b = 0; b < cl.num_blocks(); b++) {
+        const unsigned long long k = cl.map_shared_rank(&sh, b)->best;
+        best = k > best ? k : best;
+    }
+    const int top = best == 0ull ? 0 : (int)(0xffffffffu - (unsigned)(best & 0xffffffffull));
     const float temp = temperature[r];
-    if (!(temp > 0.0f)) {
-        if (threadIdx.x == 0) out[r] = top;
+    if (cl.block_rank() == 0 && threadIdx.x == 0) out[r] = top;   // stands unless a draw below replaces it
+    if (!(temp > 0.0f)) {                                          // greedy: every block of the cluster leaves here,
+        cl.sync();                                                 // but none while a peer still reads its shared memory
         return;
     }
-    const float inv_t = 1.0f / temp;
+    rv.max_score = argmax_key_value(best);
+    rv.inv_t = 1.0f / temp;
+
     float mine = 0.0f;
-    for (int i = threadIdx.x; i < V; i += blockDim.x) mine += expf((row[i] - max_score) * inv_t);
-    const float total = block_sum(mine, red);
+    for (int i = rv.lo + threadIdx.x; i < rv.hi; i += SMP_THREADS) mine += rv.weight(i);
+    mine = block_sum(mine, red);
+    if (threadIdx.x == 0) sh.sum = mine;
+    cl.sync();
+    float total = 0.0f;
+    for (unsigned b = 0; b < cl.num_blocks(); b++) total += cl.map_shared_rank(&sh, b)->sum;
 
     // The nucleus: everything heavier than the weight at the cut, and of the tokens of
     // exactly that weight the first `n_cut` by id.
+    int turn = 0;
     const float want = top_p[r] * total;
-    const Walk cut = walk_down(row, V, max_score, inv_t, want, part, tot);
+    const Walk cut = walk_down(cl, sh, hist, rv, want, turn);
     const float w_cut = __uint_as_float(cut.key);
-    int ties_cut;
-    nth_with_key(row, V, max_score, inv_t, cut.key, 1, counts, &ties_cut);
+    int before, inside, t_lo, t_hi;
+    const int ties_cut = count_with_key(cl, sh, rv, cut.key, 0, before, inside, t_lo, t_hi);
     int n_cut = w_cut > 0.0f ? (int)ceilf((want - cut.above) / w_cut) : ties_cut;
     n_cut = max(1, min(n_cut, ties_cut));
     const float kept = cut.above + (float)n_cut * w_cut;
 
     const uint64_t st = (uint64_t)(long long)step[r];
     const float rr = uniform_from(seed[r] ^ (st * 0x9e3779b97f4a7c15ull)) * kept;
-    const Walk hit = walk_down(row, V, max_score, inv_t, rr, part, tot);
+    const Walk hit = walk_down(cl, sh, hist, rv, rr, turn);
     const float w_hit = __uint_as_float(hit.key);
     int n_hit = w_hit > 0.0f ? (int)ceilf((rr - hit.above) / w_hit) : 1;
     n_hit = max(1, n_hit);
-    int pick;
-    if (hit.key < cut.key) {
-        pick = top;   // the walk ran past the kept tokens: sample.rs:61 falls back to the first
-    } else {
-        if (hit.key == cut.key && n_hit > n_cut) {
-            pick = top;
-        } else {
-            pick = nth_with_key(row, V, max_score, inv_t, hit.key, n_hit, counts, nullptr);
-            if (pick < 0) pick = top;
+    // If the walk ran past the kept tokens the first of the list stands (sample.rs:61): `top`, already written.
+    const bool past = hit.key < cut.key || (hit.key == cut.key && n_hit > n_cut);
+    const int ties_hit = count_with_key(cl, sh, rv, hit.key, 1, before, inside, t_lo, t_hi);
+    if (!past) {
+        const int wanted = max(1, min(n_hit, ties_hit));            // the wanted-th token of that weight, by ascending id
+        if (before < wanted && wanted <= before + inside) {         // it lies in this thread's span: exactly one thread of the cluster
+            int seen = before;
+            for (int i = t_lo; i < t_hi; i++)
+                if (__float_as_uint(rv.weight(i)) == hit.key && ++seen == wanted) {
+                    out[r] = i;
+                    break;
+                }
         }
     }
-    if (threadIdx.x == 0) out[r] = pick;
+    cl.sync();   // no block may leave while a peer still reads its shared memory
 }
 
 // Greedy picks for a batch in two short launches: blocks scan chunks of a row and fold
@@ -219,13 +262,6 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(const float* __r
 // inverted index in the low half, so the largest word is the largest score and, among
 // equals, the smallest index); a second launch unpacks the words and clears them.
 #define ARGMAX_CHUNK 4096
-
-__device__ __forceinline__ unsigned long long argmax_key(float v, int i) {
-    unsigned u = __float_as_uint(v);
-    u = (u & 0x80000000u) ? ~u : (u | 0x80000000u);     // larger float -> larger unsigned
-    if (v != v) u = 0u;                                  // a NaN never wins
-    return ((unsigned long long)u << 32) | (unsigned long long)(0xffffffffu - (unsigned)i);
-}
 
 __global__ void __launch_bounds__(256) argmax_partial_kernel(const float* __restrict__ scores, int V, unsigned long long* __restrict__ best) {
     __shared__ unsigned long long part[8];
@@ -269,7 +305,27 @@ extern "C" int bc_sample(const float* scores, int rows, int V, const float* temp
                          const unsigned long long* seed, const int* step, int* out, cudaStream_t s) {
     BC_CHECK_ARG(rows >= 0 && V > 0, "sample: bad sizes rows=%d V=%d", rows, V);
     if (rows == 0) return BC_OK;
-    bc_launch(sample_kernel, dim3(rows), dim3(SAMPLE_THREADS), 0, s, scores, V, temperature, top_p, seed, step, out);
+    BC_CHECK_ARG(rows <= 65535, "sample: %d rows are more than 65535", rows);
+    const size_t smem = 16 * SMP_THREADS * sizeof(float);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(SMP_CLUSTER, rows);
+    cfg.blockDim = dim3(SMP_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = SMP_CLUSTER;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_bc_pdl ? 2 : 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, sample_kernel, scores, V, temperature, top_p, seed, step, out);
+    if (e != cudaSuccess) {
+        bc_set_error("sample: launch failed: %s", cudaGetErrorString(e));
+        return (int)e;
+    }
     BC_LAUNCH_STATUS();
 }
 

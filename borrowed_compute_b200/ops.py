@@ -39,6 +39,8 @@ def lib() -> ctypes.CDLL:
         _checked_page = True
         if os.environ.get("BC_B200_PDL", "1") == "0":
             handle.bc_set_pdl(_c_int(0))
+        if os.environ.get("BC_B200_TC_STAGES"):        # measurement knob: cap the GEMM's TMA ring depth
+            handle.bc_gemm_tc_set_stage_cap(_c_int(int(os.environ["BC_B200_TC_STAGES"])))
     return handle
 
 
