@@ -243,7 +243,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         // quarters of a tile each have a counter, and the warp that arrives last adds the
         // splits' partials in the order 0, 1, 2 .., so the sum never depends on timing.
         // Scratch layout [tile][split][column][row]: a warp touches 32 consecutive floats.
-        const size_t part_tile = (size_t)OUT_TILES * TC_BM * BN;   // [accumulator][column][row]
+        const size_t part_tile = (size_t)N_ACC * TC_BM * BN;   // [accumulator][column][row]
         float* part = split ? p.partial + ((size_t)tile * gridDim.z + blockIdx.z) * part_tile + 32 * q + lane : nullptr;
         int* counter = split ? p.counters + (size_t)tile * 4 + q : nullptr;
         bool ok = true;
@@ -256,7 +256,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         if (split) {
             if (ok) {
 #pragma unroll 1
-                for (int c0 = 0; c0 < OUT_TILES * BN; c0 += 16) {   // the second accumulator follows the first in TMEM and in scratch
+                for (int c0 = 0; c0 < N_ACC * BN; c0 += 16) {   // the second accumulator follows the first in TMEM and in scratch
                     uint32_t v[16];
                     tmem_load16(taddr + c0, v);
                     tmem_load_wait();
@@ -323,15 +323,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             } else {
 #pragma unroll 1
                 for (int cc = 0; cc < TOTAL; cc += 16) {
-                    uint32_t v[16];
+                    uint32_t v[16], u[16];
 #pragma unroll
-                    for (int j = 0; j < 16; j++) v[j] = 0u;
+                    for (int j = 0; j < 16; j++) v[j] = u[j] = 0u;
                     for (int z = 0; z < (int)gridDim.z; z++) {
 #pragma unroll
-                        for (int j = 0; j < 16; j++)
+                        for (int j = 0; j < 16; j++) {
                             v[j] = __float_as_uint(__uint_as_float(v[j]) + __ldcg(all + (size_t)z * part_tile + (size_t)(cc + j) * TC_BM));
+                            if (EPI == EPI_SWIGLU)   // the up half follows the gate half; the gate is applied to the full sums
+                                u[j] = __float_as_uint(__uint_as_float(u[j]) + __ldcg(all + (size_t)z * part_tile + (size_t)(BN + cc + j) * TC_BM));
+                        }
                     }
-                    emit(v, v, cc);
+                    emit(v, u, cc);
                 }
             }
         }
@@ -425,9 +428,9 @@ static int launch(const CUtensorMap& mw, const CUtensorMap& mx, TcParams p, int 
     // Few tokens (decoding): the product streams weights and the next product's blocks should
     // be able to sit beside this one's on an SM, prefetching their weights while these drain.
     // Half the shared memory still keeps ~100 KB of loads in flight a block; where that would
-    // leave fewer than four stages (SwiGLU's double weight tile) the block takes the whole SM.
-    if (g_tc_stage_cap == 0 && BN <= 64 && (TC_SMEM_LIMIT / 2 - 2048) / STAGE_BYTES >= 4 && stages * STAGE_BYTES > (TC_SMEM_LIMIT / 2 - 2048))
-        stages = (TC_SMEM_LIMIT / 2 - 2048) / STAGE_BYTES;
+    // leave fewer than four stages (SwiGLU's double weight tile, unsplit) the block takes the whole SM.
+    const int half_stages = (TC_SMEM_LIMIT / 2 - 2048) / STAGE_BYTES;
+    if (g_tc_stage_cap == 0 && BN <= 64 && (half_stages >= 4 || (splits > 1 && half_stages >= 3)) && stages > half_stages) stages = half_stages;
     if (g_tc_stage_cap > 0 && stages > g_tc_stage_cap) stages = g_tc_stage_cap;
     if (stages > p.k_iters_per_split) stages = p.k_iters_per_split < 2 ? 2 : p.k_iters_per_split;
     p.stages = stages;
@@ -494,7 +497,7 @@ extern "C" int bc_gemm_tc_workspace(int T, int N, int epilogue, int splits, long
     const int bn = bc_gemm_tc_token_tile(T, epilogue);
     const int rows = bc_gemm_tc_rows_per_block(T, N, epilogue);
     const long long tiles = (long long)((N + rows - 1) / rows) * ((T + bn - 1) / bn);
-    *floats = splits > 1 ? tiles * splits * rows * bn : 0;
+    *floats = splits > 1 ? tiles * splits * (epilogue == EPI_SWIGLU ? 2 : 1) * rows * bn : 0;
     *ints = splits > 1 ? tiles * 4 : 0;
     return BC_OK;
 }
@@ -509,7 +512,6 @@ extern "C" int bc_gemm_tc_bf16(const void* X, const void* W, void* out, int T, i
     BC_CHECK_ARG(((uintptr_t)X % 16 == 0) && ((uintptr_t)W % 16 == 0), "gemm_tc: operands must be 16-byte aligned");
     BC_CHECK_ARG(epilogue >= 0 && epilogue <= 3, "gemm_tc: unknown epilogue %d", epilogue);
     BC_CHECK_ARG(splits >= 1 && (splits == 1 || (partial && counters)), "gemm_tc: split-K needs a workspace");
-    BC_CHECK_ARG(splits == 1 || epilogue != EPI_SWIGLU, "gemm_tc: SwiGLU cannot be split along K");
     if (T == 0) return BC_OK;
     const int bn = bc_gemm_tc_token_tile(T, epilogue);
     BC_CHECK_ARG((T + bn - 1) / bn <= 65535, "gemm_tc: %d tokens are too many token tiles", T);
@@ -534,7 +536,7 @@ extern "C" int bc_gemm_tc_bf16(const void* X, const void* W, void* out, int T, i
         case EPI_STORE: return launch_bn<EPI_STORE>(bn, stack, mw, mx, p, splits, s);
         case EPI_STORE_F32: return launch_bn<EPI_STORE_F32>(bn, stack, mw, mx, p, splits, s);
         case EPI_ADD_F32: return launch_bn<EPI_ADD_F32>(bn, stack, mw, mx, p, splits, s);
-        case EPI_SWIGLU: return launch_bn<EPI_SWIGLU>(bn, false, mw, mx, p, 1, s);
+        case EPI_SWIGLU: return launch_bn<EPI_SWIGLU>(bn, false, mw, mx, p, splits, s);
     }
     return BC_ERR_ARG;
 }

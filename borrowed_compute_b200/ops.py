@@ -211,12 +211,15 @@ def _tc_tiling(T: int, N: int, epilogue: int):
 def gemm_tc_splits(T: int, N: int, K: int, epilogue: int) -> int:
     """How many ways to split K so that a product with few weight tiles still fills the
     device's 148 SMs: as many as fit, each at least 8 k-steps of 64."""
-    if epilogue == EPI_SWIGLU:
-        return 1
     bn, rows, tiles = _tc_tiling(T, N, epilogue)
     if tiles == 0:
         return 1
-    fits = TC_SCRATCH_FLOATS // (tiles * rows * bn)      # splits whose partial tiles fit the scratch
+    accs = 2 if epilogue == EPI_SWIGLU else 1              # SwiGLU keeps gate and up sums apart until the last split
+    fits = TC_SCRATCH_FLOATS // (tiles * accs * rows * bn)   # splits whose partial tiles fit the scratch
+    if epilogue == EPI_SWIGLU:
+        # The kernel can split SwiGLU (the gate is applied to the full sums), but measured on the
+        # 8B shapes two half-depth blocks an SM stream slower than one full-depth block: unsplit.
+        return 1
     if bn <= 64:
         # Few tokens: the product streams weights, two blocks fit an SM, and measured rates keep
         # rising up to about two blocks an SM as long as a split still has 8 k-steps of 64.
@@ -246,7 +249,8 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int, 
     if splits > 1:
         partial, counters = _tc_scratch(x.device)
         bn, rows, tiles = _tc_tiling(M, N, epilogue)
-        if tiles * splits * rows * bn > partial.numel() or tiles * 4 > counters.numel():
+        accs = 2 if epilogue == EPI_SWIGLU else 1
+        if tiles * splits * accs * rows * bn > partial.numel() or tiles * 4 > counters.numel():
             raise KernelError(f"gemm_tc: {tiles} tiles are too many for the split-K scratch; use splits=1")
     _call(_fn("bc_gemm_tc_bf16"), _ptr(x), _ptr(w), _ptr(out), _c_int(M), _c_int(N), _c_int(K), _c_int(epilogue), _c_int(splits),
           _ptr(partial), _ptr(counters), _stream())

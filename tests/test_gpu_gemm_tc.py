@@ -54,8 +54,11 @@ def test_gemm_tc_all_epilogues(T, N, K, splits):
     assert np.abs(f64(acc) - (f64(base) + full[:, :N])).max() <= 2e-5 * scale, "residual add"
     g, u = full[:, :N], full[:, N:]
     ref = g / (1 + np.exp(-g)) * u
-    ops.gemm_tc(x, w, out16, ops.EPI_SWIGLU)
+    ops.gemm_tc(x, w, out16, ops.EPI_SWIGLU, splits=splits)
     assert np.abs(f64(out16) - ref).max() <= 2.0 ** -8 * (1 + np.abs(ref).max()), "SwiGLU"
+    unsplit = torch.empty_like(out16)
+    ops.gemm_tc(x, w, unsplit, ops.EPI_SWIGLU, splits=1)
+    assert np.abs(f64(unsplit) - ref).max() <= 2.0 ** -8 * (1 + np.abs(ref).max()), "SwiGLU, one split"
     assert ops.gemm_tc_status() == 0
 
 
