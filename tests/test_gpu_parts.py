@@ -174,6 +174,66 @@ def test_attention_part_alone(dtype):
         assert np.abs(np.concatenate(got[i]) - ref).max() <= tol(dtype, ref) * 2
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_windowed_attention_keeps_only_its_window(dtype):
+    """A mixer that reads only the last 70 positions gets a storage group of its own whose
+    pages behind the window go back to the pool; what it computes is attention over exactly
+    those positions, through a prompt, across page edges, and long after pages were dropped."""
+    from borrowed_compute_b200 import StepEntry
+    from borrowed_compute_b200.cache import PagedCache
+    from borrowed_compute_b200.parts import MIXERS
+
+    r = np.random.default_rng(5)
+    H, G, D, E, window, n = 4, 2, 16, 32, 70, 330
+    position = {"kind": "rotary", "head_dim": D, "theta": 10000.0, "pairing": "half", "max_positions": 512}
+    full = MIXERS.get("gqa_attention")(hidden_size=E, heads=H, kv_heads=G, head_dim=D, position=position)
+    windowed = MIXERS.get("gqa_attention")(hidden_size=E, heads=H, kv_heads=G, head_dim=D, position=position, window=window)
+    w = {k: (r.standard_normal(s.shape) * 0.4).astype(np.float32) for k, s in full.tensors().items()}
+    rt = runtime(dtype)
+    for m in (full, windowed):
+        m.load({k: dev(v, dtype) for k, v in w.items()}, rt)
+    cache = PagedCache(rt, [full.cache_need(), windowed.cache_need()], [None, None], [None, None], max_tokens=512, n_slots=2, max_seq=512)
+    assert len(cache.groups) == 2, "different needs, different storage"
+    ws = {k: f64(dev(v, dtype)) for k, v in w.items()}
+    inv = plain_llama.rope_inv_freq(D, 10000.0, None)
+    x = r.standard_normal((n, E)).astype(np.float32)
+    xs = f64(dev(x, dtype))
+    q = plain_llama.rope((xs @ ws["q_proj.weight"].T).reshape(n, H, D), range(n), inv, "half")
+    k = plain_llama.rope((xs @ ws["k_proj.weight"].T).reshape(n, G, D), range(n), inv, "half")
+    v = (xs @ ws["v_proj.weight"].T).reshape(n, G, D)
+    ref = np.zeros((n, H * D))
+    for i in range(n):                                      # row i sees positions max(0, i - window + 1) .. i
+        lo = max(0, i - window + 1)
+        for h in range(H):
+            g = h // (H // G)
+            sc = k[lo:i + 1, g] @ q[i, h] / np.sqrt(D)
+            pr = np.exp(sc - sc.max())
+            ref[i, h * D:(h + 1) * D] = (pr / pr.sum()) @ v[lo:i + 1, g]
+    ref = ref @ ws["o_proj.weight"].T
+    slot = cache.acquire()
+    got = []
+    # a prompt of 150 rows, then one row a step
+    for rows in [list(range(150))] + [[i] for i in range(150, n)]:
+        entry = StepEntry(slot, [0] * len(rows))
+        start = cache.slots.length(slot)
+        cache.slots.reserve(slot, start + len(rows), rows=len(rows))
+        cache.sync_tables()
+        ctx = context([entry], [start])
+        residual = torch.zeros((len(rows), E), dtype=torch.float32, device="cuda")
+        windowed.forward(dev(x[rows], dtype), residual, ctx, cache.memory(1))
+        scratch = torch.zeros_like(residual)
+        full.forward(dev(x[rows], dtype), scratch, ctx, cache.memory(0))
+        cache.slots.commit(slot, start + len(rows))
+        got.append(f64(residual))
+    got = np.concatenate(got)
+    assert np.abs(got - ref).max() <= tol(dtype, ref) * 2
+    held_full = sum(p >= 0 for p in cache.slots.tables[0][slot])
+    held_win = sum(p >= 0 for p in cache.slots.tables[1][slot])
+    assert held_full == 6 and held_win == 2, "the windowed group gave the pages behind its window back"
+    cache.release(slot)
+    cache.slots.check()
+
+
 # --------------------------------------------------------------------------- the toy model
 
 def register_toy():
