@@ -9,14 +9,15 @@
 // all of those heads; four warps take 16 rows each.  Per page: S = Q K^T on m16n8k16
 // tensor-core tiles, scores masked to the positions each row may see (0 .. its own, or the
 // last `window`), softmax statistics in float, P rounded to bf16, O += P V in float.
-// Pages stream through shared memory by cp.async, two ahead.  Rows are found through
+// Pages stream through shared memory by cp.async, one ahead (two stages, so that three
+// blocks fit an SM).  Rows are found through
 // per-sequence row ranges and start positions, so sequences of any lengths, with or
 // without earlier cached positions, share one launch.
 #include "common.cuh"
 #include "mma_tiles.cuh"
 
 #define AP_THREADS 128
-#define AP_STAGES 3
+#define AP_STAGES 2
 #define AP_ROWS 64
 
 template <int D>

@@ -83,6 +83,18 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
                  "l"(map), "r"(bar), "r"(x), "r"(y)
                  : "memory");
 }
+// The same with an L2 policy: weights are read once a step and should leave the L2 first,
+// so that activations, partial sums and the cache pages of the step stay.
+__device__ __forceinline__ uint64_t l2_evict_first_policy() {
+    uint64_t policy;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
+    return policy;
+}
+__device__ __forceinline__ void tma_load_2d_hint(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y, uint64_t policy) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%3, %4}], [%2], %5;" ::"r"(dst),
+                 "l"(map), "r"(bar), "r"(x), "r"(y), "l"(policy)
+                 : "memory");
+}
 __device__ __forceinline__ void tmem_alloc(uint32_t slot, uint32_t cols) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot), "r"(cols) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -189,12 +201,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             // Weights are written by no kernel, so the first ring of weight tiles is asked
             // for before the wait on the preceding kernel; activations only after it.
             const int ahead = min(stages, k_iters);
+            const uint64_t stream_once = l2_evict_first_policy();
+            auto load_w = [&](uint32_t dst, uint32_t bar, int k, int row) {
+                if (BN <= 64) tma_load_2d_hint(dst, &map_w, bar, k, row, stream_once);   // few tokens: every weight is used once
+                else tma_load_2d(dst, &map_w, bar, k, row);                              // many: token tiles share it through the L2
+            };
             for (int i = 0; i < ahead; i++) {
                 const uint32_t a = smem_u32(smem + (size_t)i * STAGE_BYTES);
                 mbar_expect_tx(full0 + 8 * i, STAGE_BYTES);
                 const int k = (k_first + i) * TC_BK;
-                tma_load_2d(a, &map_w, full0 + 8 * i, k, n0);
-                if (N_ACC == 2) tma_load_2d(a + A_BYTES, &map_w, full0 + 8 * i, k, second_row);
+                load_w(a, full0 + 8 * i, k, n0);
+                if (N_ACC == 2) load_w(a + A_BYTES, full0 + 8 * i, k, second_row);
             }
             pdl_wait();
             for (int i = 0; i < ahead; i++) {
@@ -207,8 +224,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 const uint32_t a = smem_u32(smem + (size_t)s * STAGE_BYTES);
                 mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
                 const int k = (k_first + i) * TC_BK;
-                tma_load_2d(a, &map_w, full0 + 8 * s, k, n0);
-                if (N_ACC == 2) tma_load_2d(a + A_BYTES, &map_w, full0 + 8 * s, k, second_row);
+                load_w(a, full0 + 8 * s, k, n0);
+                if (N_ACC == 2) load_w(a + A_BYTES, full0 + 8 * s, k, second_row);
                 tma_load_2d(a + N_ACC * A_BYTES, &map_x, full0 + 8 * s, k, t0);
             }
         }
