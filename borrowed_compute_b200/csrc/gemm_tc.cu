@@ -25,122 +25,10 @@
 //
 // Every wait is bounded: after about a second without progress a thread records where it
 // gave up in a status word, stops waiting, and the block frees its TMEM and returns.
-#include <cuda.h>
-
 #include <mutex>
 #include <unordered_map>
 
-#include "common.cuh"
-
-enum { EPI_STORE = 0, EPI_STORE_F32 = 1, EPI_ADD_F32 = 2, EPI_SWIGLU = 3 };
-
-#define TC_BM 128          // weight rows a tile (MMA M)
-#define TC_BK 64           // k a stage: 64 bf16 = one 128-byte swizzle row
-#define TC_THREADS 192     // warp 0 TMA, warp 1 MMA, warps 2-5 epilogue
-#define TC_SMEM_LIMIT 230400   // dynamic bytes asked for at most; static barriers take a little more
-#define TC_WAIT_CYCLES 2000000000ll
-
-// Status word: 0 while all is well, else (code << 16 | detail) of the first wait that gave up.
-__device__ int g_tc_status = 0;
-
-// ------------------------------------------------------------------------------ PTX pieces
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n"
-        ".reg .pred p;\n"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-        "selp.u32 %0, 1, 0, p;\n"
-        "}\n"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-// Waits for a phase of a barrier, at most about a second.  False (and a recorded status)
-// if it gave up; the caller then stops doing work but still reaches the teardown.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int code) {
-    if (mbar_try_wait(bar, parity)) return true;
-    const long long start = clock64();
-    while (!mbar_try_wait(bar, parity)) {
-        if (clock64() - start > TC_WAIT_CYCLES) {
-            atomicCAS(&g_tc_status, 0, (code << 16) | (int)(blockIdx.x & 0xffff));
-            return false;
-        }
-    }
-    return true;
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
-                 "l"(map), "r"(bar), "r"(x), "r"(y)
-                 : "memory");
-}
-// The same with an L2 policy: weights are read once a step and should leave the L2 first,
-// so that activations, partial sums and the cache pages of the step stay.
-__device__ __forceinline__ uint64_t l2_evict_first_policy() {
-    uint64_t policy;
-    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
-    return policy;
-}
-__device__ __forceinline__ void tma_load_2d_hint(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y, uint64_t policy) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%3, %4}], [%2], %5;" ::"r"(dst),
-                 "l"(map), "r"(bar), "r"(x), "r"(y), "l"(policy)
-                 : "memory");
-}
-__device__ __forceinline__ void tmem_alloc(uint32_t slot, uint32_t cols) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot), "r"(cols) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
-}
-__device__ __forceinline__ void mma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n"
-        ".reg .pred p;\n"
-        "setp.ne.b32 p, %4, 0;\n"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
-        "}\n" ::"r"(d_tmem),
-        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-__device__ __forceinline__ void mma_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tmem_load16(uint32_t taddr, uint32_t* v) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]),
-          "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
-        : "r"(taddr)
-        : "memory");
-}
-__device__ __forceinline__ void tmem_load_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-// Shared-memory operand descriptor: k-major tile of 128-byte rows, 128-byte swizzle, as TMA
-// writes it.  Bits 0-13 address/16; 16-29 leading offset/16 (unused for swizzled k-major,
-// 1); 32-45 stride between 8-row groups/16 (1024 bytes); 46-47 version 1; 61-63 layout 2
-// (SWIZZLE_128B).  Stepping 16 k (32 bytes) inside the swizzle row adds 2 to the address.
-__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
-    return (uint64_t)((addr >> 4) & 0x3fff) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
-}
-// Instruction descriptor of kind::f16: float accumulate (bit 4), A and B bf16 (bits 7, 10),
-// both k-major (bits 15, 16 clear), N / 8 at bit 17, M / 16 at bit 24.
-__host__ __device__ constexpr uint32_t instr_desc(int n) { return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24); }
-
-// The gate of the bf16 path: hardware exponential and division (errors of a few float ulp,
-// far below the bf16 rounding that follows).
-__device__ __forceinline__ float silu_mul(float g, float u) { return __fdividef(g, 1.0f + __expf(-g)) * u; }
+#include "tc_ptx.cuh"
 
 // ---------------------------------------------------------------------------------- kernel
 struct TcParams {
