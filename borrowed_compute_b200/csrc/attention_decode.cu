@@ -193,15 +193,15 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __
         tmax1 = fmaxf(tmax1, __shfl_xor_sync(0xffffffffu, tmax1, 1));
         tmax1 = fmaxf(tmax1, __shfl_xor_sync(0xffffffffu, tmax1, 2));
         const float mn0 = fmaxf(m0, tmax0), mn1 = fmaxf(m1, tmax1);
-        const float c0 = mn0 == -INFINITY ? 1.0f : exp2f(m0 - mn0), c1 = mn1 == -INFINITY ? 1.0f : exp2f(m1 - mn1);
+        const float c0 = mn0 == -INFINITY ? 1.0f : fast_exp2(m0 - mn0), c1 = mn1 == -INFINITY ? 1.0f : fast_exp2(m1 - mn1);
         const float base0 = mn0 == -INFINITY ? 0.0f : mn0, base1 = mn1 == -INFINITY ? 0.0f : mn1;
         float p[2][4];
 #pragma unroll
         for (int nb = 0; nb < 2; nb++) {
-            p[nb][0] = exp2f(s[nb][0] - base0);
-            p[nb][1] = exp2f(s[nb][1] - base0);
-            p[nb][2] = exp2f(s[nb][2] - base1);
-            p[nb][3] = exp2f(s[nb][3] - base1);
+            p[nb][0] = fast_exp2(s[nb][0] - base0);
+            p[nb][1] = fast_exp2(s[nb][1] - base0);
+            p[nb][2] = fast_exp2(s[nb][2] - base1);
+            p[nb][3] = fast_exp2(s[nb][3] - base1);
         }
         l0 = l0 * c0 + (p[0][0] + p[0][1] + p[1][0] + p[1][1]);
         l1 = l1 * c1 + (p[0][2] + p[0][3] + p[1][2] + p[1][3]);

@@ -127,23 +127,36 @@ attention_prefill_kernel(const bf16* __restrict__ q, int q_stride, const bf16* _
             }
         }
         float tmax[2] = {-INFINITY, -INFINITY};
+        // A page that ends at or before the position of this warp's first row is seen whole by
+        // all sixteen rows (padding rows' results are never written): no mask to work out.
+        const bool whole = window == 0 && page_ok && tile * BC_PAGE + BC_PAGE - 1 <= start + tok0 + (16 * warp) / group;
+        if (whole) {
 #pragma unroll
-        for (int nb = 0; nb < 8; nb++)
+            for (int nb = 0; nb < 8; nb++)
 #pragma unroll
-            for (int e = 0; e < 4; e++) {
-                const int i = e >> 1;
-                const int t = tile * BC_PAGE + nb * 8 + 2 * tq + (e & 1);
-                const bool seen = page_ok && live[i] && t >= lo[i] && t <= pos[i];
-                s[nb][e] = seen ? s[nb][e] * scale_log2 : -INFINITY;
-                tmax[i] = fmaxf(tmax[i], s[nb][e]);
-            }
+                for (int e = 0; e < 4; e++) {
+                    s[nb][e] *= scale_log2;
+                    tmax[e >> 1] = fmaxf(tmax[e >> 1], s[nb][e]);
+                }
+        } else {
+#pragma unroll
+            for (int nb = 0; nb < 8; nb++)
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const int i = e >> 1;
+                    const int t = tile * BC_PAGE + nb * 8 + 2 * tq + (e & 1);
+                    const bool seen = page_ok && live[i] && t >= lo[i] && t <= pos[i];
+                    s[nb][e] = seen ? s[nb][e] * scale_log2 : -INFINITY;
+                    tmax[i] = fmaxf(tmax[i], s[nb][e]);
+                }
+        }
         float corr[2], base[2];
 #pragma unroll
         for (int i = 0; i < 2; i++) {
             tmax[i] = fmaxf(tmax[i], __shfl_xor_sync(0xffffffffu, tmax[i], 1));
             tmax[i] = fmaxf(tmax[i], __shfl_xor_sync(0xffffffffu, tmax[i], 2));
             const float mn = fmaxf(m[i], tmax[i]);
-            corr[i] = mn == -INFINITY ? 1.0f : exp2f(m[i] - mn);
+            corr[i] = mn == -INFINITY ? 1.0f : fast_exp2(m[i] - mn);
             base[i] = mn == -INFINITY ? 0.0f : mn;
             m[i] = mn;
         }
@@ -152,7 +165,7 @@ attention_prefill_kernel(const bf16* __restrict__ q, int q_stride, const bf16* _
         for (int nb = 0; nb < 8; nb++)
 #pragma unroll
             for (int e = 0; e < 4; e++) {
-                s[nb][e] = exp2f(s[nb][e] - base[e >> 1]);
+                s[nb][e] = fast_exp2(s[nb][e] - base[e >> 1]);
                 psum[e >> 1] += s[nb][e];
             }
         l[0] = l[0] * corr[0] + psum[0];

@@ -89,6 +89,38 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
     for (int c = threadIdx.x; c < E; c += blockDim.x) o[c] = from_f32<T>(xr[c] * scale * w[c]);
 }
 
+// The same for many rows (prompts): 256 threads a row, each keeping its share of the row in
+// registers, so that the row is read once.  Takes E a multiple of 4 up to 8192.
+template <class T>
+__global__ void __launch_bounds__(256) rmsnorm_wide_kernel(const float* __restrict__ x, const float* __restrict__ w, T* __restrict__ out,
+                                                           const int* __restrict__ gather, int E, float eps) {
+    __shared__ float scratch[32];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int i = blockIdx.x;
+    const int r = gather ? gather[i] : i;
+    const float* xr = x + (size_t)r * E;
+    T* o = out + (size_t)i * E;
+    float4 v[8];
+    float s = 0.0f;
+#pragma unroll
+    for (int k = 0; k < 8; k++) {
+        const int c = 4 * (threadIdx.x + 256 * k);
+        v[k] = c < E ? *reinterpret_cast<const float4*>(xr + c) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        s += v[k].x * v[k].x + v[k].y * v[k].y + v[k].z * v[k].z + v[k].w * v[k].w;
+    }
+    s = block_sum(s, scratch);
+    const float scale = 1.0f / sqrtf(s / (float)E + eps);
+#pragma unroll
+    for (int k = 0; k < 8; k++) {
+        const int c = 4 * (threadIdx.x + 256 * k);
+        if (c < E) {
+            const float4 g = *reinterpret_cast<const float4*>(w + c);
+            store4<T>(o + c, v[k].x * scale * g.x, v[k].y * scale * g.y, v[k].z * scale * g.z, v[k].w * scale * g.w);
+        }
+    }
+}
+
 // --------------------------------------------------------------------------------- SwiGLU
 // out[r, j] = silu(gu[r, j]) * gu[r, F + j], silu(g) = g / (1 + e^-g) (model.rs:343;
 // kernels.h:330).  The stand-alone form; the serving GEMM fuses it into its epilogue.
@@ -104,6 +136,11 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int
     float u = to_f32(gu[r * 2 * F + F + j]);
     out[i] = from_f32<T>(g / (1.0f + expf(-g)) * u);
 }
+
+// Four or eight consecutive elements moved as one aligned piece (heads are multiples of 16
+// elements and pairs are taken four at a time, so the alignment holds).
+template <class T> struct __align__(4 * sizeof(T)) Wide4 { T v[4]; };
+template <class T> struct __align__(8 * sizeof(T)) Wide8 { T v[8]; };
 
 // ----------------------------------------------------------------- rotary + cache append
 // For every row r of the fused projection qkv[r] = [q heads | k heads | v heads]:
@@ -152,17 +189,21 @@ __global__ void rope_append_kernel(T* __restrict__ qkv, const float2* __restrict
     // must give the same bits.
     for (int i = 4 * threadIdx.x; i < half; i += 4 * blockDim.x) {
         float x0[4], x1[4], y0[4], y1[4];
+        T in[8], res[8];   // the 8 values of 4 pairs: one wide read or two, by pairing
         if (pairing) {
+            *reinterpret_cast<Wide8<T>*>(in) = *reinterpret_cast<const Wide8<T>*>(head + 2 * i);
 #pragma unroll
             for (int j = 0; j < 4; j++) {
-                x0[j] = to_f32(head[2 * (i + j)]);
-                x1[j] = to_f32(head[2 * (i + j) + 1]);
+                x0[j] = to_f32(in[2 * j]);
+                x1[j] = to_f32(in[2 * j + 1]);
             }
         } else {
+            *reinterpret_cast<Wide4<T>*>(in) = *reinterpret_cast<const Wide4<T>*>(head + i);
+            *reinterpret_cast<Wide4<T>*>(in + 4) = *reinterpret_cast<const Wide4<T>*>(head + i + half);
 #pragma unroll
             for (int j = 0; j < 4; j++) {
-                x0[j] = to_f32(head[i + j]);
-                x1[j] = to_f32(head[i + j + half]);
+                x0[j] = to_f32(in[j]);
+                x1[j] = to_f32(in[4 + j]);
             }
         }
 #pragma unroll
@@ -178,15 +219,18 @@ __global__ void rope_append_kernel(T* __restrict__ qkv, const float2* __restrict
         if (pairing) {
 #pragma unroll
             for (int j = 0; j < 4; j++) {
-                dst[2 * (i + j)] = from_f32<T>(y0[j]);
-                dst[2 * (i + j) + 1] = from_f32<T>(y1[j]);
+                res[2 * j] = from_f32<T>(y0[j]);
+                res[2 * j + 1] = from_f32<T>(y1[j]);
             }
+            *reinterpret_cast<Wide8<T>*>(dst + 2 * i) = *reinterpret_cast<const Wide8<T>*>(res);
         } else {
 #pragma unroll
             for (int j = 0; j < 4; j++) {
-                dst[i + j] = from_f32<T>(y0[j]);
-                dst[i + j + half] = from_f32<T>(y1[j]);
+                res[j] = from_f32<T>(y0[j]);
+                res[4 + j] = from_f32<T>(y1[j]);
             }
+            *reinterpret_cast<Wide4<T>*>(dst + i) = *reinterpret_cast<const Wide4<T>*>(res);
+            *reinterpret_cast<Wide4<T>*>(dst + i + half) = *reinterpret_cast<const Wide4<T>*>(res + 4);
         }
     }
 }
@@ -209,7 +253,13 @@ static int pick_threads(int n, int cap = 256) {
                                        cudaStream_t s) {                                                                         \
         BC_CHECK_ARG(rows >= 0 && E > 0 && eps > 0.0f, "rmsnorm: bad sizes rows=%d E=%d eps=%g", rows, E, (double)eps);          \
         if (rows == 0) return BC_OK;                                                                                             \
-        bc_launch(rmsnorm_kernel<T>, dim3(rows), dim3(pick_threads(E % 4 == 0 ? E / 4 : E, 1024)), 0, s, x, w, (T*)out, gather, E, eps);                                       \
+        /* The two kernels add a row's squares in different orders.  The 32-bit path promises the same bits for a row */      \
+        /* however it is batched, so it keeps one kernel; serving takes the single-pass one for prompts.                */      \
+        if (sizeof(T) == 2 && rows > 64 && E % 4 == 0 && E <= 8192)                                                             \
+            bc_launch(rmsnorm_wide_kernel<T>, dim3(rows), dim3(256), 0, s, x, w, (T*)out, gather, E, eps);                       \
+        else                                                                                                                     \
+            bc_launch(rmsnorm_kernel<T>, dim3(rows), dim3(pick_threads(E % 4 == 0 ? E / 4 : E, 1024)), 0, s, x, w, (T*)out,      \
+                      gather, E, eps);                                                                                           \
         BC_LAUNCH_STATUS();                                                                                                      \
     }                                                                                                                            \
     extern "C" int bc_swiglu_##SUFFIX(const void* gu, void* out, int rows, int F, cudaStream_t s) {                              \
