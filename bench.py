@@ -197,7 +197,7 @@ def run_ours(args) -> dict:
     eng.step([StepEntry(s, [1, 2, 3], want=())])
     before = ops.launches
     eng.step([StepEntry(s, (5,), want=(0,))])
-    launches_per_step = ops.launches - before + 1   # + the sampling kernel
+    launches_per_step = ops.launches - before + 2   # + the two kernels of greedy sampling
     eng.release(s)
     eng.use_graphs = True
 

@@ -56,6 +56,31 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __
     const int n_tiles = max(0, t_end - t_begin);
     const int* pages = page_table + (size_t)slot * max_pages;
 
+    auto load_tile = [&](int tile, int stage) {
+        int page = tile < max_pages ? pages[tile] : -1;
+        if (page < 0 || page >= n_pages) page = 0;   // never read: every position of such a tile is masked below
+        const bf16* ks = k_cache + ((size_t)page * G + g) * BC_PAGE * D;
+        const bf16* vs = v_cache + ((size_t)page * G + g) * BC_PAGE * D;
+        const uint32_t kb = ad_smem(smem + (size_t)stage * 2 * TILE_BYTES), vb = kb + TILE_BYTES;
+        for (int i = threadIdx.x; i < 64 * CHUNKS; i += AD_THREADS) {
+            const int row = i / CHUNKS, c = i - row * CHUNKS;
+            cp_async16(kb + tile_offset<D>(row, c), ks + (size_t)row * D + c * 8);
+            cp_async16(vb + tile_offset<D>(row, c), vs + (size_t)row * D + c * 8);
+        }
+    };
+
+    // The first pages are asked for at once, before the query is fetched and rotated; only the
+    // block that appends this row's key and value must write them before it reads their page.
+    const bool appends = fuse == 2 && n_tiles > 0 && t_end == end_tile;
+    auto prefetch_first = [&]() {
+#pragma unroll
+        for (int s = 0; s < AD_STAGES - 1; s++) {
+            if (s < n_tiles) load_tile(t_begin + s, s);
+            cp_async_commit();
+        }
+    };
+    if (!appends) prefetch_first();
+
     // Q fragments: row i of the tile is head g * group + i (zero past the group).
     uint32_t qf[KD][4];
     {
@@ -107,7 +132,7 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __
     }
     // The block whose split holds the row's own position also appends the row's key (rotated)
     // and value to the cache, before it starts reading pages.
-    if (fuse == 2 && n_tiles > 0 && t_end == end_tile) {
+    if (appends) {
         const int pi = pos / BC_PAGE;
         const int page = pi < max_pages ? pages[pi] : -1;
         if (page >= 0 && page < n_pages) {
@@ -132,31 +157,14 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __
         }
         __threadfence();
         __syncthreads();
+        prefetch_first();
     }
-
-    auto load_tile = [&](int tile, int stage) {
-        int page = tile < max_pages ? pages[tile] : -1;
-        if (page < 0 || page >= n_pages) page = 0;   // never read: every position of such a tile is masked below
-        const bf16* ks = k_cache + ((size_t)page * G + g) * BC_PAGE * D;
-        const bf16* vs = v_cache + ((size_t)page * G + g) * BC_PAGE * D;
-        const uint32_t kb = ad_smem(smem + (size_t)stage * 2 * TILE_BYTES), vb = kb + TILE_BYTES;
-        for (int i = threadIdx.x; i < 64 * CHUNKS; i += AD_THREADS) {
-            const int row = i / CHUNKS, c = i - row * CHUNKS;
-            cp_async16(kb + tile_offset<D>(row, c), ks + (size_t)row * D + c * 8);
-            cp_async16(vb + tile_offset<D>(row, c), vs + (size_t)row * D + c * 8);
-        }
-    };
 
     float o[ND][4];
 #pragma unroll
     for (int i = 0; i < ND; i++) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.0f, l1 = 0.0f;   // rows gq and gq + 8
 
-#pragma unroll
-    for (int s = 0; s < AD_STAGES - 1; s++) {
-        if (s < n_tiles) load_tile(t_begin + s, s);
-        cp_async_commit();
-    }
     for (int it = 0; it < n_tiles; it++) {
         cp_async_wait<AD_STAGES - 2>();
         __syncthreads();
