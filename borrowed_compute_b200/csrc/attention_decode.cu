@@ -14,8 +14,12 @@
 // so the result is the same bits whatever the scheduling.  The launch does not depend on
 // the sequence lengths (they are read on the device), so one captured graph serves every
 // step of a batch.
+#include <cooperative_groups.h>
+
 #include "common.cuh"
 #include "mma_tiles.cuh"
+
+namespace cg = cooperative_groups;
 
 #define AD_THREADS 128
 #define AD_STAGES 3
@@ -27,7 +31,7 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __
                         const int* __restrict__ page_table, const int* __restrict__ row_pos, const int* __restrict__ row_slot,
                         bf16* __restrict__ out, float* __restrict__ scratch, int* __restrict__ counters, int H, int G, int max_pages,
                         int n_pages, int window, float scale_log2, const float2* __restrict__ cos_sin, int pairing, int fuse,
-                        int k_off, int v_off, bf16* __restrict__ k_write, bf16* __restrict__ v_write) {
+                        int k_off, int v_off, bf16* __restrict__ k_write, bf16* __restrict__ v_write, int use_cluster) {
     constexpr int CHUNKS = D / 8;              // 16-byte chunks a row
     constexpr int TILE_BYTES = 64 * D * 2;     // one page of one kv head
     constexpr int KD = D / 16;                 // k-steps of Q K^T
@@ -238,6 +242,9 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __
     float* wm = reinterpret_cast<float*>(smem);              // [4][16] maxima
     float* wl = wm + 4 * 16;                                 // [4][16] sums
     float* wo = wl + 4 * 16;                                 // [4][16][D] weighted values
+    float* po = wo + 4 * 16 * D;                             // [16][D] this block's merged sum, for its cluster peers
+    float* pm = po + 16 * D;                                 // [16] its maximum
+    float* pl = pm + 16;                                     // [16] its normaliser
     if (tq == 0) {
         wm[warp * 16 + gq] = m0;
         wm[warp * 16 + gq + 8] = m1;
@@ -269,6 +276,12 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __
         const int h = g * group + hr;
         if (n_splits == 1) {
             out[((size_t)r * H + h) * D + d] = __float2bfloat16_rn(L > 0.0f ? O / L : 0.0f);
+        } else if (use_cluster) {
+            po[i] = O;
+            if (d == 0) {
+                pm[hr] = M;
+                pl[hr] = L;
+            }
         } else {
             float* dst = scratch + (((size_t)r * H + h) * n_splits + split) * stride;
             __stcg(dst + d, O);
@@ -279,6 +292,29 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __
         }
     }
     if (n_splits == 1) return;
+    if (use_cluster) {
+        // The splits of this (row, kv head) are one thread-block cluster: each block reads its
+        // peers' results out of their shared memory and finishes a share of the outputs, adding
+        // the splits in order.  No scratch memory, no counters, no round trip through the L2.
+        cg::cluster_group cl = cg::this_cluster();
+        cl.sync();
+        const int total = group * D, share = (total + n_splits - 1) / n_splits;
+        for (int i = split * share + threadIdx.x; i < min(total, (split + 1) * share); i += AD_THREADS) {
+            const int hr = i / D, d = i - hr * D;
+            float M = -INFINITY;
+            for (int sp = 0; sp < n_splits; sp++) M = fmaxf(M, cl.map_shared_rank(pm, sp)[hr]);
+            float L = 0.0f, O = 0.0f;
+            for (int sp = 0; sp < n_splits; sp++) {
+                const float ms = cl.map_shared_rank(pm, sp)[hr];
+                const float f = ms == -INFINITY ? 0.0f : exp2f(ms - M);
+                L += cl.map_shared_rank(pl, sp)[hr] * f;
+                O += cl.map_shared_rank(po, sp)[i] * f;
+            }
+            out[((size_t)r * H + g * group + hr) * D + d] = __float2bfloat16_rn(L > 0.0f ? O / L : 0.0f);
+        }
+        cl.sync();   // no block may leave while a peer still reads its shared memory
+        return;
+    }
 
     // The last block of this (row, kv head) to arrive merges the splits in order.
     __threadfence();
@@ -313,6 +349,7 @@ struct FusedRope {
     int pairing;
     int fuse;               // 0: q is already rotated and the cache already holds the row; 1: rotate q; 2: rotate q and append k, v
     int k_off, v_off;       // where a row's k and v heads start inside the fused projection, in elements
+    bool allow_cluster;     // splits may run as a thread-block cluster (else they go through scratch memory)
 };
 
 template <int D>
@@ -320,7 +357,7 @@ static int launch(const void* q, int q_stride, const void* k_cache, const void* 
                   const int* row_slot, void* out, float* scratch, int* counters, int rows, int H, int G, int max_pages, int n_pages,
                   int window, float scale, int n_splits, FusedRope fr, cudaStream_t s) {
     constexpr int TILE_BYTES = 64 * D * 2;
-    constexpr int MERGE_BYTES = (2 * 4 * 16 + 4 * 16 * D) * 4;
+    constexpr int MERGE_BYTES = (2 * 4 * 16 + 4 * 16 * D + 16 * D + 32) * 4;
     constexpr int SMEM = AD_STAGES * 2 * TILE_BYTES > MERGE_BYTES ? AD_STAGES * 2 * TILE_BYTES : MERGE_BYTES;
     static bool configured = false;
     if (!configured) {
@@ -332,10 +369,19 @@ static int launch(const void* q, int q_stride, const void* k_cache, const void* 
         configured = true;
     }
     dim3 grid(n_splits, G, rows);
-    bc_launch(attention_decode_kernel<D>, grid, dim3(AD_THREADS), (size_t)SMEM, s, (const bf16*)q, q_stride, (const bf16*)k_cache,
-              (const bf16*)v_cache, page_table, row_pos, row_slot, (bf16*)out, scratch, counters, H, G, max_pages, n_pages, window,
-              scale * 1.4426950408889634f, (const float2*)fr.cos_sin, fr.pairing, fr.fuse, fr.k_off, fr.v_off, (bf16*)k_cache,
-              (bf16*)v_cache);
+    // Up to eight splits (the portable cluster size) exchange their results through
+    // distributed shared memory; more go through the caller's scratch memory.
+    const bool clustered = n_splits > 1 && n_splits <= 8 && fr.allow_cluster;
+    if (clustered)
+        bc_launch_clustered(attention_decode_kernel<D>, grid, dim3(AD_THREADS), (size_t)SMEM, s, dim3(n_splits, 1, 1), (const bf16*)q, q_stride,
+                            (const bf16*)k_cache, (const bf16*)v_cache, page_table, row_pos, row_slot, (bf16*)out, scratch, counters, H, G,
+                            max_pages, n_pages, window, scale * 1.4426950408889634f, (const float2*)fr.cos_sin, fr.pairing, fr.fuse,
+                            fr.k_off, fr.v_off, (bf16*)k_cache, (bf16*)v_cache, 1);
+    else
+        bc_launch(attention_decode_kernel<D>, grid, dim3(AD_THREADS), (size_t)SMEM, s, (const bf16*)q, q_stride, (const bf16*)k_cache,
+                  (const bf16*)v_cache, page_table, row_pos, row_slot, (bf16*)out, scratch, counters, H, G, max_pages, n_pages, window,
+                  scale * 1.4426950408889634f, (const float2*)fr.cos_sin, fr.pairing, fr.fuse, fr.k_off, fr.v_off, (bf16*)k_cache,
+                  (bf16*)v_cache, 0);
     BC_LAUNCH_STATUS();
 }
 
@@ -356,7 +402,8 @@ extern "C" int bc_attention_decode_workspace(int rows, int H, int G, int D, int 
 // fused projection [rows, (H + 2 G) D] as the product left it, unrotated; fuse = 1 rotates
 // q on the fly, fuse = 2 also writes the row's rotated key and its value to the cache
 // before attending; fuse = 0 is the plain kernel.  cos_sin [positions, D/2, 2] float, or
-// null for no rotation.
+// null for no rotation.  Two to eight splits run as a thread-block cluster and need no
+// scratch memory; adding 4 to fuse sends them through scratch memory like larger counts.
 extern "C" int bc_attention_decode_fused_bf16(const void* q, int q_stride, const void* k_cache, const void* v_cache, const int* page_table,
                                               const int* row_pos, const int* row_slot, void* out, float* scratch, int* counters, int rows,
                                               int H, int G, int D, int max_pages, int n_pages, int window, float scale, int n_splits,
@@ -365,13 +412,13 @@ extern "C" int bc_attention_decode_fused_bf16(const void* q, int q_stride, const
     BC_CHECK_ARG(bc_attention_decode_accepts(H, G, D), "attention_decode: H=%d G=%d D=%d is outside what this kernel takes "
                  "(at most %d heads a kv head, head size a multiple of 16 up to 128)", H, G, D, AD_MAX_GROUP);
     BC_CHECK_ARG(n_splits >= 1 && n_splits <= 65535 && G <= 65535, "attention_decode: bad split count %d", n_splits);
-    BC_CHECK_ARG(n_splits == 1 || (scratch && counters), "attention_decode: splits need scratch memory");
+    BC_CHECK_ARG(n_splits == 1 || (n_splits <= 8 && (fuse & 4) == 0) || (scratch && counters), "attention_decode: these splits need scratch memory");
     BC_CHECK_ARG(q_stride % 2 == 0 && ((uintptr_t)q % 4 == 0), "attention_decode: q must be 4-byte aligned with an even stride");
-    BC_CHECK_ARG(fuse >= 0 && fuse <= 2 && (pairing == 0 || pairing == 1), "attention_decode: bad fuse %d or pairing %d", fuse, pairing);
-    BC_CHECK_ARG(fuse == 0 || q_stride == (H + 2 * G) * D, "attention_decode: fused mode wants the fused projection, stride %d", (H + 2 * G) * D);
-    BC_CHECK_ARG(fuse == 0 || cos_sin == nullptr || (uintptr_t)cos_sin % 16 == 0, "attention_decode: the rotary table must be 16-byte aligned");
+    BC_CHECK_ARG(fuse >= 0 && (fuse & 3) <= 2 && fuse < 8 && (pairing == 0 || pairing == 1), "attention_decode: bad fuse %d or pairing %d", fuse, pairing);
+    BC_CHECK_ARG((fuse & 3) == 0 || q_stride == (H + 2 * G) * D, "attention_decode: fused mode wants the fused projection, stride %d", (H + 2 * G) * D);
+    BC_CHECK_ARG((fuse & 3) == 0 || cos_sin == nullptr || (uintptr_t)cos_sin % 16 == 0, "attention_decode: the rotary table must be 16-byte aligned");
     if (rows == 0) return BC_OK;
-    FusedRope fr{cos_sin, pairing, fuse, H * D, (H + G) * D};
+    FusedRope fr{cos_sin, pairing, fuse & 3, H * D, (H + G) * D, (fuse & 4) == 0};
 #define AD_CASE(DD) \
     case DD: return launch<DD>(q, q_stride, k_cache, v_cache, page_table, row_pos, row_slot, out, scratch, counters, rows, H, G, max_pages, n_pages, window, scale, n_splits, fr, s);
     switch (D) {
@@ -391,7 +438,6 @@ extern "C" int bc_attention_decode_bf16(const void* q, int q_stride, const void*
     BC_CHECK_ARG(bc_attention_decode_accepts(H, G, D), "attention_decode: H=%d G=%d D=%d is outside what this kernel takes "
                  "(at most %d heads a kv head, head size a multiple of 16 up to 128)", H, G, D, AD_MAX_GROUP);
     BC_CHECK_ARG(n_splits >= 1 && n_splits <= 65535 && G <= 65535, "attention_decode: bad split count %d", n_splits);
-    BC_CHECK_ARG(n_splits == 1 || (scratch && counters), "attention_decode: splits need scratch memory");
     BC_CHECK_ARG(q_stride % 2 == 0 && ((uintptr_t)q % 4 == 0), "attention_decode: q must be 4-byte aligned with an even stride");
     if (rows == 0) return BC_OK;
     return bc_attention_decode_fused_bf16(q, q_stride, k_cache, v_cache, page_table, row_pos, row_slot, out, scratch, counters, rows, H, G,
@@ -418,7 +464,7 @@ static int launch_static(float* scratch, int* counters, const void* q, int q_str
                          const int* page_table, const int* row_pos, const int* row_slot, void* out, int rows, int H, int G, int max_pages,
                          int n_pages, int window, float scale, int n_splits, int device, cudaStream_t s) {
     constexpr int TILE_BYTES = 64 * D * 2;
-    constexpr int MERGE_BYTES = (2 * 4 * 16 + 4 * 16 * D) * 4;
+    constexpr int MERGE_BYTES = (2 * 4 * 16 + 4 * 16 * D + 16 * D + 32) * 4;
     constexpr int SMEM = AD_STAGES * 2 * TILE_BYTES > MERGE_BYTES ? AD_STAGES * 2 * TILE_BYTES : MERGE_BYTES;
     {
         // First call for this head size on this device: let the kernel use the shared memory it needs.
@@ -434,7 +480,7 @@ static int launch_static(float* scratch, int* counters, const void* q, int q_str
     }
     bc_launch(attention_decode_kernel<D>, dim3(n_splits, G, rows), dim3(AD_THREADS), (size_t)SMEM, s, (const bf16*)q, q_stride,
               (const bf16*)k_cache, (const bf16*)v_cache, page_table, row_pos, row_slot, (bf16*)out, scratch, counters, H, G, max_pages,
-              n_pages, window, scale * 1.4426950408889634f, (const float2*)nullptr, 0, 0, 0, 0, (bf16*)nullptr, (bf16*)nullptr);
+              n_pages, window, scale * 1.4426950408889634f, (const float2*)nullptr, 0, 0, 0, 0, (bf16*)nullptr, (bf16*)nullptr, 0);
     BC_LAUNCH_STATUS();
 }
 

@@ -22,13 +22,21 @@
 //   - With split-K (grid z > 1, for products with few weight tiles and a long K) every
 //     split leaves its partial tile in scratch memory and the block that arrives last adds
 //     them in the order of the splits, so the sum's order never changes from run to run.
+//     Two to eight splits of a product with few tokens skip the scratch memory: they are
+//     launched as one thread-block cluster, keep their partial tiles in shared memory, and
+//     every block adds up a share of the token columns out of its peers' shared memory,
+//     in the same order.
 //
 // Every wait is bounded: after about a second without progress a thread records where it
 // gave up in a status word, stops waiting, and the block frees its TMEM and returns.
 #include <mutex>
 #include <unordered_map>
 
+#include <cooperative_groups.h>
+
 #include "tc_ptx.cuh"
+
+namespace cg = cooperative_groups;
 
 // ---------------------------------------------------------------------------------- kernel
 struct TcParams {
@@ -39,6 +47,7 @@ struct TcParams {
     int up_row_offset;  // SwiGLU: rows of the up half start here in W
     int stages;
     int k_iters_per_split;
+    int clustered;      // split-K: the splits of a tile are one thread-block cluster and add up through shared memory
 };
 
 template <int BN, int EPI, bool STACK>
@@ -158,7 +167,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         tc_fence_after();
         const uint32_t taddr = tmem + ((uint32_t)(32 * q) << 16);
         bool finish = !split;   // this warp writes the output
-        if (split) {
+        if (split && p.clustered) {
+            // The partial tile goes to this block's shared memory (the ring is drained: every
+            // load was consumed before the accumulator barrier fired), [column][row].
+            if (ok) {
+                float* mine = reinterpret_cast<float*>(smem) + 32 * q + lane;
+#pragma unroll 1
+                for (int c0 = 0; c0 < N_ACC * BN; c0 += 16) {
+                    uint32_t v[16];
+                    tmem_load16(taddr + c0, v);
+                    tmem_load_wait();
+#pragma unroll
+                    for (int j = 0; j < 16; j++) mine[(size_t)(c0 + j) * TC_BM] = __uint_as_float(v[j]);
+                }
+            }
+        } else if (split) {
             if (ok) {
 #pragma unroll 1
                 for (int c0 = 0; c0 < N_ACC * BN; c0 += 16) {   // the second accumulator follows the first in TMEM and in scratch
@@ -244,6 +267,34 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             }
         }
     }
+    if (p.clustered) {
+        // Split-K inside a cluster: block z of the cluster finishes the token columns z, z + S,
+        // ..: it adds the S partial tiles in the order 0, 1, 2 .. straight out of the blocks'
+        // shared memory.  The same sums as through scratch memory, without the round trip.
+        cg::cluster_group cl = cg::this_cluster();
+        cl.sync();
+        if (warp >= 2) {
+            const int q = warp & 3, row = 32 * q + lane, n = n0 + row;
+            const int S = (int)gridDim.z, rank = (int)blockIdx.z;
+            const float* base = reinterpret_cast<const float*>(smem) + row;
+            for (int c = rank; c < BN && t0 + c < p.T; c += S) {
+                float v = 0.0f, u = 0.0f;
+                for (int z = 0; z < S; z++) {
+                    const float* theirs = cl.map_shared_rank(base, z);
+                    v += theirs[(size_t)c * TC_BM];
+                    if (EPI == EPI_SWIGLU) u += theirs[(size_t)(BN + c) * TC_BM];
+                }
+                if (n < p.N) {
+                    const size_t o = (size_t)(t0 + c) * p.N + n;
+                    if (EPI == EPI_STORE) ((bf16*)p.out)[o] = __float2bfloat16_rn(v);
+                    if (EPI == EPI_STORE_F32) ((float*)p.out)[o] = v;
+                    if (EPI == EPI_ADD_F32) atomicAdd(&((float*)p.out)[o], v);
+                    if (EPI == EPI_SWIGLU) ((bf16*)p.out)[o] = __float2bfloat16_rn(silu_mul(v, u));
+                }
+            }
+        }
+        cl.sync();   // no block may leave while a peer still reads its shared memory
+    }
     tc_fence_before();
     __syncthreads();
     if (warp == 1) {
@@ -320,6 +371,11 @@ static int weight_map(CUtensorMap* out, const void* base, int rows, int K) {
 static int g_tc_stage_cap = 0;
 extern "C" void bc_gemm_tc_set_stage_cap(int n) { g_tc_stage_cap = n < 0 ? 0 : n; }
 
+// Two to eight splits of a product with few tokens run as a thread-block cluster and add up
+// through shared memory; 0 sends them through the scratch memory like every other split.
+static int g_tc_cluster = 1;
+extern "C" void bc_gemm_tc_set_cluster(int on) { g_tc_cluster = on != 0; }
+
 template <int BN, int EPI, bool STACK>
 static int launch(const CUtensorMap& mw, const CUtensorMap& mx, TcParams p, int splits, cudaStream_t s) {
     constexpr bool TWO_TILES = EPI != EPI_SWIGLU && BN == 256 && STACK;
@@ -351,7 +407,14 @@ static int launch(const CUtensorMap& mw, const CUtensorMap& mx, TcParams p, int 
     }
     constexpr int ROWS = TWO_TILES ? 2 * TC_BM : TC_BM;   // output rows a block
     dim3 grid((p.N + ROWS - 1) / ROWS, (p.T + BN - 1) / BN, splits);
-    cudaError_t e = bc_launch(gemm_tc_kernel<BN, EPI, STACK>, grid, dim3(TC_THREADS), (size_t)smem, s, mw, mx, p);
+    // The partial tile of a clustered split lies in the drained ring: N_ACC * 128 * BN floats.
+    p.clustered = g_tc_cluster && splits > 1 && splits <= 8 && BN <= 64 && N_ACC * TC_BM * BN * 4 <= stages * STAGE_BYTES;
+    if (!p.clustered && splits > 1 && !(p.partial && p.counters)) {
+        bc_set_error("gemm_tc: this split-K needs a workspace");
+        return BC_ERR_ARG;
+    }
+    cudaError_t e = p.clustered ? bc_launch_clustered(gemm_tc_kernel<BN, EPI, STACK>, grid, dim3(TC_THREADS), (size_t)smem, s, dim3(1, 1, splits), mw, mx, p)
+                                : bc_launch(gemm_tc_kernel<BN, EPI, STACK>, grid, dim3(TC_THREADS), (size_t)smem, s, mw, mx, p);
     if (e != cudaSuccess) {
         bc_set_error("gemm_tc: launch failed: %s", cudaGetErrorString(e));
         return (int)e;
@@ -416,7 +479,7 @@ extern "C" int bc_gemm_tc_bf16(const void* X, const void* W, void* out, int T, i
     BC_CHECK_ARG(K % 8 == 0, "gemm_tc: K=%d is not a multiple of 8 (TMA needs 16-byte row strides); use the CUDA-core product", K);
     BC_CHECK_ARG(((uintptr_t)X % 16 == 0) && ((uintptr_t)W % 16 == 0), "gemm_tc: operands must be 16-byte aligned");
     BC_CHECK_ARG(epilogue >= 0 && epilogue <= 3, "gemm_tc: unknown epilogue %d", epilogue);
-    BC_CHECK_ARG(splits >= 1 && (splits == 1 || (partial && counters)), "gemm_tc: split-K needs a workspace");
+    BC_CHECK_ARG(splits >= 1, "gemm_tc: bad split count %d", splits);
     if (T == 0) return BC_OK;
     const int bn = bc_gemm_tc_token_tile(T, epilogue);
     BC_CHECK_ARG((T + bn - 1) / bn <= 65535, "gemm_tc: %d tokens are too many token tiles", T);

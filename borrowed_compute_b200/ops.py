@@ -50,6 +50,13 @@ def set_pdl(on: bool) -> None:
     lib().bc_set_pdl(_c_int(1 if on else 0))
 
 
+def set_gemm_tc_cluster(on: bool) -> None:
+    """Whether two to eight splits of a product with few tokens add up inside a thread-block
+    cluster (the default) or through scratch memory like all other splits; both give the same
+    bits.  For measurements and tests."""
+    lib().bc_gemm_tc_set_cluster(_c_int(1 if on else 0))
+
+
 def _stream() -> _c_void_p:
     return _c_void_p(torch.cuda.current_stream().cuda_stream)
 
@@ -224,7 +231,13 @@ def gemm_tc_splits(T: int, N: int, K: int, epilogue: int) -> int:
     if bn <= 64:
         # Few tokens: the product streams weights, two blocks fit an SM, and measured rates keep
         # rising up to about two blocks an SM as long as a split still has 8 k-steps of 64.
-        return max(1, min(296 // tiles, -(-K // 64) // 8, 16, fits))
+        s = max(1, min(296 // tiles, -(-K // 64) // 8, 16, fits))
+        # Up to eight splits add up inside a thread-block cluster, which saves the trip through
+        # scratch memory; clusters of 2, 4 or 8 place well on the SMs, other sizes measured
+        # up to 5 us slower.  So a count up to 12 is rounded down to a power of two.
+        if s <= 12:
+            s = 1 << (min(s, 8).bit_length() - 1)
+        return s
     return max(1, min(148 // tiles, -(-K // 64) // 8, 16, fits))
 
 
@@ -300,8 +313,15 @@ def attention_decode_accepts(heads: int, kv_heads: int, head_dim: int, dtype: to
 def attention_decode_splits(rows: int, kv_heads: int, max_pages: int) -> int:
     """Splits of the cached positions so that rows * kv_heads * splits blocks come close to,
     and stay within, one wave of two blocks on each of 148 SMs; never more than a sequence
-    can have pages."""
-    return max(1, min(296 // max(1, rows * kv_heads), max_pages, 64))
+    can have pages.  Up to eight splits merge inside a thread-block cluster, which costs
+    about 4 us less than the merge through scratch memory; so eight is the cap unless the
+    batch is so small that eight leave most SMs idle and sequences can grow so long (beyond
+    256 pages) that each split's share of the keys outweighs the dearer merge."""
+    blocks = max(1, rows * kv_heads)
+    fill = max(1, min(296 // blocks, max_pages, 64))
+    if fill <= 8 or blocks * 8 >= 148 or max_pages <= 256:
+        return min(fill, 8)
+    return fill
 
 
 def _decode_workspace(device: torch.device, floats: int, ints: int):
@@ -323,9 +343,11 @@ def _decode_workspace(device: torch.device, floats: int, ints: int):
 def attention_decode(q: torch.Tensor, q_stride: int, k_cache: torch.Tensor, v_cache: torch.Tensor, page_table: torch.Tensor,
                      row_pos: torch.Tensor, row_slot: torch.Tensor, out: torch.Tensor, heads: int, kv_heads: int, head_dim: int,
                      window: int = 0, scale: Optional[float] = None, splits: Optional[int] = None, fuse: int = 0,
-                     cos_sin: Optional[torch.Tensor] = None, pairing: int = 0) -> None:
+                     cos_sin: Optional[torch.Tensor] = None, pairing: int = 0, via_scratch: bool = False) -> None:
     """Attention of one new row a sequence (bf16): the cached positions are split across
     blocks and the heads of a kv head share each read; results are merged in a fixed order.
+    Two to eight splits form a thread-block cluster and merge through one another's shared
+    memory; more (or ``via_scratch``) merge through scratch memory, with the same result.
     ``fuse`` 1 or 2: ``q`` is the fused projection as the product left it; q is rotated on
     the fly by ``cos_sin`` (None: no rotation), and with 2 the row's rotated key and its
     value are appended to the cache first (what rope_append would have done)."""
@@ -355,7 +377,7 @@ def attention_decode(q: torch.Tensor, q_stride: int, k_cache: torch.Tensor, v_ca
     _call(_fn("bc_attention_decode_fused_bf16"), _ptr(q), _c_int(q_stride), _ptr(k_cache), _ptr(v_cache), _ptr(page_table), _ptr(row_pos),
           _ptr(row_slot), _ptr(out), _ptr(scratch), _ptr(counters), _c_int(rows), _c_int(heads), _c_int(kv_heads), _c_int(head_dim),
           _c_int(page_table.shape[1]), _c_int(k_cache.shape[0]), _c_int(window), _c_float(scale), _c_int(splits), _ptr(cos_sin),
-          _c_int(pairing), _c_int(fuse), _stream())
+          _c_int(pairing), _c_int(fuse + (4 if via_scratch else 0)), _stream())
 
 
 def attention_prefill_accepts(heads: int, kv_heads: int, head_dim: int, dtype: torch.dtype) -> bool:

@@ -62,6 +62,37 @@ def test_gemm_tc_all_epilogues(T, N, K, splits):
     assert ops.gemm_tc_status() == 0
 
 
+@pytest.mark.parametrize("T,N,K,splits", [(8, 512, 4096, 4), (33, 256, 2048, 3), (3, 100, 1024, 2), (8, 384, 2048, 8), (61, 130, 1536, 5), (8, 256, 4096, 12)])
+def test_gemm_tc_splits_agree_through_cluster_and_through_scratch(T, N, K, splits):
+    """Splits that add up inside a thread-block cluster give the bits of splits that add up
+    through scratch memory (the same order of additions), for every epilogue."""
+    from borrowed_compute_b200 import ops
+
+    x, w = operands(T, N, K, T + N + K)
+    wn = w[:N].contiguous()
+    base = torch.from_numpy(np.random.default_rng(2).standard_normal((T, N)).astype(np.float32)).cuda()
+    results = []
+    try:
+        for clustered in (True, False):
+            ops.set_gemm_tc_cluster(clustered)
+            out32 = torch.full((T, N), 7.0, dtype=torch.float32, device="cuda")
+            ops.gemm_tc(x, wn, out32, ops.EPI_STORE_F32, splits=splits)
+            out16 = torch.full((T, N), 7.0, dtype=torch.bfloat16, device="cuda")
+            ops.gemm_tc(x, wn, out16, ops.EPI_STORE, splits=splits)
+            acc = base.clone()
+            ops.gemm_tc(x, wn, acc, ops.EPI_ADD_F32, splits=splits)
+            act = torch.full((T, N), 7.0, dtype=torch.bfloat16, device="cuda")
+            ops.gemm_tc(x, w, act, ops.EPI_SWIGLU, splits=splits)
+            results.append((out32, out16, acc, act))
+    finally:
+        ops.set_gemm_tc_cluster(True)
+    assert ops.gemm_tc_status() == 0
+    for a, b, name in zip(results[0], results[1], ("float store", "bf16 store", "residual add", "SwiGLU")):
+        assert torch.equal(a, b), name
+    full = f64(x) @ f64(wn).T
+    assert np.abs(f64(results[0][0]) - full).max() <= 2e-5 * (1.0 + np.abs(full).max())
+
+
 def test_gemm_tc_matches_the_cuda_core_twin():
     from borrowed_compute_b200 import ops
 

@@ -239,7 +239,7 @@ def test_attention_finds_one_far_key(dtype):
 
 
 @pytest.mark.parametrize("H,G,D", [(6, 3, 48), (4, 4, 16), (16, 1, 32), (32, 8, 128), (8, 2, 64)])
-@pytest.mark.parametrize("splits", [1, 3, 8])
+@pytest.mark.parametrize("splits", [1, 3, 8, 11])
 @pytest.mark.parametrize("window", [0, 70])
 def test_attention_decode(H, G, D, splits, window):
     """The split bf16 decode kernel against the float64 formula and its one-warp twin, for
@@ -272,6 +272,9 @@ def test_attention_decode(H, G, D, splits, window):
     again = torch.empty_like(out)
     ops.attention_decode(*args, again, H, G, D, window=window, splits=splits)
     assert torch.equal(out, again), "the same launch twice must give the same bits"
+    again.fill_(5.0)
+    ops.attention_decode(*args, again, H, G, D, window=window, splits=splits, via_scratch=True)
+    assert torch.equal(out, again), "splits merged through a cluster's shared memory and through scratch memory must agree"
     got, qs = f64(out), stored(q, torch.bfloat16)
     for i in range(7):
         if row_slot[i] < 0:
