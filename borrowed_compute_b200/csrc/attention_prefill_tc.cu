@@ -1,0 +1,433 @@
+// Prompt attention on the 5th-generation tensor cores (bf16, head size 64 or 128).
+//
+// What is computed is the reference's attention (crates/bc-infer/src/model.rs:448-481) with
+// the running maximum / sum of its kernel (crates/bc-infer/src/gpu/kernels.h:271-324); how
+// it is laid out is Blackwell's own:
+//
+//   - A block takes 128 query rows = (tokens) x (the heads that share one kv head), token
+//     major, of one sequence.  Q comes by one 3-d TMA box per 64 elements of the head size
+//     straight out of the fused projection [row][head][d]; every 64-position page of keys
+//     and values comes by 2-d TMA boxes from the paged cache into a ring of stages.  All
+//     tiles are 128-byte-swizzled blocks of [rows][64 elements].
+//   - S = Q K^T is one chain of tcgen05.mma (M 128 rows, N 64 positions, K the head size),
+//     accumulated in TMEM, two buffers, so the scores of the next page are computed while
+//     the softmax warps work on this one.  Keys are the k-major B operand as they lie.
+//   - Four softmax warps own 32 rows each, one row a thread (TMEM lane = row), so row
+//     maxima and sums need no shuffles: tcgen05.ld the scores, mask what the row may not
+//     see (positions after its own, before its window), exponentiate against the running
+//     maximum, round to bf16 and write P to shared memory in the A-operand layout.
+//   - O += P V is a second chain of tcgen05.mma (N = head size, K = 64 positions) into a
+//     TMEM accumulator that stays there for the whole block.  Values are the n-major B
+//     operand ([position][d] with d contiguous), exactly as TMA wrote the page.
+//   - The running maximum is only raised when the new maximum exceeds it by more than 8 (in
+//     log2 units), so P stays below 2^8 and the accumulator is rescaled (TMEM load, multiply,
+//     store) a few times a block instead of once a page.  Sums and outputs use the same
+//     maximum, so the result is the softmax all the same.
+//
+// Warp roles: warp 0 issues TMA, warp 1 owns TMEM and issues the MMAs, warps 2-5 are the
+// softmax and write the output.  Every wait is bounded (about a second); a wait that gives
+// up records where in a status word, and the block frees its TMEM and returns.
+#include <mutex>
+#include <unordered_map>
+
+#include "mma_tiles.cuh"
+#include "tc_ptx.cuh"
+
+#define APT_THREADS 192
+#define APT_ROWS 128
+#define APT_STAGES 4
+#define APT_RAISE 8.0f      // the running maximum follows the true one at this distance at most
+
+template <int D>
+__global__ void __launch_bounds__(APT_THREADS, 1)
+attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                            const __grid_constant__ CUtensorMap map_v, const int* __restrict__ page_table, const int* __restrict__ seq_rows,
+                            const int* __restrict__ seq_slot, const int* __restrict__ seq_start, bf16* __restrict__ out, int H, int G,
+                            int max_pages, int n_pages, int window, float scale_log2) {
+    constexpr int DB = D / 64;                         // 64-element blocks of the head size
+    constexpr int ROW_BLOCK = APT_ROWS * 128;          // bytes of a [128 rows][64 elements] block
+    constexpr int KV_BLOCK = BC_PAGE * 128;            // bytes of a [64 positions][64 elements] block
+    constexpr int Q_BYTES = DB * ROW_BLOCK;
+    constexpr int STAGE_BYTES = 2 * DB * KV_BLOCK;     // keys, then values, of one page
+    constexpr int S_COL = 0, O_COL = 128;              // TMEM columns: scores 0-63 and 64-127, output from 128
+    constexpr int TMEM_COLS = 256;
+    static_assert(D == 64 || D == 128, "head size 64 or 128");
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t* q_smem = smem;
+    uint8_t* p_smem = q_smem + Q_BYTES;                // two P tiles
+    uint8_t* kv_smem = p_smem + 2 * ROW_BLOCK;
+    __shared__ __align__(8) uint64_t bars[2 * APT_STAGES + 6];
+    __shared__ uint32_t tmem_slot;
+
+    pdl_launch_dependents();
+    pdl_wait();
+    const int g = blockIdx.y, sq = blockIdx.z;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int group = H / G;
+    const int tokens_per_tile = APT_ROWS / group;         // rows past tokens_per_tile * group are padding
+    const int slot = seq_slot[sq];
+    const int row0 = seq_rows[sq], n_new = seq_rows[sq + 1] - row0;
+    const int n_tiles_q = (n_new + tokens_per_tile - 1) / tokens_per_tile;
+    // The last query tiles see the most keys: they go first.
+    const int q_tile = n_tiles_q - 1 - (int)blockIdx.x;
+    if (slot < 0 || q_tile < 0) return;                   // the whole block, before anything is set up
+    const int start = seq_start[sq];
+    const int tok0 = q_tile * tokens_per_tile;
+    const int tok_end = min(n_new, tok0 + tokens_per_tile);
+    const int* pages = page_table + (size_t)slot * max_pages;
+    // Pages this tile reads: from the first position its first token sees to its last token's own.
+    const int first_pos = window > 0 && start + tok0 + 1 > window ? start + tok0 + 1 - window : 0;
+    const int t_begin = first_pos / BC_PAGE, t_end = (start + tok_end - 1) / BC_PAGE + 1;
+    const int n_tiles = t_end - t_begin;
+
+    const uint32_t kv_full0 = smem_u32(&bars[0]), kv_empty0 = smem_u32(&bars[APT_STAGES]);
+    const uint32_t q_full = smem_u32(&bars[2 * APT_STAGES]), s_full0 = smem_u32(&bars[2 * APT_STAGES + 1]);
+    const uint32_t p_full0 = smem_u32(&bars[2 * APT_STAGES + 3]), o_bar = smem_u32(&bars[2 * APT_STAGES + 5]);
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < APT_STAGES; s++) {
+            mbar_init(kv_full0 + 8 * s, 1);
+            mbar_init(kv_empty0 + 8 * s, 1);
+        }
+        mbar_init(q_full, 1);
+        mbar_init(s_full0, 1);
+        mbar_init(s_full0 + 8, 1);
+        mbar_init(p_full0, 128);
+        mbar_init(p_full0 + 8, 128);
+        mbar_init(o_bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) tmem_alloc(smem_u32(&tmem_slot), TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            // Q: one box [tokens][heads of the group][64 elements] per 64 elements of the head size.
+            mbar_expect_tx(q_full, (uint32_t)(DB * tokens_per_tile * group * 128));
+            for (int b = 0; b < DB; b++) tma_load_3d(smem_u32(q_smem + b * ROW_BLOCK), &map_q, q_full, b * 64, g * group, row0 + tok0);
+            for (int j = 0; j < n_tiles; j++) {
+                const int s = j % APT_STAGES;
+                if (j >= APT_STAGES && !mbar_wait(kv_empty0 + 8 * s, ((j / APT_STAGES) & 1) ^ 1, 1)) break;
+                const int tile = t_begin + j;
+                int page = tile < max_pages ? pages[tile] : -1;
+                if (page < 0 || page >= n_pages) page = 0;   // never used: every position of such a tile is masked
+                const int y = (page * G + g) * BC_PAGE;
+                const uint32_t dst = smem_u32(kv_smem + (size_t)s * STAGE_BYTES);
+                mbar_expect_tx(kv_full0 + 8 * s, STAGE_BYTES);
+                for (int b = 0; b < DB; b++) {
+                    tma_load_2d(dst + b * KV_BLOCK, &map_k, kv_full0 + 8 * s, b * 64, y);
+                    tma_load_2d(dst + (DB + b) * KV_BLOCK, &map_v, kv_full0 + 8 * s, b * 64, y);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc_s = instr_desc_b(BC_PAGE, false);   // S: N = 64 positions, keys k-major
+            constexpr uint32_t idesc_o = instr_desc_b(D, true);          // O: N = head size, values n-major
+            const uint32_t q_addr = smem_u32(q_smem);
+            auto scores = [&](int j) {   // S[j & 1] = Q K(j)^T
+                const uint32_t k_addr = smem_u32(kv_smem + (size_t)(j % APT_STAGES) * STAGE_BYTES);
+#pragma unroll
+                for (int kk = 0; kk < D / 16; kk++)
+                    mma_bf16(tmem + S_COL + (j & 1) * BC_PAGE, smem_desc(q_addr + (kk >> 2) * ROW_BLOCK) + 2 * (kk & 3),
+                             smem_desc(k_addr + (kk >> 2) * KV_BLOCK) + 2 * (kk & 3), idesc_s, kk != 0);
+                mma_commit(s_full0 + 8 * (j & 1));
+            };
+            bool ok = mbar_wait(q_full, 0, 2);
+            for (int j = 0; j < 2 && j < n_tiles && ok; j++) {
+                ok = mbar_wait(kv_full0 + 8 * (j % APT_STAGES), 0, 3);
+                if (!ok) break;
+                tc_fence_after();
+                scores(j);
+            }
+            for (int j = 0; j < n_tiles && ok; j++) {
+                ok = mbar_wait(p_full0 + 8 * (j & 1), (j >> 1) & 1, 4);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t p_addr = smem_u32(p_smem + (j & 1) * ROW_BLOCK);
+                const uint32_t v_addr = smem_u32(kv_smem + (size_t)(j % APT_STAGES) * STAGE_BYTES + DB * KV_BLOCK);
+#pragma unroll
+                for (int kk = 0; kk < BC_PAGE / 16; kk++)
+                    mma_bf16(tmem + O_COL, smem_desc(p_addr) + 2 * kk, smem_desc_mn(v_addr + kk * 2048, KV_BLOCK), idesc_o, (j | kk) != 0);
+                mma_commit(kv_empty0 + 8 * (j % APT_STAGES));
+                mma_commit(o_bar);
+                if (j + 2 < n_tiles) {
+                    const int s = (j + 2) % APT_STAGES;
+                    ok = mbar_wait(kv_full0 + 8 * s, ((j + 2) / APT_STAGES) & 1, 5);
+                    if (!ok) break;
+                    tc_fence_after();
+                    scores(j + 2);
+                }
+            }
+        }
+    } else {
+        // Softmax: this thread owns row 32 q + lane of the tile, TMEM lane of the same number.
+        const int q = warp & 3;
+        const int row = 32 * q + lane;
+        const int tok = tok0 + row / group, head = g * group + row % group;
+        const bool live = row / group < tokens_per_tile && tok < n_new;
+        const int pos = start + tok;
+        const int lo = window > 0 && pos + 1 > window ? pos + 1 - window : 0;
+        const int warp_first_pos = start + tok0 + (32 * q) / group;      // the smallest position a row of this warp has
+        const uint32_t lane_base = tmem + ((uint32_t)(32 * q) << 16);
+        float m_used = -INFINITY, l = 0.0f;
+        bool ok = true;
+        for (int j = 0; j < n_tiles; j++) {
+            if (lane == 0) ok = mbar_wait(s_full0 + 8 * (j & 1), (j >> 1) & 1, 6);
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (!ok) break;
+            tc_fence_after();
+            uint32_t sv[64];
+#pragma unroll
+            for (int c = 0; c < 4; c++) tmem_load16(lane_base + S_COL + (j & 1) * BC_PAGE + 16 * c, sv + 16 * c);
+            tmem_load_wait();
+            const int tile = t_begin + j;
+            const bool page_ok = tile < max_pages && pages[tile] >= 0 && pages[tile] < n_pages;
+            // A page that ends at or before the position of this warp's first row is seen whole
+            // by all of its rows (padding rows are never written): no mask to work out.
+            const bool whole = window == 0 && page_ok && tile * BC_PAGE + BC_PAGE - 1 <= warp_first_pos;
+            float tmax = -INFINITY;
+            if (whole) {
+#pragma unroll
+                for (int c = 0; c < 64; c++) tmax = fmaxf(tmax, __uint_as_float(sv[c]));
+            } else {
+#pragma unroll
+                for (int c = 0; c < 64; c++) {
+                    const int t = tile * BC_PAGE + c;
+                    const bool seen = page_ok && live && t >= lo && t <= pos;
+                    const float v = seen ? __uint_as_float(sv[c]) : -INFINITY;
+                    sv[c] = __float_as_uint(v);
+                    tmax = fmaxf(tmax, v);
+                }
+            }
+            const float m_true = fmaxf(m_used, tmax * scale_log2);
+            const bool raise = m_true > m_used + APT_RAISE;     // also the first finite maximum: -inf + 8 = -inf
+            float corr = 1.0f;
+            if (raise) {
+                corr = m_used == -INFINITY ? 0.0f : exp2f(m_used - m_true);
+                m_used = m_true;
+                l *= corr;
+            }
+            if (j > 0) {
+                // Every phase of the output barrier is waited for, in order (a parity tells two
+                // phases apart, not more): the product of page j - 1 finished long ago as a rule.
+                if (lane == 0) ok = mbar_wait(o_bar, (j - 1) & 1, 7);
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+                if (!ok) break;
+            }
+            if (j > 0 && __any_sync(0xffffffffu, raise)) {
+                // Rescale this warp's rows of the accumulator: every product issued so far is in it.
+                tc_fence_after();
+#pragma unroll 1
+                for (int c = 0; c < D; c += 16) {
+                    uint32_t ov[16];
+                    tmem_load16(lane_base + O_COL + c, ov);
+                    tmem_load_wait();
+#pragma unroll
+                    for (int i = 0; i < 16; i++) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * corr);
+                    tmem_store16(lane_base + O_COL + c, ov);
+                }
+                tmem_store_wait();
+            }
+            const float base = m_used == -INFINITY ? 0.0f : m_used;
+            float sum = 0.0f;
+            uint8_t* p_row = p_smem + (j & 1) * ROW_BLOCK + row * 128;
+#pragma unroll
+            for (int c8 = 0; c8 < 8; c8++) {
+                uint32_t packed[4];
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const float a = fast_exp2(fmaf(__uint_as_float(sv[c8 * 8 + 2 * i]), scale_log2, -base));
+                    const float b = fast_exp2(fmaf(__uint_as_float(sv[c8 * 8 + 2 * i + 1]), scale_log2, -base));
+                    sum += a + b;
+                    packed[i] = pack_bf16(a, b);
+                }
+                *reinterpret_cast<uint4*>(p_row + ((c8 ^ (row & 7)) << 4)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+            }
+            l += sum;
+            fence_proxy_async();
+            tc_fence_before();
+            mbar_arrive(p_full0 + 8 * (j & 1));
+        }
+        // The output: the accumulator over this row's sum.
+        if (ok) {
+            if (lane == 0) ok = mbar_wait(o_bar, (n_tiles - 1) & 1, 8);
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+        }
+        if (ok) {
+            tc_fence_after();
+            const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+            bf16* dst = out + ((size_t)(row0 + tok) * H + head) * D;
+#pragma unroll 1
+            for (int c = 0; c < D; c += 16) {
+                uint32_t ov[16];
+                tmem_load16(lane_base + O_COL + c, ov);
+                tmem_load_wait();
+                if (live) {
+                    uint32_t packed[8];
+#pragma unroll
+                    for (int i = 0; i < 8; i++) packed[i] = pack_bf16(__uint_as_float(ov[2 * i]) * inv, __uint_as_float(ov[2 * i + 1]) * inv);
+                    *reinterpret_cast<uint4*>(dst + c) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                    *reinterpret_cast<uint4*>(dst + c + 8) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem, TMEM_COLS);
+    }
+}
+
+// -------------------------------------------------------------------------------- the host
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    });
+    return fn;
+}
+
+// The cache as a matrix [pages * kv heads * 64 positions, D], cut into boxes of 64 x 64.
+static int cache_map(CUtensorMap* map, const void* base, long long rows, int D) {
+    cuuint64_t dims[2] = {(cuuint64_t)D, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)D * 2};
+    cuuint32_t box[2] = {64, BC_PAGE};
+    cuuint32_t elem[2] = {1, 1};
+    CUresult r = encode_fn()(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        bc_set_error("attention_prefill_tc: cuTensorMapEncodeTiled failed (%d) for a cache of %lld rows of %d", (int)r, rows, D);
+        return BC_ERR_DRIVER;
+    }
+    return BC_OK;
+}
+
+// Cache maps are made once per (pointer, shape) and kept: the cache's storage does not move.
+struct CacheKey {
+    const void* p;
+    long long rows;
+    int D;
+    bool operator==(const CacheKey& o) const { return p == o.p && rows == o.rows && D == o.D; }
+};
+struct CacheKeyHash {
+    size_t operator()(const CacheKey& k) const { return std::hash<const void*>()(k.p) ^ ((size_t)k.rows * 1000003u) ^ (size_t)k.D; }
+};
+static std::unordered_map<CacheKey, CUtensorMap, CacheKeyHash> g_cache_maps;
+static std::mutex g_cache_maps_mutex;
+
+static int cached_cache_map(CUtensorMap* out, const void* base, long long rows, int D) {
+    std::lock_guard<std::mutex> lock(g_cache_maps_mutex);
+    CacheKey key{base, rows, D};
+    auto it = g_cache_maps.find(key);
+    if (it == g_cache_maps.end()) {
+        CUtensorMap m;
+        int st = cache_map(&m, base, rows, D);
+        if (st != BC_OK) return st;
+        if (g_cache_maps.size() > 4096) g_cache_maps.clear();
+        it = g_cache_maps.emplace(key, m).first;
+    }
+    *out = it->second;
+    return BC_OK;
+}
+
+// The queries as a tensor [rows][heads][D] inside the fused projection (a row is q_stride
+// elements long), cut into boxes of [tokens][heads of a group][64].
+static int query_map(CUtensorMap* map, const void* q, int q_stride, int total_rows, int H, int D, int group, int tokens_per_tile) {
+    cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)H, (cuuint64_t)total_rows};
+    cuuint64_t strides[2] = {(cuuint64_t)D * 2, (cuuint64_t)q_stride * 2};
+    cuuint32_t box[3] = {64, (cuuint32_t)group, (cuuint32_t)tokens_per_tile};
+    cuuint32_t elem[3] = {1, 1, 1};
+    CUresult r = encode_fn()(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(q), dims, strides, box, elem,
+                             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        bc_set_error("attention_prefill_tc: cuTensorMapEncodeTiled failed (%d) for queries [%d, %d, %d], row stride %d", (int)r, total_rows, H, D,
+                     q_stride);
+        return BC_ERR_DRIVER;
+    }
+    return BC_OK;
+}
+
+template <int D>
+static int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const int* page_table, const int* seq_rows,
+                  const int* seq_slot, const int* seq_start, void* out, int seqs, int max_new, int H, int G, int max_pages, int n_pages,
+                  int window, float scale, cudaStream_t s) {
+    constexpr int DB = D / 64;
+    constexpr int SMEM = DB * APT_ROWS * 128 + 2 * APT_ROWS * 128 + APT_STAGES * 2 * DB * BC_PAGE * 128 + 1024;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+        if (e != cudaSuccess) {
+            bc_set_error("attention_prefill_tc: cannot set shared memory to %d: %s", SMEM, cudaGetErrorString(e));
+            return (int)e;
+        }
+        configured = true;
+    }
+    const int tokens_per_tile = APT_ROWS / (H / G);
+    dim3 grid((max_new + tokens_per_tile - 1) / tokens_per_tile, G, seqs);
+    cudaError_t e = bc_launch(attention_prefill_tc_kernel<D>, grid, dim3(APT_THREADS), (size_t)SMEM, s, mq, mk, mv, page_table, seq_rows, seq_slot,
+                              seq_start, (bf16*)out, H, G, max_pages, n_pages, window, scale * 1.4426950408889634f);
+    if (e != cudaSuccess) {
+        bc_set_error("attention_prefill_tc: launch failed: %s", cudaGetErrorString(e));
+        return (int)e;
+    }
+    BC_LAUNCH_STATUS();
+}
+
+// Whether this kernel takes the sizes (else the caller uses the mma.sync kernel or the
+// one-warp-a-row kernel): head size 64 or 128, at most 128 heads a kv head.
+extern "C" int bc_attention_prefill_tc_accepts(int H, int G, int D) {
+    return G > 0 && H % G == 0 && H / G <= APT_ROWS && (D == 64 || D == 128) && encode_fn() != nullptr;
+}
+
+// The interface of bc_attention_prefill_bf16, plus total_rows: how many rows q has in all
+// (TMA reads past them as zeros).  q and the caches 16-byte aligned, q_stride a multiple of 8.
+extern "C" int bc_attention_prefill_tc_bf16(const void* q, int q_stride, int total_rows, const void* k_cache, const void* v_cache,
+                                            const int* page_table, const int* seq_rows, const int* seq_slot, const int* seq_start, void* out,
+                                            int seqs, int max_new, int H, int G, int D, int max_pages, int n_pages, int window, float scale,
+                                            cudaStream_t s) {
+    BC_CHECK_ARG(seqs >= 0 && seqs <= 65535 && max_new >= 0 && total_rows >= 0, "attention_prefill_tc: bad sizes seqs=%d max_new=%d rows=%d", seqs,
+                 max_new, total_rows);
+    BC_CHECK_ARG(bc_attention_prefill_tc_accepts(H, G, D), "attention_prefill_tc: H=%d G=%d D=%d is outside what this kernel takes "
+                 "(at most %d heads a kv head, head size 64 or 128)", H, G, D, APT_ROWS);
+    BC_CHECK_ARG(q_stride % 8 == 0 && (uintptr_t)q % 16 == 0 && (uintptr_t)out % 16 == 0 && (uintptr_t)k_cache % 16 == 0 && (uintptr_t)v_cache % 16 == 0,
+                 "attention_prefill_tc: q, out and the caches must be 16-byte aligned, the row stride a multiple of 8");
+    BC_CHECK_ARG(G <= 65535 && n_pages > 0, "attention_prefill_tc: bad kv heads %d or pages %d", G, n_pages);
+    if (seqs == 0 || max_new == 0 || total_rows == 0) return BC_OK;
+    CUtensorMap mq, mk, mv;
+    const int group = H / G;
+    int st = query_map(&mq, q, q_stride, total_rows, H, D, group, APT_ROWS / group);
+    if (st != BC_OK) return st;
+    const long long cache_rows = (long long)n_pages * G * BC_PAGE;
+    if ((st = cached_cache_map(&mk, k_cache, cache_rows, D)) != BC_OK) return st;
+    if ((st = cached_cache_map(&mv, v_cache, cache_rows, D)) != BC_OK) return st;
+    if (D == 64) return launch<64>(mq, mk, mv, page_table, seq_rows, seq_slot, seq_start, out, seqs, max_new, H, G, max_pages, n_pages, window, scale, s);
+    return launch<128>(mq, mk, mv, page_table, seq_rows, seq_slot, seq_start, out, seqs, max_new, H, G, max_pages, n_pages, window, scale, s);
+}
+
+// This unit's status word: 0, or where a bounded wait gave up.  Reading it waits for the
+// device; `reset` clears it.
+extern "C" int bc_attention_prefill_tc_status(int reset) {
+    int v = 0;
+    cudaMemcpyFromSymbol(&v, g_tc_status, sizeof(int));
+    if (reset && v != 0) {
+        int zero = 0;
+        cudaMemcpyToSymbol(g_tc_status, &zero, sizeof(int));
+    }
+    return v;
+}

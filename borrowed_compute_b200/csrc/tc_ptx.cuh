@@ -16,8 +16,8 @@ enum { EPI_STORE = 0, EPI_STORE_F32 = 1, EPI_ADD_F32 = 2, EPI_SWIGLU = 3 };
 #define TC_WAIT_CYCLES 2000000000ll
 
 // Status word: 0 while all is well, else (code << 16 | detail) of the first wait that gave up.
-// One copy a translation unit (the library builds without relocatable device code): the
-// tensor-core kernels all live in gemm_tc.cu's unit and report through this one word.
+// One copy a translation unit (the library builds without relocatable device code): every
+// unit that includes this header exports a reader of its own word.
 static __device__ int g_tc_status = 0;
 
 // ------------------------------------------------------------------------------ PTX pieces
@@ -60,6 +60,17 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
                  "l"(map), "r"(bar), "r"(x), "r"(y)
                  : "memory");
 }
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y, int z) {
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];" ::"r"(dst),
+                 "l"(map), "r"(bar), "r"(x), "r"(y), "r"(z)
+                 : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+// Makes this thread's ordinary shared-memory writes visible to the asynchronous proxy (the
+// tensor core reads operands through it).
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 // The same with an L2 policy: weights are read once a step and should leave the L2 first,
 // so that activations, partial sums and the cache pages of the step stay.
 __device__ __forceinline__ uint64_t l2_evict_first_policy() {
@@ -103,6 +114,14 @@ __device__ __forceinline__ void tmem_load16(uint32_t taddr, uint32_t* v) {
         : "memory");
 }
 __device__ __forceinline__ void tmem_load_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_store16(uint32_t taddr, const uint32_t* v) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(taddr),
+        "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]),
+        "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_store_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 // Shared-memory operand descriptor: k-major tile of 128-byte rows, 128-byte swizzle, as TMA
 // writes it.  Bits 0-13 address/16; 16-29 leading offset/16 (unused for swizzled k-major,
@@ -110,6 +129,19 @@ __device__ __forceinline__ void tmem_load_wait() { asm volatile("tcgen05.wait::l
 // (SWIZZLE_128B).  Stepping 16 k (32 bytes) inside the swizzle row adds 2 to the address.
 __device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
     return (uint64_t)((addr >> 4) & 0x3fff) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+}
+// The same tile read the other way round: an operand whose M or N index is the contiguous
+// one (a [k, n] matrix with n contiguous, such as values [position, head size] as the B of
+// P V), in blocks of [k rows][64 elements] with the 128-byte swizzle, as TMA writes them.
+// Eight k rows are 1024 bytes apart (stride offset); the next 64 elements of M or N are
+// `next_block` bytes on (leading offset).  Stepping 16 k adds 16 rows (2048 bytes).
+__device__ __forceinline__ uint64_t smem_desc_mn(uint32_t addr, uint32_t next_block) {
+    return (uint64_t)((addr >> 4) & 0x3fff) | ((uint64_t)((next_block >> 4) & 0x3fff) << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+}
+// Instruction descriptor of kind::f16 for M = 128, float accumulate, bf16 operands, A k-major,
+// B k-major or (b_mn) n-major.
+__host__ __device__ constexpr uint32_t instr_desc_b(int n, bool b_mn) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn ? 1u : 0u) << 16) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
 }
 // Instruction descriptor of kind::f16: float accumulate (bit 4), A and B bf16 (bits 7, 10),
 // both k-major (bits 15, 16 clear), N / 8 at bit 17, M / 16 at bit 24.

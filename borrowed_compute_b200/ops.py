@@ -276,6 +276,11 @@ def gemm_tc_status(reset: bool = True) -> int:
     return int(_fn("bc_gemm_tc_status")(_c_int(1 if reset else 0)))
 
 
+def attention_prefill_tc_status(reset: bool = True) -> int:
+    """The same word of the tcgen05 prompt attention kernel."""
+    return int(_fn("bc_attention_prefill_tc_status")(_c_int(1 if reset else 0)))
+
+
 # --------------------------------------------------------------------------------- attention
 
 def attention_rows(q: torch.Tensor, q_stride: int, k_cache: torch.Tensor, v_cache: torch.Tensor, page_table: torch.Tensor,
@@ -386,11 +391,22 @@ def attention_prefill_accepts(heads: int, kv_heads: int, head_dim: int, dtype: t
     return dtype == torch.bfloat16 and bool(_fn("bc_attention_prefill_accepts")(_c_int(heads), _c_int(kv_heads), _c_int(head_dim)))
 
 
+def attention_prefill_tc_accepts(heads: int, kv_heads: int, head_dim: int, q: Optional[torch.Tensor] = None, q_stride: int = 0) -> bool:
+    """Whether the tcgen05 prompt kernel takes these sizes (head size 64 or 128, at most 128
+    heads a kv head) and, if given, this q (16-byte aligned, row stride a multiple of 8)."""
+    if not _fn("bc_attention_prefill_tc_accepts")(_c_int(heads), _c_int(kv_heads), _c_int(head_dim)):
+        return False
+    return q is None or (q.data_ptr() % 16 == 0 and q_stride % 8 == 0)
+
+
 def attention_prefill(q: torch.Tensor, q_stride: int, k_cache: torch.Tensor, v_cache: torch.Tensor, page_table: torch.Tensor,
                       seq_rows: torch.Tensor, seq_slot: torch.Tensor, seq_start: torch.Tensor, out: torch.Tensor, seqs: int, max_new: int,
-                      heads: int, kv_heads: int, head_dim: int, window: int = 0, scale: Optional[float] = None) -> None:
+                      heads: int, kv_heads: int, head_dim: int, window: int = 0, scale: Optional[float] = None,
+                      use_tc: Optional[bool] = None) -> None:
     """Causal attention of every sequence's new rows against its cached positions (which
-    include the new rows' own keys and values), 64 query rows a block (bf16)."""
+    include the new rows' own keys and values), bf16.  Head sizes 64 and 128 run on the
+    tcgen05 tensor cores, 128 query rows a block (scores and output accumulate in TMEM);
+    other head sizes on mma.sync tiles, 64 rows a block.  ``use_tc`` forces one or the other."""
     _need(q, "q", torch.bfloat16)
     _need(k_cache, "k_cache", torch.bfloat16)
     _need(v_cache, "v_cache", torch.bfloat16)
@@ -407,6 +423,13 @@ def attention_prefill(q: torch.Tensor, q_stride: int, k_cache: torch.Tensor, v_c
         raise KernelError("attention_prefill: fewer sequence entries than sequences")
     if scale is None:
         scale = 1.0 / float(head_dim) ** 0.5
+    if use_tc is None:
+        use_tc = attention_prefill_tc_accepts(heads, kv_heads, head_dim, q, q_stride)
+    if use_tc:
+        _call(_fn("bc_attention_prefill_tc_bf16"), _ptr(q), _c_int(q_stride), _c_int(out.shape[0]), _ptr(k_cache), _ptr(v_cache), _ptr(page_table),
+              _ptr(seq_rows), _ptr(seq_slot), _ptr(seq_start), _ptr(out), _c_int(seqs), _c_int(max_new), _c_int(heads), _c_int(kv_heads),
+              _c_int(head_dim), _c_int(page_table.shape[1]), _c_int(k_cache.shape[0]), _c_int(window), _c_float(scale), _stream())
+        return
     _call(_fn("bc_attention_prefill_bf16"), _ptr(q), _c_int(q_stride), _ptr(k_cache), _ptr(v_cache), _ptr(page_table), _ptr(seq_rows),
           _ptr(seq_slot), _ptr(seq_start), _ptr(out), _c_int(seqs), _c_int(max_new), _c_int(heads), _c_int(kv_heads), _c_int(head_dim),
           _c_int(page_table.shape[1]), _c_int(k_cache.shape[0]), _c_int(window), _c_float(scale), _stream())

@@ -287,20 +287,17 @@ def test_attention_decode(H, G, D, splits, window):
     assert (out.float() - twin.float()).abs().max().item() <= 2.0 ** -6
 
 
-@pytest.mark.parametrize("H,G,D", [(6, 2, 48), (4, 4, 16), (8, 1, 32), (32, 8, 128), (8, 2, 64)])
-@pytest.mark.parametrize("window", [0, 70])
-def test_attention_prefill(H, G, D, window):
-    """The tiled bf16 prompt kernel against the float64 formula: sequences of ragged
-    lengths in one launch, some continuing from cached positions, a padding sequence, head
-    groups that do and do not divide the 64-row tile."""
+def run_attention_prefill(H, G, D, window, use_tc, cached, new, q_scale=1.5):
+    """One launch of a prompt kernel over sequences that bring new[s] rows after cached[s]
+    positions (with a padding sequence among them), against the float64 formula at chosen
+    rows and against the one-warp-a-row twin at all rows."""
     from borrowed_compute_b200 import ops
 
-    n_pages = 24
-    cached = [0, 0, 100, 64, 0]            # positions already in the cache before this step
-    new = [1, 130, 30, 65, 300]            # rows this step brings
+    width = max((c + n + 63) // 64 for c, n in zip(cached, new)) + 1
+    n_pages = sum((c + n + 63) // 64 for c, n in zip(cached, new)) + 3
     r = rng(H * 100 + D + 1)
     free = list(r.permutation(n_pages))
-    table = np.full((len(new), 8), -1, dtype=np.int32)
+    table = np.full((len(new), width), -1, dtype=np.int32)
     kp = np.zeros((n_pages, G, 64, D), dtype=np.float32)
     vp = np.zeros_like(kp)
     ks, vs, qs_ = [], [], []
@@ -311,9 +308,9 @@ def test_attention_prefill(H, G, D, window):
         ks.append(k), vs.append(v)
         kp += paged(k, pages, G, D, n_pages, torch.bfloat16)
         vp += paged(v, pages, G, D, n_pages, torch.bfloat16)
-        qs_.append((r.standard_normal((n, H * D)) * 1.5).astype(np.float32))
-    # sequence order in the step: 0, 1, a padding sequence, 2, 3, 4
-    order = [0, 1, -1, 2, 3, 4]
+        qs_.append((r.standard_normal((n, H * D)) * q_scale).astype(np.float32))
+    # sequence order in the step: 0, 1, a padding sequence, then the rest
+    order = [0, 1, -1] + list(range(2, len(new)))
     seq_rows, seq_slot, seq_start, rows = [0], [], [], []
     for s in order:
         n = 0 if s < 0 else new[s]
@@ -327,7 +324,9 @@ def test_attention_prefill(H, G, D, window):
     out = torch.full((total, H * D), 9.0, dtype=torch.bfloat16, device="cuda")
     ops.attention_prefill(dev(q, torch.bfloat16), H * D, dev(kp, torch.bfloat16), dev(vp, torch.bfloat16), dev(table),
                           dev(np.array(seq_rows, dtype=np.int32)), dev(np.array(seq_slot, dtype=np.int32)),
-                          dev(np.array(seq_start, dtype=np.int32)), out, len(order), max(new), H, G, D, window=window)
+                          dev(np.array(seq_start, dtype=np.int32)), out, len(order), max(new), H, G, D, window=window, use_tc=use_tc)
+    if use_tc:
+        assert ops.attention_prefill_tc_status() == 0
     got, qst = f64(out), stored(q, torch.bfloat16)
     at = 0
     for s in order:
@@ -340,13 +339,32 @@ def test_attention_prefill(H, G, D, window):
                                           stored(vs[s][:p + 1], torch.bfloat16), window)
                 assert np.abs(got[at + i].reshape(H, D) - ref).max() <= 2.0 ** -7 * (1 + np.abs(ref).max()), f"sequence {s} row {i}"
         at += new[s]
-    # and every row against the one-warp-a-row twin
     row_slot = np.concatenate([np.full(new[s], s, dtype=np.int32) for s in order if s >= 0])
     row_pos = np.concatenate([np.arange(cached[s], cached[s] + new[s], dtype=np.int32) for s in order if s >= 0])
     twin = torch.empty_like(out)
     ops.attention_rows(dev(q, torch.bfloat16), H * D, dev(kp, torch.bfloat16), dev(vp, torch.bfloat16), dev(table), dev(row_pos),
                        dev(row_slot), twin, H, G, D, window=window)
     assert (out.float() - twin.float()).abs().max().item() <= 2.0 ** -5
+
+
+@pytest.mark.parametrize("H,G,D", [(6, 2, 48), (4, 4, 16), (8, 1, 32), (32, 8, 128), (8, 2, 64)])
+@pytest.mark.parametrize("window", [0, 70])
+def test_attention_prefill(H, G, D, window):
+    """The mma.sync prompt kernel: sequences of ragged lengths in one launch, some
+    continuing from cached positions, a padding sequence, head groups that do and do not
+    divide the 64-row tile."""
+    run_attention_prefill(H, G, D, window, False, cached=[0, 0, 100, 64, 0], new=[1, 130, 30, 65, 300])
+
+
+@pytest.mark.parametrize("H,G,D", [(32, 8, 128), (8, 2, 64), (12, 4, 64), (4, 4, 128), (16, 1, 64), (10, 2, 128)])
+@pytest.mark.parametrize("window", [0, 70, 200])
+@pytest.mark.parametrize("q_scale", [1.5, 8.0])
+def test_attention_prefill_on_tcgen05(H, G, D, window, q_scale):
+    """The tcgen05 prompt kernel at the same workload and a longer one (the ring of pages
+    wraps, both score buffers are reused); head groups of 1, 3, 4, 5 and 16; large scores,
+    so that the running maximum is raised and the accumulator in TMEM rescaled many times."""
+    run_attention_prefill(H, G, D, window, True, cached=[0, 0, 100, 64, 0], new=[1, 130, 30, 65, 300], q_scale=q_scale)
+    run_attention_prefill(H, G, D, window, True, cached=[0, 70, 0, 1000, 63], new=[2, 900, 129, 17, 64], q_scale=q_scale)
 
 
 @pytest.mark.parametrize("H,G,D", [(6, 3, 48), (4, 4, 16), (16, 1, 32), (32, 8, 128), (8, 2, 64)])
