@@ -48,7 +48,14 @@ struct TcParams {
     int stages;
     int k_iters_per_split;
     int clustered;      // split-K: the splits of a tile are one thread-block cluster and add up through shared memory
+    int n_tiles, t_tiles;   // blocks along the weight rows and along the tokens
 };
+
+// Blocks that run at the same time should share operands: the block index walks up to
+// TC_RASTER token tiles first, then the weight tiles, then the next band of token tiles.
+// A wave of 148 blocks then touches about 16 + 9 operand tiles instead of all the weight
+// tiles of one or two token tiles, and each is fetched from HBM once, not once a token tile.
+#define TC_RASTER 16
 
 template <int BN, int EPI, bool STACK>
 __global__ void __launch_bounds__(TC_THREADS, 1)
@@ -71,7 +78,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int stages = p.stages;
-    const int n0 = blockIdx.x * (OUT_TILES * TC_BM), t0 = blockIdx.y * BN;
+    const int band_blocks = TC_RASTER * p.n_tiles;
+    const int band = blockIdx.x / band_blocks, in_band = blockIdx.x - band * band_blocks;
+    const int band_height = min(TC_RASTER, p.t_tiles - band * TC_RASTER);
+    const int tile_n = in_band / band_height, tile_t = band * TC_RASTER + in_band - tile_n * band_height;
+    const int n0 = tile_n * (OUT_TILES * TC_BM), t0 = tile_t * BN;
     const int second_row = EPI == EPI_SWIGLU ? p.up_row_offset + n0 : n0 + TC_BM;   // where the second accumulator's weight rows start
     const int total_k_iters = (p.K + TC_BK - 1) / TC_BK;
     const int k_first = blockIdx.z * p.k_iters_per_split;
@@ -152,7 +163,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         const int q = warp & 3;
         const int n_first = n0 + 32 * q + lane;
         const bool split = gridDim.z > 1;
-        const int tile = blockIdx.y * gridDim.x + blockIdx.x;
+        const int tile = blockIdx.x;
         // Split-K: every split leaves its partial tile in scratch memory; the four row
         // quarters of a tile each have a counter, and the warp that arrives last adds the
         // splits' partials in the order 0, 1, 2 .., so the sum never depends on timing.
@@ -406,7 +417,9 @@ static int launch(const CUtensorMap& mw, const CUtensorMap& mx, TcParams p, int 
         configured = true;
     }
     constexpr int ROWS = TWO_TILES ? 2 * TC_BM : TC_BM;   // output rows a block
-    dim3 grid((p.N + ROWS - 1) / ROWS, (p.T + BN - 1) / BN, splits);
+    p.n_tiles = (p.N + ROWS - 1) / ROWS;
+    p.t_tiles = (p.T + BN - 1) / BN;
+    dim3 grid(p.n_tiles * p.t_tiles, 1, splits);
     // The partial tile of a clustered split lies in the drained ring: N_ACC * 128 * BN floats.
     p.clustered = g_tc_cluster && splits > 1 && splits <= 8 && BN <= 64 && N_ACC * TC_BM * BN * 4 <= stages * STAGE_BYTES;
     if (!p.clustered && splits > 1 && !(p.partial && p.counters)) {
