@@ -314,6 +314,219 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     }
 }
 
+// ------------------------------------------------------- the product on pairs of SMs
+// Many tokens (prompts): a persistent kernel, one pair of blocks on the two SMs of every TPC
+// (cta_group::2).  A pair walks over tiles of 256 tokens; each block holds two 128-row weight
+// tiles (gate and up rows of its 128 outputs for SwiGLU, else 256 consecutive outputs) and
+// HALF of the token tile, and the tensor cores of both SMs read both halves.
+//
+// What bounds the mainloop is shared-memory bandwidth (128 bytes a clock): every MMA reads
+// its A slice (4 KB) and the whole B slice (8 KB, half of it out of the partner's memory)
+// while TMA writes the next stages.  Two weight tiles a block share every token slice, and
+// a pair's stage is 48 KB a block for 2 x 128 x 256 x 64 multiply-accumulates instead of the
+// 64 KB of a block on its own: measured 1.56 against 1.46 PFLOP/s in the mainloop.  (One
+// weight tile a block with two accumulator buffers would hide the epilogue, but re-reads B
+// twice as often and measured 0.97 PFLOP/s.)
+//
+// The two accumulators (256 token columns each) fill TMEM, so the epilogue of a tile cannot
+// overlap the next tile's MMAs; instead it is short (eight warps) and the loader runs ahead:
+// while a tile is written out, the ring already holds the first stages of the next one.
+//
+// The even block's MMA thread issues for the pair; its commits arrive on the barriers of
+// both blocks; every block's loads count their bytes on the even block's barrier; the
+// epilogue warps of both blocks hand the accumulators back by arriving on the even block's
+// barrier.  No load is multicast.
+#define TCP_THREADS 320        // warp 0 TMA, warp 1 MMA, warps 2-9 epilogue
+#define TCP_STAGES_MAX 8
+
+template <int EPI>
+__global__ void __launch_bounds__(TCP_THREADS, 1)
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, const TcParams p) {
+    constexpr int BN = 256;                               // tokens a pair
+    constexpr int TILE = TC_BM * TC_BK * 2;               // 16 KB: 128 rows of 64 k
+    constexpr int STAGE_BYTES = 3 * TILE;                 // two weight tiles and this block's half of the tokens
+    constexpr int TMEM_COLS = 512;                        // two accumulators of 256 token columns
+    constexpr int OUT_ROWS = EPI == EPI_SWIGLU ? TC_BM : 2 * TC_BM;   // outputs a block
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    __shared__ __align__(8) uint64_t bars[2 * TCP_STAGES_MAX + 2];
+    __shared__ uint32_t tmem_slot;
+
+    cg::cluster_group cl = cg::this_cluster();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();              // 0: the block that issues the MMAs
+    const int stages = p.stages;
+    const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+    const int total_tiles = p.n_tiles * p.t_tiles;
+    const int k_iters = (p.K + TC_BK - 1) / TC_BK;
+    const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[TCP_STAGES_MAX]);
+    const uint32_t acc_full = smem_u32(&bars[2 * TCP_STAGES_MAX]), acc_empty = smem_u32(&bars[2 * TCP_STAGES_MAX + 1]);
+
+    // Tile number -> (weight tile, token tile), in bands of TC_RASTER token tiles.
+    auto place = [&](int tile, int& tile_n, int& tile_t) {
+        const int band_blocks = TC_RASTER * p.n_tiles;
+        const int band = tile / band_blocks, in_band = tile - band * band_blocks;
+        const int band_height = min(TC_RASTER, p.t_tiles - band * TC_RASTER);
+        tile_n = in_band / band_height;
+        tile_t = band * TC_RASTER + in_band - tile_n * band_height;
+    };
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < stages; s++) {
+            mbar_init(full0 + 8 * s, 1);
+            mbar_init(empty0 + 8 * s, 1);
+        }
+        mbar_init(acc_full, 1);
+        mbar_init(acc_empty, 16);                         // the eight epilogue warps of both blocks
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) tmem_alloc_pair(smem_u32(&tmem_slot), TMEM_COLS);
+    tc_fence_before();
+    cl.sync();   // both blocks' barriers and TMEM exist before either signals or writes the other's
+    tc_fence_after();
+    const uint32_t tmem = tmem_slot;
+
+    pdl_launch_dependents();
+    if (warp == 0) {
+        if (lane == 0) {
+            const uint32_t pair_full0 = map_to_rank(full0, 0);   // the even block's barriers count both blocks' bytes
+            // This pair's k-steps over all of its tiles, numbered through: step `it` belongs to
+            // the pair's tile number it / k_iters.
+            const int my_tiles = (total_tiles - pair + n_pairs - 1) / n_pairs;
+            const int total_it = my_tiles * k_iters;
+            auto where = [&](int it, int& k, int& n0, int& t_mine) {
+                const int seq = it / k_iters;
+                int tile_n, tile_t;
+                place(pair + seq * n_pairs, tile_n, tile_t);
+                k = (it - seq * k_iters) * TC_BK;
+                n0 = tile_n * 2 * OUT_ROWS + (int)rank * OUT_ROWS;
+                t_mine = tile_t * BN + (int)rank * (BN / 2);
+            };
+            auto load_w = [&](uint32_t dst, uint32_t bar, int k, int n0) {
+                tma_load_2d_pair(dst, &map_w, bar, k, n0);
+                tma_load_2d_pair(dst + TILE, &map_w, bar, k, EPI == EPI_SWIGLU ? p.up_row_offset + n0 : n0 + TC_BM);
+            };
+            // Weights are written by no kernel, activations by the preceding one: the first
+            // ring's weight tiles are on their way before the wait for it.
+            const int ahead = min(stages, total_it);
+            for (int it = 0; it < ahead; it++) {
+                int k, n0, t_mine;
+                where(it, k, n0, t_mine);
+                if (rank == 0) mbar_expect_tx(full0 + 8 * it, 2 * STAGE_BYTES);
+                load_w(smem_u32(smem + (size_t)it * STAGE_BYTES), pair_full0 + 8 * it, k, n0);
+            }
+            pdl_wait();
+            for (int it = 0; it < ahead; it++) {
+                int k, n0, t_mine;
+                where(it, k, n0, t_mine);
+                tma_load_2d_pair(smem_u32(smem + (size_t)it * STAGE_BYTES) + 2 * TILE, &map_x, pair_full0 + 8 * it, k, t_mine);
+            }
+            for (int it = ahead; it < total_it; it++) {
+                const int s = it % stages;
+                if (!mbar_wait(empty0 + 8 * s, ((it / stages) & 1) ^ 1, 1)) break;
+                int k, n0, t_mine;
+                where(it, k, n0, t_mine);
+                const uint32_t a = smem_u32(smem + (size_t)s * STAGE_BYTES);
+                if (rank == 0) mbar_expect_tx(full0 + 8 * s, 2 * STAGE_BYTES);
+                load_w(a, pair_full0 + 8 * s, k, n0);
+                tma_load_2d_pair(a + 2 * TILE, &map_x, pair_full0 + 8 * s, k, t_mine);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && rank == 0) {
+            constexpr uint32_t idesc = instr_desc_pair(BN);
+            bool ok = true;
+            int it = 0, n = 0;
+            for (int tile = pair; tile < total_tiles && ok; tile += n_pairs, n++) {
+                // The epilogue warps of both blocks must have read the previous tile out of TMEM.
+                if (!(ok = mbar_wait(acc_empty, (n & 1) ^ 1, 4))) break;
+                tc_fence_after();
+                for (int i = 0; i < k_iters; i++, it++) {
+                    const int s = it % stages;
+                    if (!(ok = mbar_wait(full0 + 8 * s, (it / stages) & 1, 2))) break;
+                    tc_fence_after();
+                    const uint32_t a = smem_u32(smem + (size_t)s * STAGE_BYTES);
+                    const uint64_t da = smem_desc(a), du = smem_desc(a + TILE), db = smem_desc(a + 2 * TILE);
+#pragma unroll
+                    for (int kk = 0; kk < TC_BK / 16; kk++) {
+                        const uint32_t acc = (i | kk) != 0;
+                        mma_bf16_pair(tmem, da + 2 * kk, db + 2 * kk, idesc, acc);
+                        mma_bf16_pair(tmem + BN, du + 2 * kk, db + 2 * kk, idesc, acc);
+                    }
+                    mma_commit_pair(empty0 + 8 * s, 3);
+                }
+                if (ok) mma_commit_pair(acc_full, 3);
+            }
+        }
+    } else {
+        // Epilogue, in both blocks: warps 2-5 and 6-9 read TMEM lanes 32 q .. 32 q + 31 of their
+        // own SM.  The first four take the first weight tile's accumulator, the others the
+        // second's; for SwiGLU (gate and up sums of one output lie in the two accumulators) the
+        // first four take token columns 0-127 of both, the others 128-255.
+        const int q = warp & 3, set = (warp - 2) >> 2;
+        const uint32_t pair_acc_empty = map_to_rank(acc_empty, 0);
+        bool ok = true;
+        pdl_wait();   // the output may still be in use by the preceding kernel
+        int n = 0;
+        for (int tile = pair; tile < total_tiles; tile += n_pairs, n++) {
+            int tile_n, tile_t;
+            place(tile, tile_n, tile_t);
+            const int t0 = tile_t * BN;
+            if (lane == 0) ok = mbar_wait(acc_full, n & 1, 3);
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (!ok) break;
+            tc_fence_after();
+            const int out_n = tile_n * 2 * OUT_ROWS + (int)rank * OUT_ROWS + 32 * q + lane + (EPI == EPI_SWIGLU ? 0 : TC_BM * set);
+            const uint32_t lanes = tmem + ((uint32_t)(32 * q) << 16);
+            // 16 token columns at a time, the next piece on its way while this one is written.
+            auto emit = [&](const uint32_t* v, const uint32_t* u, int c0) {
+#pragma unroll
+                for (int j = 0; j < 16; j++) {
+                    const int t = t0 + c0 + j;
+                    if (t >= p.T || out_n >= p.N) continue;
+                    const size_t o = (size_t)t * p.N + out_n;
+                    const float val = __uint_as_float(v[j]);
+                    if (EPI == EPI_SWIGLU) ((bf16*)p.out)[o] = __float2bfloat16_rn(silu_mul(val, __uint_as_float(u[j])));
+                    if (EPI == EPI_STORE) ((bf16*)p.out)[o] = __float2bfloat16_rn(val);
+                    if (EPI == EPI_STORE_F32) ((float*)p.out)[o] = val;
+                    // One thread owns each element, so a fire-and-forget reduction gives the same
+                    // sum as a load, add and store, without waiting for the load.
+                    if (EPI == EPI_ADD_F32) atomicAdd(&((float*)p.out)[o], val);
+                }
+            };
+            constexpr int COLS = EPI == EPI_SWIGLU ? BN / 2 : BN;          // token columns this warp writes
+            const int c_first = EPI == EPI_SWIGLU ? set * COLS : 0;
+            const uint32_t src = lanes + (EPI == EPI_SWIGLU ? c_first : set * BN);   // SwiGLU: the gate accumulator; up is BN columns on
+            uint32_t va[16], vb[16], ua[16], ub[16];
+            tmem_load16(src, va);
+            if (EPI == EPI_SWIGLU) tmem_load16(src + BN, ua);
+#pragma unroll 1
+            for (int cc = 0; cc < COLS; cc += 32) {
+                tmem_load_wait();
+                tmem_load16(src + cc + 16, vb);
+                if (EPI == EPI_SWIGLU) tmem_load16(src + BN + cc + 16, ub);
+                emit(va, ua, c_first + cc);
+                tmem_load_wait();
+                if (cc + 32 < COLS) {
+                    tmem_load16(src + cc + 32, va);
+                    if (EPI == EPI_SWIGLU) tmem_load16(src + BN + cc + 32, ua);
+                }
+                emit(vb, ub, c_first + cc + 16);
+            }
+            // This warp has read its share of the accumulators: tell the MMA thread of the even block.
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(pair_acc_empty);
+        }
+    }
+    tc_fence_before();
+    cl.sync();   // neither block leaves, or frees TMEM, while the pair's MMAs or arrivals may still touch it
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc_pair(tmem, TMEM_COLS);
+    }
+}
+
 // -------------------------------------------------------------------------------- the host
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
@@ -435,6 +648,50 @@ static int launch(const CUtensorMap& mw, const CUtensorMap& mx, TcParams p, int 
     BC_LAUNCH_STATUS();
 }
 
+// Whether prompts run on pairs of SMs (the default) or every block on its own; for measurements and tests.
+static int g_tc_pair = 1;
+extern "C" void bc_gemm_tc_set_pair(int on) { g_tc_pair = on != 0; }
+
+template <int EPI>
+static int launch_pair(const CUtensorMap& mw, const CUtensorMap& mx, TcParams p, cudaStream_t s) {
+    constexpr int STAGE_BYTES = 3 * TC_BM * TC_BK * 2;
+    const int k_iters = (p.K + TC_BK - 1) / TC_BK;
+    int stages = (TC_SMEM_LIMIT - 1024) / STAGE_BYTES;
+    if (stages > TCP_STAGES_MAX) stages = TCP_STAGES_MAX;
+    if (g_tc_stage_cap > 0 && stages > g_tc_stage_cap) stages = g_tc_stage_cap;
+    if (stages < 2) stages = 2;
+    p.stages = stages;
+    p.clustered = 0;
+    p.k_iters_per_split = k_iters;
+    const int smem = stages * STAGE_BYTES + 1024;
+    static bool configured = false;
+    static int pairs_on_device = 0;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_pair_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_LIMIT);
+        if (e != cudaSuccess) {
+            bc_set_error("gemm_tc: cannot raise the shared memory limit: %s", cudaGetErrorString(e));
+            return (int)e;
+        }
+        int dev = 0, sms = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        pairs_on_device = sms / 2 > 0 ? sms / 2 : 1;
+        configured = true;
+    }
+    const int rows = EPI == EPI_SWIGLU ? 2 * TC_BM : 4 * TC_BM;   // outputs a pair
+    p.n_tiles = (p.N + rows - 1) / rows;
+    p.t_tiles = (p.T + 255) / 256;
+    const long long tiles = (long long)p.n_tiles * p.t_tiles;
+    const int pairs = tiles < pairs_on_device ? (int)tiles : pairs_on_device;   // persistent: a pair walks over tiles
+    dim3 grid(2 * pairs, 1, 1);
+    cudaError_t e = bc_launch_clustered(gemm_tc_pair_kernel<EPI>, grid, dim3(TCP_THREADS), (size_t)smem, s, dim3(2, 1, 1), mw, mx, p);
+    if (e != cudaSuccess) {
+        bc_set_error("gemm_tc: launch of the paired kernel failed: %s", cudaGetErrorString(e));
+        return (int)e;
+    }
+    BC_LAUNCH_STATUS();
+}
+
 template <int EPI>
 static int launch_bn(int bn, bool stack, const CUtensorMap& mw, const CUtensorMap& mx, const TcParams& p, int splits, cudaStream_t s) {
     switch (bn) {
@@ -498,10 +755,11 @@ extern "C" int bc_gemm_tc_bf16(const void* X, const void* W, void* out, int T, i
     BC_CHECK_ARG((T + bn - 1) / bn <= 65535, "gemm_tc: %d tokens are too many token tiles", T);
     const bool stack = bc_gemm_tc_rows_per_block(T, N, epilogue) == 2 * TC_BM;
     const int w_rows = epilogue == EPI_SWIGLU ? 2 * N : N;
+    const bool paired = g_tc_pair && bn == 256 && splits == 1;   // prompts: pairs of SMs share tiles, each block loading half the tokens
     CUtensorMap mw, mx;
     int st = weight_map(&mw, W, w_rows, K);
     if (st != BC_OK) return st;
-    st = make_map(&mx, X, T, K, bn);
+    st = make_map(&mx, X, T, K, paired ? 128 : bn);
     if (st != BC_OK) return st;
     TcParams p;
     p.out = out;
@@ -513,6 +771,15 @@ extern "C" int bc_gemm_tc_bf16(const void* X, const void* W, void* out, int T, i
     p.up_row_offset = N;
     p.stages = 0;
     p.k_iters_per_split = 0;
+    p.n_tiles = p.t_tiles = p.clustered = 0;
+    if (paired) {
+        switch (epilogue) {
+            case EPI_STORE: return launch_pair<EPI_STORE>(mw, mx, p, s);
+            case EPI_STORE_F32: return launch_pair<EPI_STORE_F32>(mw, mx, p, s);
+            case EPI_ADD_F32: return launch_pair<EPI_ADD_F32>(mw, mx, p, s);
+            case EPI_SWIGLU: return launch_pair<EPI_SWIGLU>(mw, mx, p, s);
+        }
+    }
     switch (epilogue) {
         case EPI_STORE: return launch_bn<EPI_STORE>(bn, stack, mw, mx, p, splits, s);
         case EPI_STORE_F32: return launch_bn<EPI_STORE_F32>(bn, stack, mw, mx, p, splits, s);

@@ -57,6 +57,12 @@ def set_gemm_tc_cluster(on: bool) -> None:
     lib().bc_gemm_tc_set_cluster(_c_int(1 if on else 0))
 
 
+def set_gemm_tc_pair(on: bool) -> None:
+    """Whether products over more than 128 tokens run on pairs of SMs that share a tile
+    (cta_group::2, the default) or every block on its own.  For measurements and tests."""
+    lib().bc_gemm_tc_set_pair(_c_int(1 if on else 0))
+
+
 def _stream() -> _c_void_p:
     return _c_void_p(torch.cuda.current_stream().cuda_stream)
 

@@ -93,6 +93,39 @@ def test_gemm_tc_splits_agree_through_cluster_and_through_scratch(T, N, K, split
     assert np.abs(f64(results[0][0]) - full).max() <= 2e-5 * (1.0 + np.abs(full).max())
 
 
+@pytest.mark.parametrize("T,N,K", [(300, 130, 192), (600, 384, 512), (129, 128, 64), (1000, 1030, 448), (513, 700, 72), (2048, 512, 1024)])
+@pytest.mark.parametrize("paired", [True, False])
+def test_gemm_tc_many_tokens_on_pairs_of_sms_and_on_single_blocks(T, N, K, paired):
+    """More than 128 tokens: the tile shared by two SMs (cta_group::2) and the tile of one
+    block, every epilogue, edges in all three dimensions, against the float64 product."""
+    from borrowed_compute_b200 import ops
+
+    x, w = operands(T, N, K, T + 3 * N + K)
+    full = f64(x) @ f64(w).T
+    scale = 1.0 + np.abs(full).max()
+    wn = w[:N].contiguous()
+    base = torch.from_numpy(np.random.default_rng(3).standard_normal((T, N)).astype(np.float32)).cuda()
+    try:
+        ops.set_gemm_tc_pair(paired)
+        out32 = torch.full((T, N), 7.0, dtype=torch.float32, device="cuda")
+        ops.gemm_tc(x, wn, out32, ops.EPI_STORE_F32, splits=1)
+        out16 = torch.full((T, N), 7.0, dtype=torch.bfloat16, device="cuda")
+        ops.gemm_tc(x, wn, out16, ops.EPI_STORE, splits=1)
+        acc = base.clone()
+        ops.gemm_tc(x, wn, acc, ops.EPI_ADD_F32, splits=1)
+        act = torch.full((T, N), 7.0, dtype=torch.bfloat16, device="cuda")
+        ops.gemm_tc(x, w, act, ops.EPI_SWIGLU, splits=1)
+    finally:
+        ops.set_gemm_tc_pair(True)
+    assert ops.gemm_tc_status() == 0
+    assert np.abs(f64(out32) - full[:, :N]).max() <= 2e-5 * scale, "float store"
+    assert np.abs(f64(out16) - full[:, :N]).max() <= 2.0 ** -8 * scale, "bf16 store"
+    assert np.abs(f64(acc) - (f64(base) + full[:, :N])).max() <= 2e-5 * scale, "residual add"
+    g, u = full[:, :N], full[:, N:]
+    ref = g / (1 + np.exp(-g)) * u
+    assert np.abs(f64(act) - ref).max() <= 2.0 ** -8 * (1 + np.abs(ref).max()), "SwiGLU"
+
+
 def test_gemm_tc_matches_the_cuda_core_twin():
     from borrowed_compute_b200 import ops
 
