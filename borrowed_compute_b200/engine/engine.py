@@ -49,17 +49,32 @@ class _DecodeGraph:
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.scores: Optional[torch.Tensor] = None
 
-    def _fill(self, plan: StepPlan) -> None:
-        rows, n = self.rows, plan.seqs
-        seq_rows = np.full(rows + 1, plan.rows, dtype=np.int32)
-        seq_rows[: n + 1] = plan.seq_rows
-        seq_slot = np.full(rows, -1, dtype=np.int32)
-        seq_slot[:n] = plan.seq_slot
-        seq_start = np.zeros(rows, dtype=np.int32)
-        seq_start[:n] = plan.seq_start
-        packed = np.concatenate([plan.tokens, plan.row_pos, plan.row_slot, seq_rows, seq_slot, seq_start, np.arange(rows, dtype=np.int32)])
+    def pack(self, tokens, row_pos, row_slot, rows_used: int) -> np.ndarray:
+        """The step's integers in the layout of ``sizes``: one row a sequence, padding rows
+        (slot -1) after them.  ``tokens`` may be None and filled into [:rows_used] later."""
+        rows, n = self.rows, rows_used
+        out = np.zeros(sum(size for _, size in self.sizes), dtype=np.int32)
+        at = {}
+        o = 0
+        for name, size in self.sizes:
+            at[name] = o
+            o += size
+        if tokens is not None:
+            out[at["tokens"]:at["tokens"] + n] = tokens
+        out[at["row_pos"]:at["row_pos"] + n] = row_pos
+        out[at["row_slot"]:at["row_slot"] + rows] = -1
+        out[at["row_slot"]:at["row_slot"] + n] = row_slot
+        out[at["seq_rows"]:at["seq_rows"] + rows + 1] = n
+        out[at["seq_rows"]:at["seq_rows"] + n + 1] = np.arange(n + 1, dtype=np.int32)
+        out[at["seq_slot"]:at["seq_slot"] + rows] = -1
+        out[at["seq_slot"]:at["seq_slot"] + n] = row_slot
+        out[at["seq_start"]:at["seq_start"] + n] = row_pos
+        out[at["want_rows"]:at["want_rows"] + rows] = np.arange(rows, dtype=np.int32)
+        return out
+
+    def _upload(self, packed: np.ndarray) -> None:
         if self.copied is not None:
-            self.copied.synchronize()
+            self.copied.synchronize()   # the last copy out of the pinned buffer is done
         self.host.copy_(torch.from_numpy(packed))
         self.ints.copy_(self.host, non_blocking=True)
         if self.copied is None:
@@ -73,8 +88,8 @@ class _DecodeGraph:
                           extras={"graph": True})
         return self.engine.model.forward(ctx, self.engine.cache, v["want_rows"], rows)
 
-    def run(self, plan: StepPlan) -> torch.Tensor:
-        self._fill(plan)
+    def run(self, packed: np.ndarray) -> torch.Tensor:
+        self._upload(packed)
         if self.graph is None:
             self._forward()   # once eagerly: first-use set-up must not happen inside a capture
             torch.cuda.synchronize()
@@ -84,6 +99,15 @@ class _DecodeGraph:
             self.graph = graph
         self.graph.replay()
         return self.scores
+
+
+class _Ahead:
+    """The next decode step of the same sequences, staged on the host while the device
+    still runs the current one: slots reserved, page tables sent, every integer of the
+    step but the tokens."""
+
+    def __init__(self, slots, starts, graph: _DecodeGraph, packed: np.ndarray):
+        self.slots, self.starts, self.graph, self.packed = tuple(slots), list(starts), graph, packed
 
 
 class Engine:
@@ -98,6 +122,7 @@ class Engine:
         self._host_ints: Optional[torch.Tensor] = None
         self._staged: Optional[torch.cuda.Event] = None
         self._graphs: Dict[int, "_DecodeGraph"] = {}
+        self._ahead: Optional[_Ahead] = None
         # Decode steps replay a captured CUDA graph unless a part plans on the host.
         self.use_graphs = all(part.graph_safe for _, part in model._named_parts())
         self.steps_run = 0
@@ -179,6 +204,7 @@ class Engine:
 
     def release(self, slot: int) -> None:
         """Gives a sequence's slot and pages back."""
+        self._ahead = None
         self.cache.release(slot)
 
     def length(self, slot: int) -> int:
@@ -186,6 +212,7 @@ class Engine:
 
     def rollback(self, slot: int, length: int) -> None:
         """Cuts a sequence back to ``length`` positions; the next step writes from there."""
+        self._ahead = None
         self.cache.slots.rollback(slot, length)
 
     # -------------------------------------------------------------------------------- step
@@ -235,33 +262,69 @@ class Engine:
             b *= 2
         return b if n <= 16 else -(-n // 16) * 16
 
-    def _decode_graph_step(self, entries: Sequence[StepEntry], starts: Sequence[int]) -> torch.Tensor:
-        """A step of one token a sequence, replayed from a CUDA graph captured once per
-        padded batch size: the kernels, their order and their buffers are fixed, only the
-        integers that name tokens, positions and slots change."""
-        n = len(entries)
+    def _graph_for(self, n: int) -> _DecodeGraph:
         bucket = self._bucket(n)
         g = self._graphs.get(bucket)
         if g is None:
             g = self._graphs[bucket] = _DecodeGraph(self, bucket)
-        plan = plan_step(entries, starts, pad_rows_to=bucket)
-        return g.run(plan)[:n]
+        return g
+
+    def _decode_graph_step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        """A step of one token a sequence, replayed from a CUDA graph captured once per
+        padded batch size: the kernels, their order and their buffers are fixed, only the
+        integers that name tokens, positions and slots change.
+
+        While the device runs the step, the host stages the next one for the same
+        sequences (their slots' next position reserved, page tables sent, all integers
+        but the tokens packed); if the next call brings exactly these sequences, only
+        their tokens are filled in before the launch.  Anything else (a sequence ended,
+        another joined, a rollback) takes the ordinary way."""
+        n = len(entries)
+        slots = tuple(e.slot for e in entries)
+        ahead, self._ahead = self._ahead, None
+        tokens = [int(e.tokens[0]) for e in entries]
+        if ahead is not None and ahead.slots == slots and all(self.cache.slots.length(s) == p for s, p in zip(slots, ahead.starts)):
+            for t in tokens:
+                if not 0 <= t < self.vocab_size:
+                    raise ValueError(f"token {t} is outside the vocabulary")
+            starts, g, packed = ahead.starts, ahead.graph, ahead.packed
+            packed[:n] = tokens
+        else:
+            starts = self.check_entries(entries)
+            for slot, start in zip(slots, starts):
+                self.cache.slots.reserve(slot, start + 1, rows=1)
+            g = self._graph_for(n)
+            packed = g.pack(tokens, starts, slots, n)
+        self.cache.sync_tables()
+        scores = g.run(packed)[:n]
+        for slot, start in zip(slots, starts):
+            self.cache.slots.commit(slot, start + 1)
+        self.steps_run += 1
+        # The device is busy now: stage the step after this one.
+        try:
+            nxt = [start + 1 for start in starts]
+            if max(nxt) + 1 <= self.max_seq:
+                for slot, start in zip(slots, nxt):
+                    self.cache.slots.reserve(slot, start + 1, rows=1)
+                self.cache.sync_tables()
+                self._ahead = _Ahead(slots, nxt, g, g.pack(None, nxt, slots, n))
+        except CacheError:
+            self._ahead = None   # the step itself will say what is wrong, if it comes
+        return scores
 
     def step(self, entries: Sequence[StepEntry], pad_rows_to: int = 1) -> torch.Tensor:
         """Runs the given tokens of every entry as one batch from the cache and returns
         the scores [wanted, vocab] (float32, on the device) at the wanted places, in entry
         order then ``want`` order.  ``pad_rows_to`` adds rows that belong to no sequence;
         they change no result."""
+        if self.use_graphs and pad_rows_to == 1 and entries and all(len(e.tokens) == 1 and tuple(e.want) == (0,) for e in entries) \
+                and len({e.slot for e in entries}) == len(entries):
+            return self._decode_graph_step(entries)
+        self._ahead = None
         starts = self.check_entries(entries)
         for e, start in zip(entries, starts):
             self.cache.slots.reserve(e.slot, start + len(e.tokens), rows=len(e.tokens))
         self.cache.sync_tables()
-        if self.use_graphs and pad_rows_to == 1 and all(len(e.tokens) == 1 and tuple(e.want) == (0,) for e in entries):
-            scores = self._decode_graph_step(entries, starts)
-            for e, start in zip(entries, starts):
-                self.cache.slots.commit(e.slot, start + 1)
-            self.steps_run += 1
-            return scores
         plan = plan_step(entries, starts, pad_rows_to)
         v = self._stage(plan)
         ctx = StepContext(

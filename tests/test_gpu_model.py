@@ -180,6 +180,55 @@ def test_float32_cuts_agree_to_the_bit(engines, name):
     assert np.array_equal(np.concatenate([first] + rest), whole)
 
 
+@pytest.mark.parametrize("name,dtype", [("A", "float32"), ("B", "bfloat16")])
+def test_decode_steps_staged_ahead_and_every_way_out_of_them(engines, name, dtype):
+    """After a decode step the engine stages the next one for the same sequences.  The
+    staged step is used when exactly they come again, and dropped when they come in another
+    order, when one of them has ended and its slot is taken by a new sequence, or after a
+    cut back; the scores match the plain implementation every time."""
+    from borrowed_compute_b200.engine import StepEntry
+
+    eng, cfg, weights = engines(name, dtype)
+    assert eng.use_graphs
+    V = cfg["vocab_size"]
+    seqs = [seeded_tokens(300 + i, n, V) for i, n in enumerate([70, 9, 63, 30])]
+    held = [3, 2, 3, 5]          # tokens of each sequence that its prompt step takes
+    slots = [eng.acquire() for _ in seqs]
+    eng.step([StepEntry(s, t[:h], want=()) for s, t, h in zip(slots, seqs, held)])
+    at = list(held)
+
+    def decode(order):
+        scores = eng.step([StepEntry(slots[i], (seqs[i][at[i]],), want=(0,)) for i in order]).float().cpu().numpy()
+        for row, i in zip(scores, order):
+            close(row, plain(name, dtype, cfg, weights, seqs[i][:at[i] + 1])[-1], dtype, f"sequence {i} position {at[i]}")
+            at[i] += 1
+
+    decode([0, 1, 2, 3])
+    assert eng._ahead is not None
+    decode([0, 1, 2, 3])                  # the staged step
+    decode([0, 1, 2, 3])
+    decode([3, 2, 1, 0])                  # another order: not the staged step
+    decode([3, 2, 1, 0])
+    decode([0, 2])                        # fewer sequences
+    decode([0, 2])
+    eng.release(slots[1])                 # a sequence ends, a new one takes its slot
+    seqs[1] = seeded_tokens(400, 40, V)
+    slots[1] = eng.acquire()
+    eng.step([StepEntry(slots[1], seqs[1][:4], want=())])
+    at[1] = 4
+    decode([0, 1, 2, 3])
+    decode([0, 1, 2, 3])
+    eng.rollback(slots[3], at[3] - 2)     # a cut back between two steps of the same sequences
+    at[3] -= 2
+    assert eng._ahead is None
+    decode([0, 1, 2, 3])
+    for _ in range(6):                    # sequence 2 crosses a page edge on staged steps
+        decode([0, 1, 2, 3])
+    for s in slots:
+        eng.release(s)
+    eng.cache.slots.check()
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_going_back_reproduces(engines, dtype):
     """Re-running a position after cutting the cache back gives the same scores again
