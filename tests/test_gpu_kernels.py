@@ -238,6 +238,54 @@ def test_attention_finds_one_far_key(dtype):
             assert np.abs(f64(out).reshape(H, D) - want).max() > 0.05, f"window {outside} must not see position {far}"
 
 
+@pytest.mark.parametrize("kernel", ["decode_cluster", "decode_scratch", "decode_many_splits", "prefill_mma", "prefill_tcgen05"])
+@pytest.mark.parametrize("D", [64, 128])
+def test_tensor_core_attention_finds_one_far_key_and_keeps_every_rows_window(kernel, D):
+    """The tiled bf16 kernels against planted keys: one key among 700 matches every query, so
+    a row's output is that position's value exactly when the row may see it: not before its
+    own position reaches it (the causal edge, row by row), and no longer once it has left
+    the row's window (the window's edge, row by row).  Wherever the key lies: first and last
+    position of a page, of the cached part, of the new rows."""
+    from borrowed_compute_b200 import ops
+
+    H, G, n_pages, T, cached, window = 4, 2, 14, 700, 200, 130
+    table = np.array([[9, 1, 12, 4, 2, 7, 0, 11, 5, 13, 3]], dtype=np.int32)
+    q_row = np.zeros(H * D, dtype=np.float32)
+    for h in range(H):
+        q_row[h * D + 3] = 4.0
+    for far in (0, 63, 64, 199, 200, 201, 447, 448, 640, 698, 699):
+        k = np.zeros((T, G, D), dtype=np.float32)
+        v = rng(far).standard_normal((T, G, D)).astype(np.float32)
+        k[far, :, 3] = 100.0
+        kp, vp = dev(paged(k, table[0], G, D, n_pages, torch.bfloat16), torch.bfloat16), dev(paged(v, table[0], G, D, n_pages, torch.bfloat16), torch.bfloat16)
+        want = np.repeat(stored(v[far], torch.bfloat16), H // G, axis=0)     # [H, D]: every head of a kv head finds its value
+        for w in (0, window):
+            if kernel.startswith("decode"):
+                rows = [p for p in (far - 1, far, far + 1, far + window - 1, far + window, T - 1) if 0 <= p < T]
+                q = dev(np.tile(q_row, (len(rows), 1)), torch.bfloat16)
+                out = torch.empty((len(rows), H * D), dtype=torch.bfloat16, device="cuda")
+                splits = {"decode_cluster": 4, "decode_scratch": 4, "decode_many_splits": 11}[kernel]
+                ops.attention_decode(q, H * D, kp, vp, dev(table), dev(np.array(rows, dtype=np.int32)), dev(np.zeros(len(rows), dtype=np.int32)),
+                                     out, H, G, D, window=w, splits=splits, via_scratch=kernel == "decode_scratch")
+                got = {p: f64(out[i]).reshape(H, D) for i, p in enumerate(rows)}
+            else:
+                new = T - cached
+                q = dev(np.tile(q_row, (new, 1)), torch.bfloat16)
+                out = torch.empty((new, H * D), dtype=torch.bfloat16, device="cuda")
+                ops.attention_prefill(q, H * D, kp, vp, dev(table), dev(np.array([0, new], dtype=np.int32)), dev(np.array([0], dtype=np.int32)),
+                                      dev(np.array([cached], dtype=np.int32)), out, 1, new, H, G, D, window=w, use_tc=kernel == "prefill_tcgen05")
+                if kernel == "prefill_tcgen05":
+                    assert ops.attention_prefill_tc_status() == 0
+                got = {p: f64(out[p - cached]).reshape(H, D) for p in range(cached, T)}
+            for p, o in got.items():
+                sees = far <= p and (w == 0 or far >= p - w + 1)
+                err = np.abs(o - want).max()
+                if sees:
+                    assert err <= 2.0 ** -7, f"{kernel}: the row at {p} (window {w}) did not find the key at {far}"
+                elif p > 0:
+                    assert err > 0.05, f"{kernel}: the row at {p} (window {w}) must not see the key at {far}"
+
+
 @pytest.mark.parametrize("H,G,D", [(6, 3, 48), (4, 4, 16), (16, 1, 32), (32, 8, 128), (8, 2, 64)])
 @pytest.mark.parametrize("splits", [1, 3, 8, 11])
 @pytest.mark.parametrize("window", [0, 70])
