@@ -39,14 +39,17 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ int is_last;
 
+    // Slots, positions and page tables are in place before the step starts, and the pages read
+    // here were written by earlier steps: the first pages are asked for before the wait for
+    // the preceding kernel (which makes this row's q, k and v).  Nothing is written before it.
     pdl_launch_dependents();
-    pdl_wait();
     const int split = blockIdx.x, n_splits = gridDim.x, g = blockIdx.y, r = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int gq = lane >> 2, tq = lane & 3;
     const int group = H / G;
     const int slot = row_slot[r];
     if (slot < 0) {
+        pdl_wait();
         if (split == 0)
             for (int i = threadIdx.x; i < group * D; i += AD_THREADS) out[((size_t)r * H + (size_t)g * group) * D + i] = __float2bfloat16_rn(0.0f);
         return;
@@ -73,17 +76,17 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __
         }
     };
 
-    // The first pages are asked for at once, before the query is fetched and rotated; only the
-    // block that appends this row's key and value must write them before it reads their page.
+    // The first pages are asked for at once, before the wait and before the query is fetched
+    // and rotated.  Only the row's own page (the last one of the last split) must wait: this
+    // step writes the row's key and value into it, this block (fuse 2) or a kernel before it.
     const bool appends = fuse == 2 && n_tiles > 0 && t_end == end_tile;
-    auto prefetch_first = [&]() {
-#pragma unroll
-        for (int s = 0; s < AD_STAGES - 1; s++) {
-            if (s < n_tiles) load_tile(t_begin + s, s);
-            cp_async_commit();
-        }
-    };
-    if (!appends) prefetch_first();
+    int asked = 0;   // stages of the first ring asked for so far, in order
+    for (; asked < AD_STAGES - 1; asked++) {
+        if (t_begin + asked == end_tile - 1) break;
+        if (asked < n_tiles) load_tile(t_begin + asked, asked);
+        cp_async_commit();
+    }
+    pdl_wait();
 
     // Q fragments: row i of the tile is head g * group + i (zero past the group).
     uint32_t qf[KD][4];
@@ -161,7 +164,10 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __
         }
         __threadfence();
         __syncthreads();
-        prefetch_first();
+    }
+    for (; asked < AD_STAGES - 1; asked++) {
+        if (asked < n_tiles) load_tile(t_begin + asked, asked);
+        cp_async_commit();
     }
 
     float o[ND][4];
