@@ -34,7 +34,7 @@ attention_prefill_kernel(const bf16* __restrict__ q, int q_stride, const bf16* _
 
     pdl_launch_dependents();
     pdl_wait();
-    const int g = blockIdx.y, sq = blockIdx.z;
+    const int g = blockIdx.x, sq = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int gq = lane >> 2, tq = lane & 3;
     const int group = H / G;
@@ -42,8 +42,9 @@ attention_prefill_kernel(const bf16* __restrict__ q, int q_stride, const bf16* _
     const int slot = seq_slot[sq];
     const int row0 = seq_rows[sq], n_new = seq_rows[sq + 1] - row0;
     const int n_tiles_q = (n_new + tokens_per_tile - 1) / tokens_per_tile;
-    // The last query tiles see the most keys: they go first.
-    const int q_tile = n_tiles_q - 1 - (int)blockIdx.x;
+    // The last query tiles see the most keys: they go first, for all kv heads (x runs fastest),
+    // so that the blocks start in the order of their work.
+    const int q_tile = n_tiles_q - 1 - (int)blockIdx.y;
     if (slot < 0 || q_tile < 0) return;
     const int start = seq_start[sq];
     const int tok0 = q_tile * tokens_per_tile;            // first token (within the step) of this tile
@@ -217,7 +218,7 @@ static int launch(const void* q, int q_stride, const void* k_cache, const void* 
         configured = true;
     }
     const int tokens_per_tile = AP_ROWS / (H / G);
-    dim3 grid((max_new + tokens_per_tile - 1) / tokens_per_tile, G, seqs);
+    dim3 grid(G, (max_new + tokens_per_tile - 1) / tokens_per_tile, seqs);
     bc_launch(attention_prefill_kernel<D>, grid, dim3(AP_THREADS), (size_t)SMEM, s, (const bf16*)q, q_stride, (const bf16*)k_cache,
               (const bf16*)v_cache, page_table, seq_rows, seq_slot, seq_start, (bf16*)out, H, G, max_pages, n_pages, window,
               scale * 1.4426950408889634f);
@@ -236,7 +237,7 @@ extern "C" int bc_attention_prefill_accepts(int H, int G, int D) {
 extern "C" int bc_attention_prefill_bf16(const void* q, int q_stride, const void* k_cache, const void* v_cache, const int* page_table,
                                          const int* seq_rows, const int* seq_slot, const int* seq_start, void* out, int seqs, int max_new,
                                          int H, int G, int D, int max_pages, int n_pages, int window, float scale, cudaStream_t s) {
-    BC_CHECK_ARG(seqs >= 0 && seqs <= 65535 && max_new >= 0, "attention_prefill: bad sizes seqs=%d max_new=%d", seqs, max_new);
+    BC_CHECK_ARG(seqs >= 0 && seqs <= 65535 && max_new >= 0 && max_new < 65535, "attention_prefill: bad sizes seqs=%d max_new=%d", seqs, max_new);
     BC_CHECK_ARG(bc_attention_prefill_accepts(H, G, D), "attention_prefill: H=%d G=%d D=%d is outside what this kernel takes "
                  "(at most %d heads a kv head, head size a multiple of 16 up to 128)", H, G, D, AP_ROWS);
     BC_CHECK_ARG(q_stride % 2 == 0 && ((uintptr_t)q % 4 == 0) && ((uintptr_t)out % 4 == 0), "attention_prefill: q and out must be 4-byte aligned");

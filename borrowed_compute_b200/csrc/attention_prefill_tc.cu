@@ -4,8 +4,8 @@
 // the running maximum / sum of its kernel (crates/bc-infer/src/gpu/kernels.h:271-324); how
 // it is laid out is Blackwell's own:
 //
-//   - A block takes 128 query rows = (tokens) x (the heads that share one kv head), token
-//     major, of one sequence.  Q comes by one 3-d TMA box per 64 elements of the head size
+//   - A block takes one or two tiles of 128 query rows = (tokens) x (the heads that share one
+//     kv head), token major, of one sequence.  Q comes by one 3-d TMA box per 64 elements of the head size
 //     straight out of the fused projection [row][head][d]; every 64-position page of keys
 //     and values comes by 2-d TMA boxes from the paged cache into a ring of stages.  All
 //     tiles are 128-byte-swizzled blocks of [rows][64 elements].
@@ -24,8 +24,8 @@
 //     store) a few times a block instead of once a page.  Sums and outputs use the same
 //     maximum, so the result is the softmax all the same.
 //
-// Warp roles: warp 0 issues TMA, warp 1 owns TMEM and issues the MMAs, warps 2-5 are the
-// softmax and write the output.  Every wait is bounded (about a second); a wait that gives
+// Warp roles: warp 0 issues TMA, warp 1 owns TMEM and issues the MMAs, warps 2-5 (and 6-9 for
+// the second query tile) are the softmax and write the output.  Every wait is bounded (about a second); a wait that gives
 // up records where in a status word, and the block frees its TMEM and returns.
 #include <mutex>
 #include <unordered_map>
@@ -33,71 +33,95 @@
 #include "mma_tiles.cuh"
 #include "tc_ptx.cuh"
 
-#define APT_THREADS 192
-#define APT_ROWS 128
-#define APT_STAGES 4
+#define APT_ROWS 128        // query rows of one tile: the M of the MMAs, the lanes of TMEM
+#define APT_PAGES_KEPT 256
 #define APT_RAISE 8.0f      // the running maximum follows the true one at this distance at most
 
-template <int D>
-__global__ void __launch_bounds__(APT_THREADS, 1)
+// NT query tiles a block (1 or 2).  Two tiles share every page of keys and values, and their
+// two groups of softmax warps give every SM sub-partition two warps to switch between while
+// one waits for TMEM, a fence or a barrier: with one tile the softmax warps, one a
+// sub-partition, are the kernel's limit.  One tile serves steps with few new rows.
+template <int D, int NT>
+__global__ void __launch_bounds__(64 + NT * 128, 1)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                             const __grid_constant__ CUtensorMap map_v, const int* __restrict__ page_table, const int* __restrict__ seq_rows,
                             const int* __restrict__ seq_slot, const int* __restrict__ seq_start, bf16* __restrict__ out, int H, int G,
                             int max_pages, int n_pages, int window, float scale_log2) {
+    constexpr int THREADS = 64 + NT * 128;
+    constexpr int STAGES = (D == 128 && NT == 2) ? 3 : 4;
     constexpr int DB = D / 64;                         // 64-element blocks of the head size
     constexpr int ROW_BLOCK = APT_ROWS * 128;          // bytes of a [128 rows][64 elements] block
     constexpr int KV_BLOCK = BC_PAGE * 128;            // bytes of a [64 positions][64 elements] block
-    constexpr int Q_BYTES = DB * ROW_BLOCK;
+    constexpr int Q_BYTES = DB * NT * ROW_BLOCK;       // per 64 elements: the rows of all tiles, one after another
     constexpr int STAGE_BYTES = 2 * DB * KV_BLOCK;     // keys, then values, of one page
-    constexpr int S_COL = 0, O_COL = 128;              // TMEM columns: scores 0-63 and 64-127, output from 128
-    constexpr int TMEM_COLS = 256;
+    constexpr int O_COL = NT * 128;                    // TMEM columns: scores of (tile t, buffer b) from (2 t + b) 64, outputs from O_COL + t D
+    constexpr int TMEM_COLS = NT == 1 ? 256 : 512;
     static_assert(D == 64 || D == 128, "head size 64 or 128");
+    static_assert(NT == 1 || NT == 2, "one or two query tiles");
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* q_smem = smem;
-    uint8_t* p_smem = q_smem + Q_BYTES;                // two P tiles
-    uint8_t* kv_smem = p_smem + 2 * ROW_BLOCK;
-    __shared__ __align__(8) uint64_t bars[2 * APT_STAGES + 6];
+    uint8_t* p_smem = q_smem + Q_BYTES;                // P of (tile t, buffer b) at (2 t + b) ROW_BLOCK
+    uint8_t* kv_smem = p_smem + NT * 2 * ROW_BLOCK;
+    __shared__ __align__(8) uint64_t bars[2 * STAGES + 1 + 6 * NT];
     __shared__ uint32_t tmem_slot;
+    __shared__ int page_of[APT_PAGES_KEPT];   // the first pages this block reads, fetched once (-1: none)
 
     pdl_launch_dependents();
     pdl_wait();
-    const int g = blockIdx.y, sq = blockIdx.z;
+    const int g = blockIdx.x, sq = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int group = H / G;
-    const int tokens_per_tile = APT_ROWS / group;         // rows past tokens_per_tile * group are padding
+    const int tokens_per_block = NT * APT_ROWS / group;   // rows past tokens_per_block * group are padding
     const int slot = seq_slot[sq];
     const int row0 = seq_rows[sq], n_new = seq_rows[sq + 1] - row0;
-    const int n_tiles_q = (n_new + tokens_per_tile - 1) / tokens_per_tile;
-    // The last query tiles see the most keys: they go first.
-    const int q_tile = n_tiles_q - 1 - (int)blockIdx.x;
-    if (slot < 0 || q_tile < 0) return;                   // the whole block, before anything is set up
+    const int n_blocks_q = (n_new + tokens_per_block - 1) / tokens_per_block;
+    // The last query rows see the most keys: they go first, for all kv heads (x runs fastest),
+    // so that the blocks start in the order of their work.
+    const int q_block = n_blocks_q - 1 - (int)blockIdx.y;
+    if (slot < 0 || q_block < 0) return;                  // the whole block, before anything is set up
     const int start = seq_start[sq];
-    const int tok0 = q_tile * tokens_per_tile;
-    const int tok_end = min(n_new, tok0 + tokens_per_tile);
+    const int tok0 = q_block * tokens_per_block;
+    const int tok_end = min(n_new, tok0 + tokens_per_block);
     const int* pages = page_table + (size_t)slot * max_pages;
-    // Pages this tile reads: from the first position its first token sees to its last token's own.
+    // Pages this block reads: from the first position its first token sees to its last token's own.
     const int first_pos = window > 0 && start + tok0 + 1 > window ? start + tok0 + 1 - window : 0;
     const int t_begin = first_pos / BC_PAGE, t_end = (start + tok_end - 1) / BC_PAGE + 1;
     const int n_tiles = t_end - t_begin;
 
-    const uint32_t kv_full0 = smem_u32(&bars[0]), kv_empty0 = smem_u32(&bars[APT_STAGES]);
-    const uint32_t q_full = smem_u32(&bars[2 * APT_STAGES]), s_full0 = smem_u32(&bars[2 * APT_STAGES + 1]);
-    const uint32_t p_full0 = smem_u32(&bars[2 * APT_STAGES + 3]), o_bar = smem_u32(&bars[2 * APT_STAGES + 5]);
+    const uint32_t kv_full0 = smem_u32(&bars[0]), kv_empty0 = smem_u32(&bars[STAGES]), q_full = smem_u32(&bars[2 * STAGES]);
+    // Per query tile t and buffer b: scores ready, P written, product done.
+    auto s_full = [&](int t, int b) { return smem_u32(&bars[2 * STAGES + 1 + 6 * t + b]); };
+    auto p_full = [&](int t, int b) { return smem_u32(&bars[2 * STAGES + 1 + 6 * t + 2 + b]); };
+    auto o_done = [&](int t, int b) { return smem_u32(&bars[2 * STAGES + 1 + 6 * t + 4 + b]); };
     if (threadIdx.x == 0) {
-        for (int s = 0; s < APT_STAGES; s++) {
+        for (int s = 0; s < STAGES; s++) {
             mbar_init(kv_full0 + 8 * s, 1);
             mbar_init(kv_empty0 + 8 * s, 1);
         }
         mbar_init(q_full, 1);
-        mbar_init(s_full0, 1);
-        mbar_init(s_full0 + 8, 1);
-        mbar_init(p_full0, 128);
-        mbar_init(p_full0 + 8, 128);
-        mbar_init(o_bar, 1);
+        for (int t = 0; t < NT; t++)
+            for (int b = 0; b < 2; b++) {
+                mbar_init(s_full(t, b), 1);
+                mbar_init(p_full(t, b), 128);
+                // The products of even pages arrive on the first, of odd pages on the second: a
+                // waiter is then never more than one phase behind either of them.
+                mbar_init(o_done(t, b), 1);
+            }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) tmem_alloc(smem_u32(&tmem_slot), TMEM_COLS);
+    for (int i = threadIdx.x; i < min(n_tiles, APT_PAGES_KEPT); i += THREADS) {
+        const int tile = t_begin + i;
+        const int page = tile < max_pages ? pages[tile] : -1;
+        page_of[i] = page >= 0 && page < n_pages ? page : -1;
+    }
+    auto page_at = [&](int j) {   // the page of this block's j-th tile, or -1
+        if (j < APT_PAGES_KEPT) return page_of[j];
+        const int tile = t_begin + j;
+        const int page = tile < max_pages ? pages[tile] : -1;
+        return page >= 0 && page < n_pages ? page : -1;
+    };
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -106,14 +130,13 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     if (warp == 0) {
         if (lane == 0) {
             // Q: one box [tokens][heads of the group][64 elements] per 64 elements of the head size.
-            mbar_expect_tx(q_full, (uint32_t)(DB * tokens_per_tile * group * 128));
-            for (int b = 0; b < DB; b++) tma_load_3d(smem_u32(q_smem + b * ROW_BLOCK), &map_q, q_full, b * 64, g * group, row0 + tok0);
+            mbar_expect_tx(q_full, (uint32_t)(DB * tokens_per_block * group * 128));
+            for (int b = 0; b < DB; b++) tma_load_3d(smem_u32(q_smem + b * NT * ROW_BLOCK), &map_q, q_full, b * 64, g * group, row0 + tok0);
             for (int j = 0; j < n_tiles; j++) {
-                const int s = j % APT_STAGES;
-                if (j >= APT_STAGES && !mbar_wait(kv_empty0 + 8 * s, ((j / APT_STAGES) & 1) ^ 1, 1)) break;
-                const int tile = t_begin + j;
-                int page = tile < max_pages ? pages[tile] : -1;
-                if (page < 0 || page >= n_pages) page = 0;   // never used: every position of such a tile is masked
+                const int s = j % STAGES;
+                if (j >= STAGES && !mbar_wait(kv_empty0 + 8 * s, ((j / STAGES) & 1) ^ 1, 1)) break;
+                int page = page_at(j);
+                if (page < 0) page = 0;   // never used: every position of such a tile is masked
                 const int y = (page * G + g) * BC_PAGE;
                 const uint32_t dst = smem_u32(kv_smem + (size_t)s * STAGE_BYTES);
                 mbar_expect_tx(kv_full0 + 8 * s, STAGE_BYTES);
@@ -128,35 +151,42 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             constexpr uint32_t idesc_s = instr_desc_b(BC_PAGE, false);   // S: N = 64 positions, keys k-major
             constexpr uint32_t idesc_o = instr_desc_b(D, true);          // O: N = head size, values n-major
             const uint32_t q_addr = smem_u32(q_smem);
-            auto scores = [&](int j) {   // S[j & 1] = Q K(j)^T
-                const uint32_t k_addr = smem_u32(kv_smem + (size_t)(j % APT_STAGES) * STAGE_BYTES);
+            auto scores = [&](int j) {   // S[t][j & 1] = Q_t K(j)^T for every query tile t
+                const uint32_t k_addr = smem_u32(kv_smem + (size_t)(j % STAGES) * STAGE_BYTES);
 #pragma unroll
-                for (int kk = 0; kk < D / 16; kk++)
-                    mma_bf16(tmem + S_COL + (j & 1) * BC_PAGE, smem_desc(q_addr + (kk >> 2) * ROW_BLOCK) + 2 * (kk & 3),
-                             smem_desc(k_addr + (kk >> 2) * KV_BLOCK) + 2 * (kk & 3), idesc_s, kk != 0);
-                mma_commit(s_full0 + 8 * (j & 1));
+                for (int t = 0; t < NT; t++) {
+#pragma unroll
+                    for (int kk = 0; kk < D / 16; kk++)
+                        mma_bf16(tmem + (2 * t + (j & 1)) * BC_PAGE, smem_desc(q_addr + (kk >> 2) * NT * ROW_BLOCK + t * ROW_BLOCK) + 2 * (kk & 3),
+                                 smem_desc(k_addr + (kk >> 2) * KV_BLOCK) + 2 * (kk & 3), idesc_s, kk != 0);
+                    mma_commit(s_full(t, j & 1));
+                }
             };
             bool ok = mbar_wait(q_full, 0, 2);
             for (int j = 0; j < 2 && j < n_tiles && ok; j++) {
-                ok = mbar_wait(kv_full0 + 8 * (j % APT_STAGES), 0, 3);
+                ok = mbar_wait(kv_full0 + 8 * (j % STAGES), 0, 3);
                 if (!ok) break;
                 tc_fence_after();
                 scores(j);
             }
             for (int j = 0; j < n_tiles && ok; j++) {
-                ok = mbar_wait(p_full0 + 8 * (j & 1), (j >> 1) & 1, 4);
-                if (!ok) break;
-                tc_fence_after();
-                const uint32_t p_addr = smem_u32(p_smem + (j & 1) * ROW_BLOCK);
-                const uint32_t v_addr = smem_u32(kv_smem + (size_t)(j % APT_STAGES) * STAGE_BYTES + DB * KV_BLOCK);
+                const uint32_t v_addr = smem_u32(kv_smem + (size_t)(j % STAGES) * STAGE_BYTES + DB * KV_BLOCK);
 #pragma unroll
-                for (int kk = 0; kk < BC_PAGE / 16; kk++)
-                    mma_bf16(tmem + O_COL, smem_desc(p_addr) + 2 * kk, smem_desc_mn(v_addr + kk * 2048, KV_BLOCK), idesc_o, (j | kk) != 0);
-                mma_commit(kv_empty0 + 8 * (j % APT_STAGES));
-                mma_commit(o_bar);
+                for (int t = 0; t < NT; t++) {
+                    ok = ok && mbar_wait(p_full(t, j & 1), (j >> 1) & 1, 4);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t p_addr = smem_u32(p_smem + (2 * t + (j & 1)) * ROW_BLOCK);
+#pragma unroll
+                    for (int kk = 0; kk < BC_PAGE / 16; kk++)
+                        mma_bf16(tmem + O_COL + t * D, smem_desc(p_addr) + 2 * kk, smem_desc_mn(v_addr + kk * 2048, KV_BLOCK), idesc_o, (j | kk) != 0);
+                    mma_commit(o_done(t, j & 1));
+                }
+                if (!ok) break;
+                mma_commit(kv_empty0 + 8 * (j % STAGES));
                 if (j + 2 < n_tiles) {
-                    const int s = (j + 2) % APT_STAGES;
-                    ok = mbar_wait(kv_full0 + 8 * s, ((j + 2) / APT_STAGES) & 1, 5);
+                    const int s = (j + 2) % STAGES;
+                    ok = mbar_wait(kv_full0 + 8 * s, ((j + 2) / STAGES) & 1, 5);
                     if (!ok) break;
                     tc_fence_after();
                     scores(j + 2);
@@ -164,28 +194,30 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             }
         }
     } else {
-        // Softmax: this thread owns row 32 q + lane of the tile, TMEM lane of the same number.
-        const int q = warp & 3;
-        const int row = 32 * q + lane;
+        // Softmax: warps 2-5 own query tile 0, warps 6-9 tile 1; this thread owns row 32 q + lane
+        // of its tile, the TMEM lane of the same number.
+        const int q = warp & 3, t = (warp - 2) >> 2;
+        const int row = t * APT_ROWS + 32 * q + lane;                    // among the block's rows
         const int tok = tok0 + row / group, head = g * group + row % group;
-        const bool live = row / group < tokens_per_tile && tok < n_new;
+        const bool live = row / group < tokens_per_block && tok < n_new;
         const int pos = start + tok;
         const int lo = window > 0 && pos + 1 > window ? pos + 1 - window : 0;
-        const int warp_first_pos = start + tok0 + (32 * q) / group;      // the smallest position a row of this warp has
+        const int warp_first_pos = start + tok0 + (t * APT_ROWS + 32 * q) / group;   // the smallest position a row of this warp has
         const uint32_t lane_base = tmem + ((uint32_t)(32 * q) << 16);
+        const uint32_t o_addr = lane_base + O_COL + t * D;
         float m_used = -INFINITY, l = 0.0f;
         bool ok = true;
         for (int j = 0; j < n_tiles; j++) {
-            if (lane == 0) ok = mbar_wait(s_full0 + 8 * (j & 1), (j >> 1) & 1, 6);
+            if (lane == 0) ok = mbar_wait(s_full(t, j & 1), (j >> 1) & 1, 6);
             ok = __shfl_sync(0xffffffffu, ok, 0);
             if (!ok) break;
             tc_fence_after();
             uint32_t sv[64];
 #pragma unroll
-            for (int c = 0; c < 4; c++) tmem_load16(lane_base + S_COL + (j & 1) * BC_PAGE + 16 * c, sv + 16 * c);
+            for (int c = 0; c < 4; c++) tmem_load16(lane_base + (2 * t + (j & 1)) * BC_PAGE + 16 * c, sv + 16 * c);
             tmem_load_wait();
             const int tile = t_begin + j;
-            const bool page_ok = tile < max_pages && pages[tile] >= 0 && pages[tile] < n_pages;
+            const bool page_ok = page_at(j) >= 0;
             // A page that ends at or before the position of this warp's first row is seen whole
             // by all of its rows (padding rows are never written): no mask to work out.
             const bool whole = window == 0 && page_ok && tile * BC_PAGE + BC_PAGE - 1 <= warp_first_pos;
@@ -196,8 +228,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             } else {
 #pragma unroll
                 for (int c = 0; c < 64; c++) {
-                    const int t = tile * BC_PAGE + c;
-                    const bool seen = page_ok && live && t >= lo && t <= pos;
+                    const int kpos = tile * BC_PAGE + c;
+                    const bool seen = page_ok && live && kpos >= lo && kpos <= pos;
                     const float v = seen ? __uint_as_float(sv[c]) : -INFINITY;
                     sv[c] = __float_as_uint(v);
                     tmax = fmaxf(tmax, v);
@@ -211,30 +243,34 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 m_used = m_true;
                 l *= corr;
             }
-            if (j > 0) {
-                // Every phase of the output barrier is waited for, in order (a parity tells two
-                // phases apart, not more): the product of page j - 1 finished long ago as a rule.
-                if (lane == 0) ok = mbar_wait(o_bar, (j - 1) & 1, 7);
+            if (j > 1) {
+                // The P tile written below was read by the product of page j - 2: done long ago as
+                // a rule (the scores of page j were issued after it).  Waiting for every phase in
+                // order also keeps the parities apart: a parity tells two phases apart, not more.
+                if (lane == 0) ok = mbar_wait(o_done(t, j & 1), ((j >> 1) - 1) & 1, 7);
                 ok = __shfl_sync(0xffffffffu, ok, 0);
                 if (!ok) break;
             }
             if (j > 0 && __any_sync(0xffffffffu, raise)) {
-                // Rescale this warp's rows of the accumulator: every product issued so far is in it.
+                // Rescale this warp's rows of the accumulator, once every product issued so far is in it.
+                if (lane == 0) ok = mbar_wait(o_done(t, (j - 1) & 1), ((j - 1) >> 1) & 1, 9);
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+                if (!ok) break;
                 tc_fence_after();
 #pragma unroll 1
                 for (int c = 0; c < D; c += 16) {
                     uint32_t ov[16];
-                    tmem_load16(lane_base + O_COL + c, ov);
+                    tmem_load16(o_addr + c, ov);
                     tmem_load_wait();
 #pragma unroll
                     for (int i = 0; i < 16; i++) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * corr);
-                    tmem_store16(lane_base + O_COL + c, ov);
+                    tmem_store16(o_addr + c, ov);
                 }
                 tmem_store_wait();
             }
             const float base = m_used == -INFINITY ? 0.0f : m_used;
             float sum = 0.0f;
-            uint8_t* p_row = p_smem + (j & 1) * ROW_BLOCK + row * 128;
+            uint8_t* p_row = p_smem + (2 * t + (j & 1)) * ROW_BLOCK + (32 * q + lane) * 128;
 #pragma unroll
             for (int c8 = 0; c8 < 8; c8++) {
                 uint32_t packed[4];
@@ -245,16 +281,16 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                     sum += a + b;
                     packed[i] = pack_bf16(a, b);
                 }
-                *reinterpret_cast<uint4*>(p_row + ((c8 ^ (row & 7)) << 4)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                *reinterpret_cast<uint4*>(p_row + ((c8 ^ (lane & 7)) << 4)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
             }
             l += sum;
             fence_proxy_async();
             tc_fence_before();
-            mbar_arrive(p_full0 + 8 * (j & 1));
+            mbar_arrive(p_full(t, j & 1));
         }
         // The output: the accumulator over this row's sum.
         if (ok) {
-            if (lane == 0) ok = mbar_wait(o_bar, (n_tiles - 1) & 1, 8);
+            if (lane == 0) ok = mbar_wait(o_done(t, (n_tiles - 1) & 1), ((n_tiles - 1) >> 1) & 1, 8);
             ok = __shfl_sync(0xffffffffu, ok, 0);
         }
         if (ok) {
@@ -264,7 +300,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 #pragma unroll 1
             for (int c = 0; c < D; c += 16) {
                 uint32_t ov[16];
-                tmem_load16(lane_base + O_COL + c, ov);
+                tmem_load16(o_addr + c, ov);
                 tmem_load_wait();
                 if (live) {
                     uint32_t packed[8];
@@ -363,30 +399,45 @@ static int query_map(CUtensorMap* map, const void* q, int q_stride, int total_ro
     return BC_OK;
 }
 
-template <int D>
+template <int D, int NT>
 static int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const int* page_table, const int* seq_rows,
                   const int* seq_slot, const int* seq_start, void* out, int seqs, int max_new, int H, int G, int max_pages, int n_pages,
                   int window, float scale, cudaStream_t s) {
     constexpr int DB = D / 64;
-    constexpr int SMEM = DB * APT_ROWS * 128 + 2 * APT_ROWS * 128 + APT_STAGES * 2 * DB * BC_PAGE * 128 + 1024;
+    constexpr int STAGES = (D == 128 && NT == 2) ? 3 : 4;
+    constexpr int SMEM = DB * NT * APT_ROWS * 128 + NT * 2 * APT_ROWS * 128 + STAGES * 2 * DB * BC_PAGE * 128 + 1024;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+        cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel<D, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
         if (e != cudaSuccess) {
             bc_set_error("attention_prefill_tc: cannot set shared memory to %d: %s", SMEM, cudaGetErrorString(e));
             return (int)e;
         }
         configured = true;
     }
-    const int tokens_per_tile = APT_ROWS / (H / G);
-    dim3 grid((max_new + tokens_per_tile - 1) / tokens_per_tile, G, seqs);
-    cudaError_t e = bc_launch(attention_prefill_tc_kernel<D>, grid, dim3(APT_THREADS), (size_t)SMEM, s, mq, mk, mv, page_table, seq_rows, seq_slot,
-                              seq_start, (bf16*)out, H, G, max_pages, n_pages, window, scale * 1.4426950408889634f);
+    const int tokens_per_block = NT * APT_ROWS / (H / G);
+    dim3 grid(G, (max_new + tokens_per_block - 1) / tokens_per_block, seqs);
+    cudaError_t e = bc_launch(attention_prefill_tc_kernel<D, NT>, grid, dim3(64 + NT * 128), (size_t)SMEM, s, mq, mk, mv, page_table, seq_rows,
+                              seq_slot, seq_start, (bf16*)out, H, G, max_pages, n_pages, window, scale * 1.4426950408889634f);
     if (e != cudaSuccess) {
         bc_set_error("attention_prefill_tc: launch failed: %s", cudaGetErrorString(e));
         return (int)e;
     }
     BC_LAUNCH_STATUS();
+}
+
+// Query tiles a block: 0 lets the launcher choose, 1 or 2 force it (measurements and tests).
+static int g_apt_tiles = 0;
+extern "C" void bc_attention_prefill_tc_set_tiles(int n) { g_apt_tiles = n == 1 || n == 2 ? n : 0; }
+
+static int g_apt_sms() {
+    static int sms = 0;
+    if (sms == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+    }
+    return sms;
 }
 
 // Whether this kernel takes the sizes (else the caller uses the mma.sync kernel or the
@@ -407,17 +458,26 @@ extern "C" int bc_attention_prefill_tc_bf16(const void* q, int q_stride, int tot
                  "(at most %d heads a kv head, head size 64 or 128)", H, G, D, APT_ROWS);
     BC_CHECK_ARG(q_stride % 8 == 0 && (uintptr_t)q % 16 == 0 && (uintptr_t)out % 16 == 0 && (uintptr_t)k_cache % 16 == 0 && (uintptr_t)v_cache % 16 == 0,
                  "attention_prefill_tc: q, out and the caches must be 16-byte aligned, the row stride a multiple of 8");
-    BC_CHECK_ARG(G <= 65535 && n_pages > 0, "attention_prefill_tc: bad kv heads %d or pages %d", G, n_pages);
+    BC_CHECK_ARG(n_pages > 0 && max_new / (APT_ROWS / (H / G)) < 65535, "attention_prefill_tc: bad pages %d or too many new rows %d", n_pages, max_new);
     if (seqs == 0 || max_new == 0 || total_rows == 0) return BC_OK;
     CUtensorMap mq, mk, mv;
     const int group = H / G;
-    int st = query_map(&mq, q, q_stride, total_rows, H, D, group, APT_ROWS / group);
+    // Two query tiles a block when that still gives every SM a block (about: the host knows the
+    // longest sequence's rows, not every one's); else one tile, twice as many blocks.
+    const int per_two = 2 * APT_ROWS / group;
+    const long long blocks_of_two = (long long)seqs * ((max_new + per_two - 1) / per_two) * G;
+    const int nt = g_apt_tiles ? g_apt_tiles : (blocks_of_two >= g_apt_sms() ? 2 : 1);
+    int st = query_map(&mq, q, q_stride, total_rows, H, D, group, nt * APT_ROWS / group);
     if (st != BC_OK) return st;
     const long long cache_rows = (long long)n_pages * G * BC_PAGE;
     if ((st = cached_cache_map(&mk, k_cache, cache_rows, D)) != BC_OK) return st;
     if ((st = cached_cache_map(&mv, v_cache, cache_rows, D)) != BC_OK) return st;
-    if (D == 64) return launch<64>(mq, mk, mv, page_table, seq_rows, seq_slot, seq_start, out, seqs, max_new, H, G, max_pages, n_pages, window, scale, s);
-    return launch<128>(mq, mk, mv, page_table, seq_rows, seq_slot, seq_start, out, seqs, max_new, H, G, max_pages, n_pages, window, scale, s);
+#define APT_GO(DD, NN) return launch<DD, NN>(mq, mk, mv, page_table, seq_rows, seq_slot, seq_start, out, seqs, max_new, H, G, max_pages, n_pages, window, scale, s)
+    if (D == 64 && nt == 1) APT_GO(64, 1);
+    if (D == 64) APT_GO(64, 2);
+    if (nt == 1) APT_GO(128, 1);
+    APT_GO(128, 2);
+#undef APT_GO
 }
 
 // This unit's status word: 0, or where a bounded wait gave up.  Reading it waits for the

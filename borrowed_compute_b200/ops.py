@@ -282,6 +282,13 @@ def gemm_tc_status(reset: bool = True) -> int:
     return int(_fn("bc_gemm_tc_status")(_c_int(1 if reset else 0)))
 
 
+def set_attention_prefill_tc_tiles(n: int) -> None:
+    """Query tiles (of 128 rows) a block of the tcgen05 prompt attention: 0 lets the launcher
+    choose (two, unless no sequence brings more rows than one tile holds), 1 or 2 force it.
+    For measurements and tests."""
+    lib().bc_attention_prefill_tc_set_tiles(_c_int(int(n)))
+
+
 def attention_prefill_tc_status(reset: bool = True) -> int:
     """The same word of the tcgen05 prompt attention kernel."""
     return int(_fn("bc_attention_prefill_tc_status")(_c_int(1 if reset else 0)))

@@ -407,12 +407,20 @@ def test_attention_prefill(H, G, D, window):
 @pytest.mark.parametrize("H,G,D", [(32, 8, 128), (8, 2, 64), (12, 4, 64), (4, 4, 128), (16, 1, 64), (10, 2, 128)])
 @pytest.mark.parametrize("window", [0, 70, 200])
 @pytest.mark.parametrize("q_scale", [1.5, 8.0])
-def test_attention_prefill_on_tcgen05(H, G, D, window, q_scale):
-    """The tcgen05 prompt kernel at the same workload and a longer one (the ring of pages
-    wraps, both score buffers are reused); head groups of 1, 3, 4, 5 and 16; large scores,
-    so that the running maximum is raised and the accumulator in TMEM rescaled many times."""
-    run_attention_prefill(H, G, D, window, True, cached=[0, 0, 100, 64, 0], new=[1, 130, 30, 65, 300], q_scale=q_scale)
-    run_attention_prefill(H, G, D, window, True, cached=[0, 70, 0, 1000, 63], new=[2, 900, 129, 17, 64], q_scale=q_scale)
+@pytest.mark.parametrize("tiles", [1, 2])
+def test_attention_prefill_on_tcgen05(H, G, D, window, q_scale, tiles):
+    """The tcgen05 prompt kernel, one and two query tiles a block, at the same workload and a
+    longer one (the ring of pages wraps, both score buffers are reused); head groups of 1, 3,
+    4, 5 and 16; large scores, so that the running maximum is raised and the accumulator in
+    TMEM rescaled many times."""
+    from borrowed_compute_b200 import ops
+
+    try:
+        ops.set_attention_prefill_tc_tiles(tiles)
+        run_attention_prefill(H, G, D, window, True, cached=[0, 0, 100, 64, 0], new=[1, 130, 30, 65, 300], q_scale=q_scale)
+        run_attention_prefill(H, G, D, window, True, cached=[0, 70, 0, 1000, 63], new=[2, 900, 129, 17, 64], q_scale=q_scale)
+    finally:
+        ops.set_attention_prefill_tc_tiles(0)
 
 
 @pytest.mark.parametrize("H,G,D", [(6, 3, 48), (4, 4, 16), (16, 1, 32), (32, 8, 128), (8, 2, 64)])
