@@ -48,7 +48,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                             const int* __restrict__ seq_slot, const int* __restrict__ seq_start, bf16* __restrict__ out, int H, int G,
                             int max_pages, int n_pages, int window, float scale_log2) {
     constexpr int THREADS = 64 + NT * 128;
-    constexpr int STAGES = (D == 128 && NT == 2) ? 3 : 4;
+    constexpr int STAGES = 4;
+    // Two P tiles a query tile let the softmax of page j + 1 write while the product of page j
+    // reads; with two query tiles of head size 128 shared memory has room for one only, and
+    // the softmax then waits for that product (the fourth stage of pages is worth more).
+    constexpr int PB = (D == 128 && NT == 2) ? 1 : 2;
     constexpr int DB = D / 64;                         // 64-element blocks of the head size
     constexpr int ROW_BLOCK = APT_ROWS * 128;          // bytes of a [128 rows][64 elements] block
     constexpr int KV_BLOCK = BC_PAGE * 128;            // bytes of a [64 positions][64 elements] block
@@ -61,8 +65,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* q_smem = smem;
-    uint8_t* p_smem = q_smem + Q_BYTES;                // P of (tile t, buffer b) at (2 t + b) ROW_BLOCK
-    uint8_t* kv_smem = p_smem + NT * 2 * ROW_BLOCK;
+    uint8_t* p_smem = q_smem + Q_BYTES;                // P of (tile t, buffer b) at (PB t + b) ROW_BLOCK
+    uint8_t* kv_smem = p_smem + NT * PB * ROW_BLOCK;
     __shared__ __align__(8) uint64_t bars[2 * STAGES + 1 + 6 * NT];
     __shared__ uint32_t tmem_slot;
     __shared__ int page_of[APT_PAGES_KEPT];   // the first pages this block reads, fetched once (-1: none)
@@ -176,7 +180,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                     ok = ok && mbar_wait(p_full(t, j & 1), (j >> 1) & 1, 4);
                     if (!ok) break;
                     tc_fence_after();
-                    const uint32_t p_addr = smem_u32(p_smem + (2 * t + (j & 1)) * ROW_BLOCK);
+                    const uint32_t p_addr = smem_u32(p_smem + (PB * t + (j & (PB - 1))) * ROW_BLOCK);
 #pragma unroll
                     for (int kk = 0; kk < BC_PAGE / 16; kk++)
                         mma_bf16(tmem + O_COL + t * D, smem_desc(p_addr) + 2 * kk, smem_desc_mn(v_addr + kk * 2048, KV_BLOCK), idesc_o, (j | kk) != 0);
@@ -243,19 +247,22 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 m_used = m_true;
                 l *= corr;
             }
-            if (j > 1) {
-                // The P tile written below was read by the product of page j - 2: done long ago as
-                // a rule (the scores of page j were issued after it).  Waiting for every phase in
-                // order also keeps the parities apart: a parity tells two phases apart, not more.
-                if (lane == 0) ok = mbar_wait(o_done(t, j & 1), ((j >> 1) - 1) & 1, 7);
+            if (j >= PB) {
+                // The P tile written below was last read by the product of page j - PB (with two
+                // P tiles: done long ago as a rule, the scores of page j were issued after it).
+                // Waiting for every phase in order also keeps the parities apart: a parity tells
+                // two phases apart, not more.
+                if (lane == 0) ok = mbar_wait(o_done(t, (j - PB) & 1), ((j - PB) >> 1) & 1, 7);
                 ok = __shfl_sync(0xffffffffu, ok, 0);
                 if (!ok) break;
             }
             if (j > 0 && __any_sync(0xffffffffu, raise)) {
                 // Rescale this warp's rows of the accumulator, once every product issued so far is in it.
-                if (lane == 0) ok = mbar_wait(o_done(t, (j - 1) & 1), ((j - 1) >> 1) & 1, 9);
-                ok = __shfl_sync(0xffffffffu, ok, 0);
-                if (!ok) break;
+                if (PB == 2) {
+                    if (lane == 0) ok = mbar_wait(o_done(t, (j - 1) & 1), ((j - 1) >> 1) & 1, 9);
+                    ok = __shfl_sync(0xffffffffu, ok, 0);
+                    if (!ok) break;
+                }
                 tc_fence_after();
 #pragma unroll 1
                 for (int c = 0; c < D; c += 16) {
@@ -270,7 +277,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             }
             const float base = m_used == -INFINITY ? 0.0f : m_used;
             float sum = 0.0f;
-            uint8_t* p_row = p_smem + (2 * t + (j & 1)) * ROW_BLOCK + (32 * q + lane) * 128;
+            uint8_t* p_row = p_smem + (PB * t + (j & (PB - 1))) * ROW_BLOCK + (32 * q + lane) * 128;
 #pragma unroll
             for (int c8 = 0; c8 < 8; c8++) {
                 uint32_t packed[4];
@@ -404,8 +411,8 @@ static int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMa
                   const int* seq_slot, const int* seq_start, void* out, int seqs, int max_new, int H, int G, int max_pages, int n_pages,
                   int window, float scale, cudaStream_t s) {
     constexpr int DB = D / 64;
-    constexpr int STAGES = (D == 128 && NT == 2) ? 3 : 4;
-    constexpr int SMEM = DB * NT * APT_ROWS * 128 + NT * 2 * APT_ROWS * 128 + STAGES * 2 * DB * BC_PAGE * 128 + 1024;
+    constexpr int STAGES = 4, PB = (D == 128 && NT == 2) ? 1 : 2;
+    constexpr int SMEM = DB * NT * APT_ROWS * 128 + NT * PB * APT_ROWS * 128 + STAGES * 2 * DB * BC_PAGE * 128 + 1024;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel<D, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
