@@ -10,8 +10,8 @@ import torch
 
 from ..architectures import resolve
 from ..parts import base as P
-from ..parts.base import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, CacheNeed, ModelSpec, PartSpec, Runtime,
-                          StateNeed, StepContext, TensorSpec)
+from ..parts.base import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, POSITION_ENCODINGS, CacheNeed, ModelSpec, PartSpec,
+                          Runtime, StateNeed, StepContext, TensorSpec)
 
 
 def _build(registry: P.Registry, spec: PartSpec):
@@ -27,6 +27,7 @@ class DecoderModel:
             if run.memory_of is not None and not (0 <= run.memory_of < i and spec.schedule[run.memory_of].memory_of is None):
                 raise ValueError(f"schedule entry {i} reads the memory of entry {run.memory_of}, which is not an earlier owner")
         self.embedding = _build(EMBEDDINGS, spec.embedding)
+        self.position = None if spec.position is None else _build(POSITION_ENCODINGS, spec.position)
         self.blocks = []
         for layer in spec.layers:
             block_cls = BLOCKS.get(layer.block)
@@ -38,6 +39,8 @@ class DecoderModel:
 
     def _named_parts(self):
         yield self.spec.embedding.prefix, self.embedding
+        if self.position is not None:
+            yield self.spec.position.prefix, self.position
         for layer, block in zip(self.spec.layers, self.blocks):
             yield layer.norm1.prefix, block.norm1
             yield layer.mixer.prefix, block.mixer
@@ -73,6 +76,8 @@ class DecoderModel:
         rt = self.rt
         residual = torch.empty((ctx.rows, self.spec.hidden_size), dtype=torch.float32, device=rt.device)
         self.embedding.forward(ctx, residual)
+        if self.position is not None:
+            self.position.on_embeddings(residual, ctx)
         for i, run in enumerate(self.spec.schedule):
             self.blocks[run.layer].forward(residual, ctx, cache.memory(i), rt)
         h = torch.empty((n_want, self.spec.hidden_size), dtype=rt.dtype, device=rt.device)

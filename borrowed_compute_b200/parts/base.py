@@ -106,6 +106,10 @@ class ModelSpec:
     final_norm: PartSpec
     head: PartSpec
     stop_ids: Tuple[int, ...] = ()
+    # A position encoding that acts on the stream right after the embedding (its
+    # ``on_embeddings``), with tensors of its own if it wants any; None for models whose
+    # positions live inside their mixers (rotary tables).
+    position: Optional[PartSpec] = None
 
 
 # -------------------------------------------------------------------------- declared tensors

@@ -1,7 +1,9 @@
 """Each part alone against the plain implementation's function for it, and a model made
 of other parts: a toy mixer with state of its own, defined here, registered, built from a
 config.json and stepped without touching the package's files; its layers differ in their
-mixer, its schedule names a layer several times and lets one run read another's cache."""
+mixer, its schedule names a layer several times and lets one run read another's cache.  A
+second toy model has a feed-forward with routing and positions learned as a table that is
+added to the embeddings."""
 
 from __future__ import annotations
 
@@ -388,3 +390,156 @@ def test_toy_model_with_a_stateful_mixer(tmp_path):
     assert np.abs(np.concatenate(got_b) - ref_b).max() <= 1e-4 * (1 + np.abs(ref_b).max())
     eng.cache.slots.check()
     assert eng.cache.slots.live() == []
+
+
+# -------------------------------------------- toy parts: a routed feed-forward, learned positions
+
+def register_routed_toy():
+    """A second toy architecture: attention without rotation, positions learned as a table
+    added to the stream after the embedding, and a feed-forward that routes every row to
+    one of three small experts.  All of it defined here, none of it in the framework."""
+    from borrowed_compute_b200.architectures import register_architecture
+    from borrowed_compute_b200.config.llama import LlamaConfig
+    from borrowed_compute_b200.parts.base import (FEED_FORWARDS, POSITION_ENCODINGS, FeedForward, LayerSpec, ModelSpec, PartSpec,
+                                                  PositionEncoding, RunSpec, TensorSpec)
+
+    if "toy_top1_experts" not in FEED_FORWARDS.names():
+        @FEED_FORWARDS.register("toy_top1_experts")
+        class Top1Experts(FeedForward):
+            """Each row goes to the expert whose router score is largest (float32 scores, the
+            first of equals): out = down_e(relu(up_e(x))).  Runs on the device without a
+            look at the host, so decode steps can be captured."""
+
+            def __init__(self, hidden_size, inner, experts):
+                super().__init__(hidden_size=hidden_size, inner=inner, experts=experts)
+                self.hidden_size, self.inner, self.experts = hidden_size, inner, experts
+
+            def tensors(self):
+                return {"router.weight": TensorSpec((self.experts, self.hidden_size)),
+                        "up.weight": TensorSpec((self.experts * self.inner, self.hidden_size)),
+                        "down.weight": TensorSpec((self.experts * self.hidden_size, self.inner))}
+
+            def load(self, tensors, rt):
+                super().load(tensors, rt)
+                self.router = tensors["router.weight"].float()
+                self.up = tensors["up.weight"].float().reshape(self.experts, self.inner, self.hidden_size)
+                self.down = tensors["down.weight"].float().reshape(self.experts, self.hidden_size, self.inner)
+
+            def forward(self, x, residual, ctx):
+                xf = x.float()
+                choice = torch.argmax(xf @ self.router.T, dim=1)                      # [rows]
+                hidden = torch.relu(torch.einsum("rh,eih->rei", xf, self.up))         # every expert, then pick: a toy
+                out = torch.einsum("rei,ehi->reh", hidden, self.down)
+                residual[: x.shape[0]] += out[torch.arange(x.shape[0], device=x.device), choice]
+
+    if "toy_learned_positions" not in POSITION_ENCODINGS.names():
+        @POSITION_ENCODINGS.register("toy_learned_positions")
+        class LearnedPositions(PositionEncoding):
+            """A table [positions, hidden] added to the stream after the embedding."""
+
+            def __init__(self, hidden_size, max_positions):
+                super().__init__(hidden_size=hidden_size, max_positions=max_positions)
+                self.hidden_size, self.max_positions = hidden_size, max_positions
+
+            def tensors(self):
+                return {"table": TensorSpec((self.max_positions, self.hidden_size))}
+
+            def load(self, tensors, rt):
+                super().load(tensors, rt)
+                self.table = tensors["table"].float()
+
+            def on_embeddings(self, residual, ctx):
+                residual[: ctx.rows] += self.table[ctx.row_pos.long()] * (ctx.row_slot >= 0)[:, None]
+
+    def routed_spec(cfg):
+        norm = lambda p: PartSpec("rmsnorm", {"size": cfg.hidden_size, "eps": cfg.rms_norm_eps}, p)
+        layers = tuple(
+            LayerSpec("prenorm", norm(f"l{i}.n1."), PartSpec("gqa_attention", {
+                "hidden_size": cfg.hidden_size, "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
+                "head_dim": cfg.head_dim, "position": {"kind": "none"}}, f"l{i}.attn."), norm(f"l{i}.n2."),
+                PartSpec("toy_top1_experts", {"hidden_size": cfg.hidden_size, "inner": cfg.intermediate_size, "experts": 3}, f"l{i}.moe."))
+            for i in range(cfg.num_hidden_layers))
+        return ModelSpec(hidden_size=cfg.hidden_size, vocab_size=cfg.vocab_size, max_positions=cfg.max_position_embeddings,
+                         embedding=PartSpec("token_embedding", {"vocab_size": cfg.vocab_size, "hidden_size": cfg.hidden_size}, "emb."),
+                         position=PartSpec("toy_learned_positions", {"hidden_size": cfg.hidden_size, "max_positions": cfg.max_position_embeddings}, "pos."),
+                         layers=layers, schedule=tuple(RunSpec(i) for i in range(cfg.num_hidden_layers)), final_norm=norm("out_norm."),
+                         head=PartSpec("linear_head", {"vocab_size": cfg.vocab_size, "hidden_size": cfg.hidden_size, "tied": True}, "head."))
+
+    register_architecture("ToyRoutedForCausalLM", LlamaConfig.from_dict, routed_spec)
+
+
+ROUTED = {"architectures": ["ToyRoutedForCausalLM"], "num_hidden_layers": 2, "hidden_size": 40, "num_attention_heads": 2,
+          "num_key_value_heads": 2, "head_dim": 16, "intermediate_size": 24, "vocab_size": 70, "rope_theta": 10000.0,
+          "rms_norm_eps": 1e-5, "max_position_embeddings": 160}
+
+
+def routed_reference(w, tokens):
+    """The routed toy in plain NumPy, whole sequence at once; also which expert each row took."""
+    c = plain_llama.read_config(ROUTED)
+    n, hid, inner = len(tokens), 40, 24
+    x = plain_llama.embed(w["emb.weight"], tokens) + w["pos.table"][:n]
+    taken = []
+    for i in range(2):
+        h = plain_llama.rms_norm(x, w[f"l{i}.n1.weight"], c["eps"])
+        q = (h @ w[f"l{i}.attn.q_proj.weight"].T).reshape(n, 2, 16)
+        k = (h @ w[f"l{i}.attn.k_proj.weight"].T).reshape(n, 2, 16)
+        v = (h @ w[f"l{i}.attn.v_proj.weight"].T).reshape(n, 2, 16)
+        x = x + plain_llama.attention(q, k, v).reshape(n, 32) @ w[f"l{i}.attn.o_proj.weight"].T
+        h = plain_llama.rms_norm(x, w[f"l{i}.n2.weight"], c["eps"])
+        choice = np.argmax(h @ w[f"l{i}.moe.router.weight"].T, axis=1)
+        up = w[f"l{i}.moe.up.weight"].reshape(3, inner, hid)
+        down = w[f"l{i}.moe.down.weight"].reshape(3, hid, inner)
+        x = x + np.stack([down[e] @ np.maximum(up[e] @ h[r], 0.0) for r, e in enumerate(choice)])
+        taken.append(choice)
+    return plain_llama.rms_norm(x, w["out_norm.weight"], c["eps"]) @ w["emb.weight"].T, taken
+
+
+def test_toy_model_with_a_routed_feed_forward_and_learned_positions(tmp_path):
+    """A feed-forward with routing and a position encoding that acts on the embeddings,
+    registered from here, run through the ordinary engine (captured decode steps included)
+    in float32, against their plain NumPy twin: whole, prompt then single tokens, and two
+    requests in a batch."""
+    from borrowed_compute_b200 import Engine, StepEntry
+    from borrowed_compute_b200.engine.model import expected_tensors_for_config
+    from borrowed_compute_b200.weights import write_safetensors
+
+    register_routed_toy()
+    expected = expected_tensors_for_config(ROUTED)
+    assert "pos.table" in expected and "l1.moe.router.weight" in expected and "l0.attn.q_proj.weight" in expected
+    r = np.random.default_rng(11)
+    w = {k: ((1 + 0.1 * r.standard_normal(s.shape)) if s.role == "vector" else r.standard_normal(s.shape) * (1.0 if k == "emb.weight" else 0.3))
+         .astype(np.float32) for k, s in expected.items() if not s.optional}
+    folder = str(tmp_path / "routed")
+    os.makedirs(folder)
+    json.dump(ROUTED, open(os.path.join(folder, "config.json"), "w"))
+    write_safetensors(os.path.join(folder, "model.safetensors"), {k: torch.from_numpy(v) for k, v in w.items()})
+    eng = Engine.from_folder(folder, dtype="float32", max_tokens=512, max_slots=3)
+    assert eng.use_graphs                                          # nothing here plans on the host
+    w64 = {k: v.astype(np.float64) for k, v in w.items()}
+    a, b = seeded_tokens(5, 90, 70), seeded_tokens(6, 13, 70)
+    (ref_a, taken_a), (ref_b, _) = routed_reference(w64, a), routed_reference(w64, b)
+    assert all(len(set(t.tolist())) == 3 for t in taken_a), "the routing must reach every expert, or the test shows little"
+    tol_a, tol_b = 2e-4 * (1 + np.abs(ref_a).max()), 2e-4 * (1 + np.abs(ref_b).max())
+    s = eng.acquire()
+    whole = eng.step([StepEntry(s, a, want=tuple(range(len(a))))]).cpu().numpy()
+    eng.release(s)
+    assert np.abs(whole - ref_a).max() <= tol_a, "whole"
+    s = eng.acquire()
+    head = eng.step([StepEntry(s, a[:50], want=tuple(range(50)))]).cpu().numpy()
+    tail = np.concatenate([eng.step([StepEntry(s, [t], want=(0,))]).cpu().numpy() for t in a[50:]])
+    eng.release(s)
+    assert np.abs(np.concatenate([head, tail]) - ref_a).max() <= tol_a, "prompt, then single tokens through the captured step"
+    sa, sb = eng.acquire(), eng.acquire()
+    first = eng.step([StepEntry(sa, a[:60], want=tuple(range(60))), StepEntry(sb, b[:5], want=tuple(range(5)))]).cpu().numpy()
+    got_a, got_b = [first[:60]], [first[60:]]
+    for i in range(30):
+        entries = [StepEntry(sa, [a[60 + i]], want=(0,))] + ([StepEntry(sb, [b[5 + i]], want=(0,))] if 5 + i < len(b) else [])
+        out = eng.step(entries).cpu().numpy()
+        got_a.append(out[:1])
+        if len(entries) == 2:
+            got_b.append(out[1:])
+        if 5 + i == len(b) - 1:
+            eng.release(sb)
+    eng.release(sa)
+    assert np.abs(np.concatenate(got_a) - ref_a).max() <= tol_a and np.abs(np.concatenate(got_b) - ref_b).max() <= tol_b, "batch"
+    eng.cache.slots.check()
