@@ -49,6 +49,7 @@ struct TcParams {
     int k_iters_per_split;
     int clustered;      // split-K: the splits of a tile are one thread-block cluster and add up through shared memory
     int n_tiles, t_tiles;   // blocks along the weight rows and along the tokens
+    int pair_tokens;        // the paired kernel: tokens a tile (64, 128, 192 or 256)
 };
 
 // Blocks that run at the same time should share operands: the block index walks up to
@@ -342,7 +343,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 template <int EPI>
 __global__ void __launch_bounds__(TCP_THREADS, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, const TcParams p) {
-    constexpr int BN = 256;                               // tokens a pair
+    constexpr int BN = 256;                               // token columns of an accumulator in TMEM; a pair's tile takes p.pair_tokens <= BN
     constexpr int TILE = TC_BM * TC_BK * 2;               // 16 KB: 128 rows of 64 k
     constexpr int STAGE_BYTES = 3 * TILE;                 // two weight tiles and this block's half of the tokens
     constexpr int TMEM_COLS = 512;                        // two accumulators of 256 token columns
@@ -359,6 +360,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
     const int total_tiles = p.n_tiles * p.t_tiles;
     const int k_iters = (p.K + TC_BK - 1) / TC_BK;
+    const int bn = p.pair_tokens;                         // tokens a pair's tile: a multiple of 64 (each block loads a box of 128 and uses bn / 2)
     const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[TCP_STAGES_MAX]);
     const uint32_t acc_full = smem_u32(&bars[2 * TCP_STAGES_MAX]), acc_empty = smem_u32(&bars[2 * TCP_STAGES_MAX + 1]);
 
@@ -400,7 +402,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                 place(pair + seq * n_pairs, tile_n, tile_t);
                 k = (it - seq * k_iters) * TC_BK;
                 n0 = tile_n * 2 * OUT_ROWS + (int)rank * OUT_ROWS;
-                t_mine = tile_t * BN + (int)rank * (BN / 2);
+                t_mine = tile_t * bn + (int)rank * (bn / 2);
             };
             auto load_w = [&](uint32_t dst, uint32_t bar, int k, int n0) {
                 tma_load_2d_pair(dst, &map_w, bar, k, n0);
@@ -434,7 +436,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         }
     } else if (warp == 1) {
         if (lane == 0 && rank == 0) {
-            constexpr uint32_t idesc = instr_desc_pair(BN);
+            const uint32_t idesc = instr_desc_pair(bn);
             bool ok = true;
             int it = 0, n = 0;
             for (int tile = pair; tile < total_tiles && ok; tile += n_pairs, n++) {
@@ -471,7 +473,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         for (int tile = pair; tile < total_tiles; tile += n_pairs, n++) {
             int tile_n, tile_t;
             place(tile, tile_n, tile_t);
-            const int t0 = tile_t * BN;
+            const int t0 = tile_t * bn;
             if (lane == 0) ok = mbar_wait(acc_full, n & 1, 3);
             ok = __shfl_sync(0xffffffffu, ok, 0);
             if (!ok) break;
@@ -494,7 +496,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                     if (EPI == EPI_ADD_F32) atomicAdd(&((float*)p.out)[o], val);
                 }
             };
-            constexpr int COLS = EPI == EPI_SWIGLU ? BN / 2 : BN;          // token columns this warp writes
+            const int COLS = EPI == EPI_SWIGLU ? bn / 2 : bn;              // token columns this warp writes (a multiple of 32)
             const int c_first = EPI == EPI_SWIGLU ? set * COLS : 0;
             const uint32_t src = lanes + (EPI == EPI_SWIGLU ? c_first : set * BN);   // SwiGLU: the gate accumulator; up is BN columns on
             uint32_t va[16], vb[16], ua[16], ub[16];
@@ -650,6 +652,8 @@ static int launch(const CUtensorMap& mw, const CUtensorMap& mx, TcParams p, int 
 
 // Whether prompts run on pairs of SMs (the default) or every block on its own; for measurements and tests.
 static int g_tc_pair = 1;
+static int g_tc_pair_tokens = 0;   // 0: the launcher chooses the tokens a paired tile takes; 64, 128, 192, 256 force it
+extern "C" void bc_gemm_tc_set_pair_tokens(int n) { g_tc_pair_tokens = (n == 64 || n == 128 || n == 192 || n == 256) ? n : 0; }
 extern "C" void bc_gemm_tc_set_pair(int on) { g_tc_pair = on != 0; }
 
 template <int EPI>
@@ -680,7 +684,22 @@ static int launch_pair(const CUtensorMap& mw, const CUtensorMap& mx, TcParams p,
     }
     const int rows = EPI == EPI_SWIGLU ? 2 * TC_BM : 4 * TC_BM;   // outputs a pair
     p.n_tiles = (p.N + rows - 1) / rows;
-    p.t_tiles = (p.T + 255) / 256;
+    // Tokens a tile: whole tiles are lost when the tile count is just over a multiple of the
+    // pairs (96 tiles on 74 pairs take two rounds).  A narrower tile costs less than its share
+    // (per k-step about 640 + 2 x tokens clocks of shared-memory traffic: the weight slices
+    // and the TMA writes do not shrink), so it pays only when it saves a round.
+    int best = 256;
+    if (g_tc_pair_tokens > 0) best = g_tc_pair_tokens;
+    else {
+        double best_cost = 1e30;
+        for (int bn = 256; bn >= 128; bn -= 64) {
+            const long long tiles = (long long)p.n_tiles * ((p.T + bn - 1) / bn);
+            const double cost = (double)((tiles + pairs_on_device - 1) / pairs_on_device) * (700.0 + 2.0 * bn);
+            if (cost < best_cost * 0.97) best_cost = cost, best = bn;
+        }
+    }
+    p.pair_tokens = best;
+    p.t_tiles = (p.T + best - 1) / best;
     const long long tiles = (long long)p.n_tiles * p.t_tiles;
     const int pairs = tiles < pairs_on_device ? (int)tiles : pairs_on_device;   // persistent: a pair walks over tiles
     dim3 grid(2 * pairs, 1, 1);
@@ -772,6 +791,7 @@ extern "C" int bc_gemm_tc_bf16(const void* X, const void* W, void* out, int T, i
     p.stages = 0;
     p.k_iters_per_split = 0;
     p.n_tiles = p.t_tiles = p.clustered = 0;
+    p.pair_tokens = 256;
     if (paired) {
         switch (epilogue) {
             case EPI_STORE: return launch_pair<EPI_STORE>(mw, mx, p, s);

@@ -63,6 +63,12 @@ def set_gemm_tc_pair(on: bool) -> None:
     lib().bc_gemm_tc_set_pair(_c_int(1 if on else 0))
 
 
+def set_gemm_tc_pair_tokens(n: int) -> None:
+    """Tokens a tile of the paired product takes: 0 lets the launcher choose (256 unless a
+    narrower tile saves a whole round of tiles), 64, 128, 192 or 256 force it."""
+    lib().bc_gemm_tc_set_pair_tokens(_c_int(int(n)))
+
+
 def _stream() -> _c_void_p:
     return _c_void_p(torch.cuda.current_stream().cuda_stream)
 

@@ -94,7 +94,7 @@ def test_gemm_tc_splits_agree_through_cluster_and_through_scratch(T, N, K, split
 
 
 @pytest.mark.parametrize("T,N,K", [(300, 130, 192), (600, 384, 512), (129, 128, 64), (1000, 1030, 448), (513, 700, 72), (2048, 512, 1024)])
-@pytest.mark.parametrize("paired", [True, False])
+@pytest.mark.parametrize("paired", [True, False, 64, 128, 192])
 def test_gemm_tc_many_tokens_on_pairs_of_sms_and_on_single_blocks(T, N, K, paired):
     """More than 128 tokens: the tile shared by two SMs (cta_group::2) and the tile of one
     block, every epilogue, edges in all three dimensions, against the float64 product."""
@@ -106,7 +106,8 @@ def test_gemm_tc_many_tokens_on_pairs_of_sms_and_on_single_blocks(T, N, K, paire
     wn = w[:N].contiguous()
     base = torch.from_numpy(np.random.default_rng(3).standard_normal((T, N)).astype(np.float32)).cuda()
     try:
-        ops.set_gemm_tc_pair(paired)
+        ops.set_gemm_tc_pair(bool(paired))
+        ops.set_gemm_tc_pair_tokens(0 if isinstance(paired, bool) else paired)   # a number: that many tokens a paired tile
         out32 = torch.full((T, N), 7.0, dtype=torch.float32, device="cuda")
         ops.gemm_tc(x, wn, out32, ops.EPI_STORE_F32, splits=1)
         out16 = torch.full((T, N), 7.0, dtype=torch.bfloat16, device="cuda")
@@ -117,6 +118,7 @@ def test_gemm_tc_many_tokens_on_pairs_of_sms_and_on_single_blocks(T, N, K, paire
         ops.gemm_tc(x, w, act, ops.EPI_SWIGLU, splits=1)
     finally:
         ops.set_gemm_tc_pair(True)
+        ops.set_gemm_tc_pair_tokens(0)
     assert ops.gemm_tc_status() == 0
     assert np.abs(f64(out32) - full[:, :N]).max() <= 2e-5 * scale, "float store"
     assert np.abs(f64(out16) - full[:, :N]).max() <= 2.0 ** -8 * scale, "bf16 store"
