@@ -5,14 +5,14 @@
 // it is laid out is Blackwell's own:
 //
 //   - A block takes one or two tiles of 128 query rows = (tokens) x (the heads that share one
-//     kv head), token major, of one sequence.  Q comes by one 3-d TMA box per 64 elements of the head size
-//     straight out of the fused projection [row][head][d]; every 64-position page of keys
-//     and values comes by 2-d TMA boxes from the paged cache into a ring of stages.  All
-//     tiles are 128-byte-swizzled blocks of [rows][64 elements].
+//     kv head), token major, of one sequence.  Q comes by one 3-d TMA box per 64 elements
+//     of the head size straight out of the fused projection [row][head][d]; every
+//     64-position page of keys and values comes by 2-d TMA boxes from the paged cache into
+//     a ring of stages.  All tiles are 128-byte-swizzled blocks of [rows][64 elements].
 //   - S = Q K^T is one chain of tcgen05.mma (M 128 rows, N 64 positions, K the head size),
 //     accumulated in TMEM, two buffers, so the scores of the next page are computed while
 //     the softmax warps work on this one.  Keys are the k-major B operand as they lie.
-//   - Four softmax warps own 32 rows each, one row a thread (TMEM lane = row), so row
+//   - Four softmax warps a query tile own 32 rows each, one row a thread (TMEM lane = row), so row
 //     maxima and sums need no shuffles: tcgen05.ld the scores, mask what the row may not
 //     see (positions after its own, before its window), exponentiate against the running
 //     maximum, round to bf16 and write P to shared memory in the A-operand layout.
@@ -25,8 +25,9 @@
 //     maximum, so the result is the softmax all the same.
 //
 // Warp roles: warp 0 issues TMA, warp 1 owns TMEM and issues the MMAs, warps 2-5 (and 6-9 for
-// the second query tile) are the softmax and write the output.  Every wait is bounded (about a second); a wait that gives
-// up records where in a status word, and the block frees its TMEM and returns.
+// the second query tile) are the softmax and write the output.  Every wait is bounded
+// (about a second); a wait that gives up records where in a status word, and the block
+// frees its TMEM and returns.
 #include <mutex>
 #include <unordered_map>
 

@@ -26,6 +26,8 @@
 //     launched as one thread-block cluster, keep their partial tiles in shared memory, and
 //     every block adds up a share of the token columns out of its peers' shared memory,
 //     in the same order.
+//   - More than 128 tokens (prompts) take the second kernel of this file: persistent, on
+//     pairs of SMs (cta_group::2); see there.
 //
 // Every wait is bounded: after about a second without progress a thread records where it
 // gave up in a status word, stops waiting, and the block frees its TMEM and returns.
