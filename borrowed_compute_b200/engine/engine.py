@@ -12,6 +12,9 @@ vocabulary (274-276).
 
 from __future__ import annotations
 
+import gc
+import weakref
+
 from typing import Any, Dict, List, Mapping, Optional, Sequence
 
 import numpy as np
@@ -33,7 +36,7 @@ class _DecodeGraph:
     """One captured decode step for a fixed number of rows."""
 
     def __init__(self, engine: "Engine", rows: int):
-        self.engine, self.rows = engine, rows
+        self._engine, self.rows = weakref.ref(engine), rows   # no cycle: a dropped engine and its graphs go at once
         dev = engine.rt.device
         # tokens, row_pos, row_slot, seq_rows (+1), seq_slot, seq_start, want_rows
         self.sizes = [("tokens", rows), ("row_pos", rows), ("row_slot", rows), ("seq_rows", rows + 1), ("seq_slot", rows),
@@ -81,6 +84,13 @@ class _DecodeGraph:
             self.copied = torch.cuda.Event()
         self.copied.record()
 
+    @property
+    def engine(self) -> "Engine":
+        eng = self._engine()
+        if eng is None:
+            raise RuntimeError("the engine of this captured step is gone")
+        return eng
+
     def _forward(self) -> torch.Tensor:
         v, rows = self.views, self.rows
         ctx = StepContext(rows=rows, seqs=rows, tokens=v["tokens"], row_pos=v["row_pos"], row_slot=v["row_slot"], seq_rows=v["seq_rows"],
@@ -93,9 +103,19 @@ class _DecodeGraph:
         if self.graph is None:
             self._forward()   # once eagerly: first-use set-up must not happen inside a capture
             torch.cuda.synchronize()
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):
-                self.scores = self._forward()
+            # Nothing may free device memory or destroy another graph while this one is being
+            # captured: objects waiting for the cycle collector (an engine dropped earlier in
+            # the process, with its graphs) go now, and the collector rests during the capture.
+            gc.collect()
+            was_enabled = gc.isenabled()
+            gc.disable()
+            try:
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph):
+                    self.scores = self._forward()
+            finally:
+                if was_enabled:
+                    gc.enable()
             self.graph = graph
         self.graph.replay()
         return self.scores
