@@ -4,7 +4,7 @@ head.  Nothing here knows an architecture; the sequence of work is the reference
 
 from __future__ import annotations
 
-from typing import Any, Dict, List, Mapping, Optional, Sequence, Tuple
+from typing import Any, Dict, List, Mapping, Optional, Tuple
 
 import torch
 
