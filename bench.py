@@ -50,7 +50,7 @@ def peaks() -> dict:
         if "bf16_tflops_sustained" in d:
             out["bf16_tflops_sustained"] = float(d["bf16_tflops_sustained"])
         return out
-    except (OSError, KeyError, ValueError):
+    except (OSError, KeyError, ValueError, TypeError):
         return dict(FALLBACK_PEAKS)
 
 
