@@ -252,6 +252,84 @@ __global__ void rope_append_kernel(T* __restrict__ qkv, const float2* __restrict
     }
 }
 
+// The same for many rows of bf16 (prompts) with a head size that is a multiple of 16: eight
+// pairs a thread, 16-byte reads and writes, 32 heads of a row a block.  The same products,
+// sums and roundings as above.
+__global__ void __launch_bounds__(256)
+rope_append_wide_kernel(bf16* __restrict__ qkv, const float2* __restrict__ cos_sin, const int* __restrict__ row_pos,
+                        const int* __restrict__ row_slot, const int* __restrict__ page_table, bf16* __restrict__ k_cache,
+                        bf16* __restrict__ v_cache, int H, int G, int D, int pairing, int max_pages, int n_pages, int write_cache) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int r = blockIdx.x, h = blockIdx.y * blockDim.y + threadIdx.y;
+    if (h >= H + 2 * G) return;
+    const int slot = row_slot[r];
+    if (slot < 0) return;
+    const int pos = row_pos[r];
+    const int half = D / 2;
+    bf16* head = qkv + ((size_t)r * (H + 2 * G) + h) * D;
+    int page = -1;
+    if (h >= H && write_cache && pos / BC_PAGE < max_pages) page = page_table[(size_t)slot * max_pages + pos / BC_PAGE];
+    const bool can_write = page >= 0 && page < n_pages;
+    const int in_page = pos % BC_PAGE;
+    if (h >= H + G) {
+        if (!can_write) return;
+        bf16* dst = v_cache + (((size_t)page * G + (h - H - G)) * BC_PAGE + in_page) * D;
+        for (int d = threadIdx.x * 8; d < D; d += blockDim.x * 8) *reinterpret_cast<uint4*>(dst + d) = *reinterpret_cast<const uint4*>(head + d);
+        return;
+    }
+    const float2* cs = cos_sin ? cos_sin + (size_t)pos * half : nullptr;
+    bf16* dst = h < H ? head : (can_write ? k_cache + (((size_t)page * G + (h - H)) * BC_PAGE + in_page) * D : nullptr);
+    if (!dst) return;
+    for (int i = 8 * threadIdx.x; i < half; i += 8 * blockDim.x) {   // pairs i .. i + 7
+        bf16 lo[8], hi[8];   // pairing 0: elements i.. and i + half..; pairing 1: elements 2 i .. 2 i + 15, even and odd taken apart below
+        if (pairing) {
+            *reinterpret_cast<uint4*>(lo) = *reinterpret_cast<const uint4*>(head + 2 * i);
+            *reinterpret_cast<uint4*>(hi) = *reinterpret_cast<const uint4*>(head + 2 * i + 8);
+        } else {
+            *reinterpret_cast<uint4*>(lo) = *reinterpret_cast<const uint4*>(head + i);
+            *reinterpret_cast<uint4*>(hi) = *reinterpret_cast<const uint4*>(head + i + half);
+        }
+        float2 c[8];
+        if (cs) {
+#pragma unroll
+            for (int j = 0; j < 8; j += 2) {
+                const float4 two = *reinterpret_cast<const float4*>(cs + i + j);
+                c[j] = make_float2(two.x, two.y);
+                c[j + 1] = make_float2(two.z, two.w);
+            }
+        }
+        bf16 out_lo[8], out_hi[8];
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            // pair j of this thread: (lo[j], hi[j]), or for adjacent pairs elements 2 j and 2 j + 1 of the 16 read
+            const bf16 a = pairing ? (j < 4 ? lo[2 * j] : hi[2 * j - 8]) : lo[j];
+            const bf16 b = pairing ? (j < 4 ? lo[2 * j + 1] : hi[2 * j - 7]) : hi[j];
+            const float x0 = __bfloat162float(a), x1 = __bfloat162float(b);
+            float y0 = x0, y1 = x1;
+            if (cs) {
+                y0 = __fsub_rn(__fmul_rn(x0, c[j].x), __fmul_rn(x1, c[j].y));
+                y1 = __fadd_rn(__fmul_rn(x0, c[j].y), __fmul_rn(x1, c[j].x));
+            }
+            if (pairing) {
+                bf16* o = j < 4 ? out_lo : out_hi;
+                o[(2 * j) & 7] = __float2bfloat16_rn(y0);
+                o[(2 * j + 1) & 7] = __float2bfloat16_rn(y1);
+            } else {
+                out_lo[j] = __float2bfloat16_rn(y0);
+                out_hi[j] = __float2bfloat16_rn(y1);
+            }
+        }
+        if (pairing) {
+            *reinterpret_cast<uint4*>(dst + 2 * i) = *reinterpret_cast<const uint4*>(out_lo);
+            *reinterpret_cast<uint4*>(dst + 2 * i + 8) = *reinterpret_cast<const uint4*>(out_hi);
+        } else {
+            *reinterpret_cast<uint4*>(dst + i) = *reinterpret_cast<const uint4*>(out_lo);
+            *reinterpret_cast<uint4*>(dst + i + half) = *reinterpret_cast<const uint4*>(out_hi);
+        }
+    }
+}
+
 // ------------------------------------------------------------------------------ launchers
 static int pick_threads(int n, int cap = 256) {
     int t = 32;
@@ -294,6 +372,14 @@ static int pick_threads(int n, int cap = 256) {
         BC_CHECK_ARG(pairing == 0 || pairing == 1, "rope_append: pairing %d is neither 0 (half) nor 1 (adjacent)", pairing);     \
         if (rows == 0) return BC_OK;                                                                                             \
         BC_CHECK_ARG(H + 2 * G <= 65535, "rope_append: too many heads (%d)", H + 2 * G);                                          \
+        if (sizeof(T) == 2 && rows > 64 && D % 16 == 0) {                                                                        \
+            /* many rows (prompts): eight pairs a thread, 32 heads of a row a block */                                           \
+            const int wx = D / 16 < 32 ? D / 16 : 32, wy = 256 / wx < H + 2 * G ? 256 / wx : H + 2 * G;                          \
+            bc_launch(rope_append_wide_kernel, dim3(rows, (H + 2 * G + wy - 1) / wy), dim3(wx, wy), 0, s, (bf16*)qkv,              \
+                      (const float2*)cos_sin, row_pos, row_slot, page_table, (bf16*)k_cache, (bf16*)v_cache, H, G, D, pairing,     \
+                      max_pages, n_pages, write_cache);                                                                          \
+            BC_LAUNCH_STATUS();                                                                                                  \
+        }                                                                                                                        \
         /* few rows (decoding): a block a head, for the shortest critical path; many rows: eight heads a block */                \
         const int tx = pick_threads(D / 8, 32), ty = rows <= 64 ? 1 : 8;                                         \
         bc_launch(rope_append_kernel<T>, dim3(rows, (H + 2 * G + ty - 1) / ty), dim3(tx, ty), 0, s, (T*)qkv,                       \

@@ -157,6 +157,41 @@ def test_rope_append(dtype, pairing):
     assert np.array_equal(vp, expect_v)
 
 
+@pytest.mark.parametrize("H,G,D", [(6, 3, 48), (4, 4, 16), (32, 8, 128), (5, 1, 64)])
+@pytest.mark.parametrize("pairing", [0, 1])
+def test_rope_append_of_many_rows_gives_the_bits_of_few_rows(H, G, D, pairing):
+    """Prompts of bf16 take a kernel with wider accesses (more than 64 rows a launch): the
+    same rows fed 50 at a time go through the narrow kernel and must leave the same bits in
+    q and in both caches; padding rows stay untouched."""
+    from borrowed_compute_b200 import ops
+    from borrowed_compute_b200.parts.rope import inverse_frequencies, rotary_table
+
+    rows, n_pages, max_pages = 150, 12, 4
+    r = rng(H + D + pairing)
+    slot = r.integers(0, 3, rows).astype(np.int32)
+    slot[[3, 77, 149]] = -1
+    pos = np.zeros(rows, dtype=np.int32)
+    seen = {0: 0, 1: 0, 2: 0}
+    for i in range(rows):
+        if slot[i] >= 0:
+            pos[i] = seen[int(slot[i])]
+            seen[int(slot[i])] += 1
+    table = np.array([[4, 7, 2, 9], [1, 8, 3, 0], [5, 10, 11, 6]], dtype=np.int32)
+    qkv = r.standard_normal((rows, (H + 2 * G) * D)).astype(np.float32)
+    cos_sin = rotary_table(inverse_frequencies(D, 10000.0, None), 256).cuda()
+    results = []
+    for chunk in (rows, 50):
+        qd = dev(qkv, torch.bfloat16)
+        k_pages = torch.zeros((n_pages, G, 64, D), dtype=torch.bfloat16, device="cuda")
+        v_pages = torch.zeros_like(k_pages)
+        for a in range(0, rows, chunk):
+            ops.rope_append(qd[a:a + chunk], cos_sin, dev(pos[a:a + chunk]), dev(slot[a:a + chunk]), dev(table), k_pages, v_pages, H, G, D, pairing)
+        results.append((qd, k_pages, v_pages))
+    for wide, narrow, what in zip(results[0], results[1], ("q", "k cache", "v cache")):
+        assert torch.equal(wide, narrow), what
+    assert torch.equal(results[0][0][[3, 77, 149]], dev(qkv, torch.bfloat16)[[3, 77, 149]]), "a padding row was touched"
+
+
 def attention_reference(q, k, v, window=0):
     """q [H, D] at the last position of k, v [T, G, D]."""
     H, D = q.shape
