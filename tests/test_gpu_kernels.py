@@ -370,6 +370,26 @@ def test_attention_decode(H, G, D, splits, window):
     assert (out.float() - twin.float()).abs().max().item() <= 2.0 ** -6
 
 
+def test_tcgen05_prompt_attention_refuses_what_it_cannot_do():
+    """Head sizes other than 64 and 128, and a q that is not 16-byte aligned, are for the
+    mma.sync kernel: the chooser says so, and forcing the tcgen05 kernel is a clear error."""
+    from borrowed_compute_b200 import ops
+
+    assert ops.attention_prefill_tc_accepts(32, 8, 128) and ops.attention_prefill_tc_accepts(10, 2, 64)
+    assert not ops.attention_prefill_tc_accepts(6, 2, 48) and not ops.attention_prefill_tc_accepts(8, 3, 64)
+    H, G, D = 6, 2, 48
+    q = torch.zeros((4, H * D), dtype=torch.bfloat16, device="cuda")
+    k = torch.zeros((2, G, 64, D), dtype=torch.bfloat16, device="cuda")
+    ints = lambda *v: torch.tensor(v, dtype=torch.int32, device="cuda")
+    with pytest.raises(ops.KernelError, match="head size 64 or 128"):
+        ops.attention_prefill(q, H * D, k, k.clone(), ints(0, 1).reshape(1, 2), ints(0, 4), ints(0), ints(0), torch.empty_like(q), 1, 4,
+                              H, G, D, use_tc=True)
+    H, G, D = 4, 2, 64
+    buf = torch.zeros((4 * H * D + 8,), dtype=torch.bfloat16, device="cuda")
+    shifted = buf[4:4 + 4 * H * D].reshape(4, H * D)                      # 8 bytes off a 16-byte boundary
+    assert not ops.attention_prefill_tc_accepts(H, G, D, shifted, H * D)
+
+
 def run_attention_prefill(H, G, D, window, use_tc, cached, new, q_scale=1.5):
     """One launch of a prompt kernel over sequences that bring new[s] rows after cached[s]
     positions (with a padding sequence among them), against the float64 formula at chosen
