@@ -26,7 +26,7 @@ def llama_model_spec(cfg: LlamaConfig) -> ModelSpec:
     for l in range(cfg.num_hidden_layers):
         p = f"model.layers.{l}."
         layers.append(LayerSpec(
-            block="prenorm",
+            "prenorm",
             norm1=PartSpec("rmsnorm", {"size": cfg.hidden_size, "eps": cfg.rms_norm_eps}, p + "input_layernorm."),
             mixer=PartSpec("gqa_attention", {
                 "hidden_size": cfg.hidden_size, "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,

@@ -1,11 +1,11 @@
 """The cache on the device: pages of keys and values per storage group, page tables that
 mirror the host's bookkeeping, and per-sequence state of fixed size.
 
-Runs of layers whose mixers need the same memory (kv heads, head size, window) form one
-*group* with storage of its own:
+Runs of layers whose mixers need the same memory (the same planes of values a position,
+the same window) form one *group* with storage of its own:
 
-    pages  [runs in the group, 2 (keys, values), pages, kv_heads, 64, head_dim]
-    table  [slots, pages a sequence can have] int32, -1 where no page is held
+    planes[i]  [runs in the group, pages, heads_i, 64, width_i]   (keys and values are two planes)
+    table      [slots, pages a sequence can have] int32, -1 where no page is held
 
 A mixer that asks for state gets one tensor [slots, *shape] for its run, zeroed whenever a
 slot is handed out.  The reference's cache is one f32 buffer per layer and conversation
@@ -27,7 +27,7 @@ from .slots import PAGE, GroupPlan, SlotTable, pages_for
 class _Group:
     need: CacheNeed
     runs: List[int]                 # schedule entries that own a line of this group
-    pages: Optional[torch.Tensor] = None
+    planes: Optional[List[torch.Tensor]] = None
     table: Optional[torch.Tensor] = None
     host_table: Optional[torch.Tensor] = None
 
@@ -57,8 +57,8 @@ class PagedCache:
         self.n_pages = n_pages
         self.slots = SlotTable(n_slots, n_pages, max_seq, [GroupPlan(g.need.window) for g in self.groups])
         for g in self.groups:
-            shape = (len(g.runs), 2, n_pages, g.need.kv_heads, PAGE, g.need.head_dim)
-            g.pages = torch.zeros(shape, dtype=rt.dtype, device=rt.device)
+            g.planes = [torch.zeros((len(g.runs), n_pages, heads, PAGE, width), dtype=rt.dtype, device=rt.device)
+                        for heads, width in g.need.planes]
             g.host_table = torch.full((n_slots, self.slots.max_pages), -1, dtype=torch.int32).pin_memory() \
                 if rt.device.type == "cuda" else torch.full((n_slots, self.slots.max_pages), -1, dtype=torch.int32)
             g.table = torch.full((n_slots, self.slots.max_pages), -1, dtype=torch.int32, device=rt.device)
@@ -103,14 +103,14 @@ class PagedCache:
         if owner in self._line:
             g, line = self._line[owner]
             grp = self.groups[g]
-            mem.k_pages, mem.v_pages, mem.page_table = grp.pages[line, 0], grp.pages[line, 1], grp.table
+            mem.planes, mem.page_table = tuple(t[line] for t in grp.planes), grp.table
         if owner in self.state:
             mem.state = self.state[owner]
         return mem
 
     def bytes(self) -> int:
-        total = sum(g.pages.numel() * g.pages.element_size() for g in self.groups)
+        total = sum(t.numel() * t.element_size() for g in self.groups for t in g.planes)
         return total + sum(t.numel() * t.element_size() for t in self.state.values())
 
     def bytes_per_token(self) -> int:
-        return sum(len(g.runs) * 2 * g.need.kv_heads * g.need.head_dim * g.pages.element_size() for g in self.groups)
+        return sum(len(g.runs) * g.need.values_per_token() * g.planes[0].element_size() for g in self.groups)

@@ -161,6 +161,26 @@ class SlotTable:
             if dropped or more > 0:
                 self._write_row(g, slot, pages)
 
+    def reserve_many(self, requests: Sequence[tuple]) -> None:
+        """``reserve`` for several slots, all or nothing: ``requests`` holds (slot, new_len,
+        rows) of distinct slots; what all of them need together is counted against every
+        pool before any page moves, so a refusal leaves the bookkeeping as it was."""
+        need = [0] * len(self.groups)
+        for slot, new_len, rows in requests:
+            st = self._held(slot)
+            if new_len > self.max_seq:
+                raise CacheError(f"slot {slot} would reach {new_len} positions, the cache holds {self.max_seq} a sequence")
+            if new_len < st.length:
+                raise CacheError(f"slot {slot} holds {st.length} positions, reserve cannot shrink it to {new_len}")
+            for g, pages in enumerate(st.pages):
+                need[g] += pages_for(new_len) - len(pages) - self._releasable(g, pages, new_len, rows)
+        for g, n in enumerate(need):
+            if n > self.pools[g].available:
+                raise CacheError(f"the cache is full: this step needs {n} more pages of {PAGE} tokens in group {g}, "
+                                 f"{self.pools[g].available} are free")
+        for slot, new_len, rows in requests:
+            self.reserve(slot, new_len, rows)
+
     def _releasable(self, g: int, pages: List[int], new_len: int, rows: int) -> int:
         first = self._first_needed_page(g, new_len, rows)
         return sum(1 for p in pages[:first] if p >= 0)
@@ -175,19 +195,27 @@ class SlotTable:
         """Cuts a sequence back to ``new_len`` positions (the reference does so by writing
         at an earlier position, crates/bc-infer/src/model.rs:321-322).  Groups that keep
         only a window may have dropped what lies before it; those refuse."""
+        self.check_rollback(slot, new_len)
         st = self._held(slot)
-        if not 0 <= new_len <= st.length:
-            raise CacheError(f"slot {slot} holds {st.length} positions, cannot go back to {new_len}")
         keep = pages_for(new_len)
-        for g, pages in enumerate(st.pages):
-            if any(p < 0 for p in pages[:keep]):
-                raise CacheError(f"slot {slot}: group {g} keeps a window and no longer holds the positions before it")
         for g, pages in enumerate(st.pages):
             if len(pages) > keep:
                 self.pools[g].give_back([p for p in pages[keep:] if p >= 0])
                 del pages[keep:]
                 self._write_row(g, slot, pages)
         st.length = new_len
+
+    def check_rollback(self, slot: int, new_len: int) -> None:
+        """Raises if ``rollback(slot, new_len)`` would be refused; changes nothing."""
+        st = self._held(slot)
+        if not 0 <= new_len <= st.length:
+            raise CacheError(f"slot {slot} holds {st.length} positions, cannot go back to {new_len}")
+        keep = pages_for(new_len)
+        for g, pages in enumerate(st.pages):
+            # The next row, at position new_len, looks back a window: the pages from there on must still be held.
+            first = self._first_needed_page(g, new_len + 1, 1)
+            if any(p < 0 for p in pages[first:keep]):
+                raise CacheError(f"slot {slot}: group {g} keeps a window and no longer holds the positions before it")
 
     def _write_row(self, g: int, slot: int, pages: List[int]) -> None:
         row = self.tables[g][slot]

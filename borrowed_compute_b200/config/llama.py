@@ -8,7 +8,6 @@ the head count (model.rs:60), the head size to hidden / heads (51), the rope bas
 
 from __future__ import annotations
 
-import math
 from dataclasses import dataclass, field
 from typing import Any, Mapping, Optional, Tuple
 
@@ -42,10 +41,9 @@ def _get(d: Mapping[str, Any], key: str, kind, default=None, required: bool = Fa
 
 @dataclass(frozen=True)
 class Llama3RopeScaling:
-    """The llama3 rule for long contexts: low frequencies are slowed by ``factor``.
-
-    The reference only divides each frequency by a stored per-pair factor
-    (model.rs:208-211); this rule is what produces those factors.
+    """The four numbers of config.json's ``rope_scaling`` object for the llama3 rule (low
+    frequencies are slowed by ``factor``).  The rule itself belongs to the rotary part,
+    which takes these numbers as plain parameters.
     """
 
     factor: float
@@ -78,17 +76,6 @@ class Llama3RopeScaling:
             "high_freq_factor": self.high_freq_factor,
             "original_max_position_embeddings": self.original_max_position_embeddings,
         }
-
-    def scale_frequency(self, f: float) -> float:
-        """The frequency that replaces ``f`` (radians per position)."""
-        wavelen = 2.0 * math.pi / f
-        orig = float(self.original_max_position_embeddings)
-        if wavelen < orig / self.high_freq_factor:
-            return f
-        if wavelen > orig / self.low_freq_factor:
-            return f / self.factor
-        t = (orig / wavelen - self.low_freq_factor) / (self.high_freq_factor - self.low_freq_factor)
-        return (1.0 - t) * f / self.factor + t * f
 
 
 @dataclass(frozen=True)

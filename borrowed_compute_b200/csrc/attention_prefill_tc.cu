@@ -443,7 +443,7 @@ static int g_apt_sms() {
     if (sms == 0) {
         int dev = 0;
         cudaGetDevice(&dev);
-        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = bc_sm_count();
     }
     return sms;
 }
@@ -488,14 +488,6 @@ extern "C" int bc_attention_prefill_tc_bf16(const void* q, int q_stride, int tot
 #undef APT_GO
 }
 
-// This unit's status word: 0, or where a bounded wait gave up.  Reading it waits for the
-// device; `reset` clears it.
-extern "C" int bc_attention_prefill_tc_status(int reset) {
-    int v = 0;
-    cudaMemcpyFromSymbol(&v, g_tc_status, sizeof(int));
-    if (reset && v != 0) {
-        int zero = 0;
-        cudaMemcpyToSymbol(g_tc_status, &zero, sizeof(int));
-    }
-    return v;
-}
+// This unit's status word (0, or where a bounded wait gave up), its wait limit and its word
+// of host memory: bc_attention_prefill_tc_status / _set_wait_cycles / _bind_host_word.
+TC_STATUS_EXPORTS(attention_prefill_tc)

@@ -17,6 +17,7 @@
 #define BC_PAGE 64
 
 void bc_set_error(const char* fmt, ...);
+extern "C" int bc_sm_count();   // streaming multiprocessors of the current device
 
 #define BC_CHECK_ARG(cond, ...)        \
     do {                               \

@@ -52,6 +52,7 @@ struct TcParams {
     int clustered;      // split-K: the splits of a tile are one thread-block cluster and add up through shared memory
     int n_tiles, t_tiles;   // blocks along the weight rows and along the tokens
     int pair_tokens;        // the paired kernel: tokens a tile (64, 128, 192 or 256)
+    int starve;             // test hook: the first stage expects 16 bytes that never come, so a bounded wait runs out
 };
 
 // Blocks that run at the same time should share operands: the block index walks up to
@@ -78,6 +79,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     __shared__ __align__(8) uint64_t bars[2 * 16 + 1];
     __shared__ uint32_t tmem_slot;
+    __shared__ int gave_up;   // a wait of this block ran out: nothing is written, the block only tears down
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int stages = p.stages;
@@ -93,6 +95,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[16]), acc_bar = smem_u32(&bars[32]);
 
     if (threadIdx.x == 0) {
+        gave_up = 0;
         for (int s = 0; s < stages; s++) {
             mbar_init(full0 + 8 * s, 1);
             mbar_init(empty0 + 8 * s, 1);
@@ -119,7 +122,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             };
             for (int i = 0; i < ahead; i++) {
                 const uint32_t a = smem_u32(smem + (size_t)i * STAGE_BYTES);
-                mbar_expect_tx(full0 + 8 * i, STAGE_BYTES);
+                mbar_expect_tx(full0 + 8 * i, STAGE_BYTES + (p.starve && i == 0 ? 16 : 0));
                 const int k = (k_first + i) * TC_BK;
                 load_w(a, full0 + 8 * i, k, n0);
                 if (N_ACC == 2) load_w(a + A_BYTES, full0 + 8 * i, k, second_row);
@@ -131,7 +134,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             }
             for (int i = ahead; i < k_iters; i++) {
                 const int s = i % stages;
-                if (!mbar_wait(empty0 + 8 * s, ((i / stages) & 1) ^ 1, 1)) break;
+                if (!mbar_wait(empty0 + 8 * s, ((i / stages) & 1) ^ 1, 1)) {
+                    *reinterpret_cast<volatile int*>(&gave_up) = 1;
+                    break;
+                }
                 const uint32_t a = smem_u32(smem + (size_t)s * STAGE_BYTES);
                 mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
                 const int k = (k_first + i) * TC_BK;
@@ -159,7 +165,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 }
                 mma_commit(empty0 + 8 * s);
             }
-            mma_commit(acc_bar);
+            if (!ok) {
+                *reinterpret_cast<volatile int*>(&gave_up) = 1;
+                __threadfence_block();
+            }
+            mma_commit(acc_bar);   // also after a wait that ran out: the epilogue warps must not be left waiting
         }
     } else {
         // Epilogue: this warp reads TMEM lanes 32 q .. 32 q + 31, i.e. weight rows n0 + 32 q + lane.
@@ -176,7 +186,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         int* counter = split ? p.counters + (size_t)tile * 4 + q : nullptr;
         bool ok = true;
         pdl_wait();   // the output, the scratch and the counters may still be in use by the preceding kernel
-        if (lane == 0) ok = mbar_wait(acc_bar, 0, 3);
+        if (lane == 0) ok = mbar_wait(acc_bar, 0, 3) && *reinterpret_cast<volatile int*>(&gave_up) == 0;
         ok = __shfl_sync(0xffffffffu, ok, 0);
         tc_fence_after();
         const uint32_t taddr = tmem + ((uint32_t)(32 * q) << 16);
@@ -740,7 +750,10 @@ extern "C" int bc_gemm_tc_token_tile(int T, int epilogue) {
 // number of blocks; it is used unless that leaves the last wave of blocks much emptier.
 static int g_tc_stack = -1;   // tuning knob for measurements: -1 decide here, 0 never, 1 always
 extern "C" void bc_gemm_tc_set_stack(int mode) { g_tc_stack = mode; }
-static double wave_fill(long long blocks) { return (double)blocks / (double)(((blocks + 147) / 148) * 148); }
+static double wave_fill(long long blocks) {
+    const long long sms = bc_sm_count();
+    return (double)blocks / (double)(((blocks + sms - 1) / sms) * sms);
+}
 extern "C" int bc_gemm_tc_rows_per_block(int T, int N, int epilogue) {
     const int bn = bc_gemm_tc_token_tile(T, epilogue);
     if (bn != 256 || epilogue == EPI_SWIGLU || g_tc_stack == 0) return TC_BM;
@@ -760,6 +773,14 @@ extern "C" int bc_gemm_tc_workspace(int T, int N, int epilogue, int splits, long
     *ints = splits > 1 ? tiles * 4 : 0;
     return BC_OK;
 }
+
+// Test hook: the next launch of the one-block kernel (at most 128 tokens) arms its first
+// stage for 16 bytes more than it loads, so that a bounded wait of that launch runs out,
+// the blocks tear down, and the status word names the wait.  Nothing faults or hangs; with
+// the wait limit set to a millisecond or so the launch returns at once.  The output of such
+// a launch is left unwritten.
+static int g_tc_starve = 0;
+extern "C" void bc_gemm_tc_test_starve_next_launch() { g_tc_starve = 1; }
 
 // X [T, K] bf16, W [N, K] bf16 (SwiGLU: [2N, K], gate rows then up rows); out [T, N] bf16 or
 // float by epilogue.  K must be a multiple of 8 (a TMA row stride is a multiple of 16
@@ -794,6 +815,8 @@ extern "C" int bc_gemm_tc_bf16(const void* X, const void* W, void* out, int T, i
     p.k_iters_per_split = 0;
     p.n_tiles = p.t_tiles = p.clustered = 0;
     p.pair_tokens = 256;
+    p.starve = paired ? 0 : g_tc_starve;
+    if (!paired) g_tc_starve = 0;
     if (paired) {
         switch (epilogue) {
             case EPI_STORE: return launch_pair<EPI_STORE>(mw, mx, p, s);
@@ -811,14 +834,6 @@ extern "C" int bc_gemm_tc_bf16(const void* X, const void* W, void* out, int T, i
     return BC_ERR_ARG;
 }
 
-// The status word of the tensor-core kernels: 0, or where a bounded wait gave up.  Reading
-// it waits for the device; `reset` clears it.
-extern "C" int bc_gemm_tc_status(int reset) {
-    int v = 0;
-    cudaMemcpyFromSymbol(&v, g_tc_status, sizeof(int));
-    if (reset && v != 0) {
-        int zero = 0;
-        cudaMemcpyToSymbol(g_tc_status, &zero, sizeof(int));
-    }
-    return v;
-}
+// This unit's status word (0, or where a bounded wait gave up), its wait limit and its word
+// of host memory: bc_gemm_tc_status / _set_wait_cycles / _bind_host_word.
+TC_STATUS_EXPORTS(gemm_tc)

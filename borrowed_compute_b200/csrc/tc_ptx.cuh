@@ -13,12 +13,46 @@ enum { EPI_STORE = 0, EPI_STORE_F32 = 1, EPI_ADD_F32 = 2, EPI_SWIGLU = 3 };
 #define TC_BK 64           // k a stage: 64 bf16 = one 128-byte swizzle row
 #define TC_THREADS 192     // warp 0 TMA, warp 1 MMA, warps 2-5 epilogue
 #define TC_SMEM_LIMIT 230400   // dynamic bytes asked for at most; static barriers take a little more
-#define TC_WAIT_CYCLES 2000000000ll
+#define TC_WAIT_CYCLES 2000000000ll   // clocks a wait may take before it gives up: about a second
 
 // Status word: 0 while all is well, else (code << 16 | detail) of the first wait that gave up.
 // One copy a translation unit (the library builds without relocatable device code): every
-// unit that includes this header exports a reader of its own word.
+// unit that includes this header exports, with TC_STATUS_EXPORTS below, a reader of its own
+// word, a setter of its wait limit, and a binder of a word of host memory that the device
+// can write: the first wait that gives up leaves its code there too, so the host can look
+// after any synchronisation of its own without a copy from the device.
 static __device__ int g_tc_status = 0;
+static __device__ long long g_tc_wait_cycles = TC_WAIT_CYCLES;
+static __device__ int* g_tc_host_word = nullptr;
+
+__device__ __forceinline__ void tc_give_up(int code) {
+    const int v = (code << 16) | (int)(blockIdx.x & 0xffff);
+    if (atomicCAS(&g_tc_status, 0, v) == 0) {
+        int* host = g_tc_host_word;
+        if (host) {
+            *reinterpret_cast<volatile int*>(host) = v;
+            __threadfence_system();
+        }
+    }
+}
+
+#define TC_STATUS_EXPORTS(NAME)                                                                                  \
+    extern "C" int bc_##NAME##_status(int reset) {                                                               \
+        int v = 0;                                                                                               \
+        cudaMemcpyFromSymbol(&v, g_tc_status, sizeof(int));                                                      \
+        if (reset && v != 0) {                                                                                   \
+            int zero = 0;                                                                                        \
+            cudaMemcpyToSymbol(g_tc_status, &zero, sizeof(int));                                                 \
+        }                                                                                                        \
+        return v;                                                                                                \
+    }                                                                                                            \
+    extern "C" int bc_##NAME##_set_wait_cycles(long long cycles) {                                               \
+        if (cycles <= 0) cycles = TC_WAIT_CYCLES;                                                                \
+        return (int)cudaMemcpyToSymbol(g_tc_wait_cycles, &cycles, sizeof(cycles));                               \
+    }                                                                                                            \
+    extern "C" int bc_##NAME##_bind_host_word(int* device_pointer_to_host_word) {                                \
+        return (int)cudaMemcpyToSymbol(g_tc_host_word, &device_pointer_to_host_word, sizeof(int*));              \
+    }
 
 // ------------------------------------------------------------------------------ PTX pieces
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -42,14 +76,15 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// Waits for a phase of a barrier, at most about a second.  False (and a recorded status)
-// if it gave up; the caller then stops doing work but still reaches the teardown.
+// Waits for a phase of a barrier, at most the wait limit (about a second unless set
+// otherwise).  False (and a recorded status) if it gave up; the caller then stops doing work
+// but still reaches the teardown.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int code) {
     if (mbar_try_wait(bar, parity)) return true;
-    const long long start = clock64();
+    const long long start = clock64(), limit = g_tc_wait_cycles;
     while (!mbar_try_wait(bar, parity)) {
-        if (clock64() - start > TC_WAIT_CYCLES) {
-            atomicCAS(&g_tc_status, 0, (code << 16) | (int)(blockIdx.x & 0xffff));
+        if (clock64() - start > limit) {
+            tc_give_up(code);
             return false;
         }
     }

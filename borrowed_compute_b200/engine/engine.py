@@ -99,8 +99,11 @@ class _DecodeGraph:
         return self.engine.model.forward(ctx, self.engine.cache, v["want_rows"], rows)
 
     def run(self, packed: np.ndarray) -> torch.Tensor:
-        self._upload(packed)
         if self.graph is None:
+            # Warm-up and capture run on padding rows only (every slot -1), which change nothing
+            # that outlives the step: the real rows then run exactly once, in the replay below.
+            # A mixer that keeps state of its own would otherwise see its first step twice.
+            self._upload(self.pack(None, [], [], 0))
             self._forward()   # once eagerly: first-use set-up must not happen inside a capture
             torch.cuda.synchronize()
             # Nothing may free device memory or destroy another graph while this one is being
@@ -117,6 +120,7 @@ class _DecodeGraph:
                 if was_enabled:
                     gc.enable()
             self.graph = graph
+        self._upload(packed)
         self.graph.replay()
         return self.scores
 
@@ -144,7 +148,7 @@ class Engine:
         self._graphs: Dict[int, "_DecodeGraph"] = {}
         self._ahead: Optional[_Ahead] = None
         # Decode steps replay a captured CUDA graph unless a part plans on the host.
-        self.use_graphs = all(part.graph_safe for _, part in model._named_parts())
+        self.use_graphs = all(part.graph_safe for _, part in model.named_parts())
         self.steps_run = 0
 
     # ------------------------------------------------------------------------ construction
@@ -158,6 +162,9 @@ class Engine:
         if not torch.cuda.is_available():
             raise RuntimeError("no CUDA device is available; there is no CPU path")
         ops.lib()  # fail now, and loudly, if the kernels cannot be had
+        with torch.cuda.device(dev):
+            ops.bind_status(dev)
+            ops.self_check(dev)   # once a device: every product against float64 sums, before anything is trusted to it
         return Runtime(device=dev, dtype=DTYPES[dtype])
 
     @classmethod
@@ -186,19 +193,24 @@ class Engine:
 
     @classmethod
     def from_random(cls, config: Mapping[str, Any], seed: int, dtype="bfloat16", device="cuda:0",
-                    max_tokens: Optional[int] = None, max_slots: Optional[int] = None, max_seq: Optional[int] = None) -> "Engine":
-        """Random weights drawn on the device, without a folder (other values than a
-        folder written from the same seed holds: the device's generator differs)."""
+                    max_tokens: Optional[int] = None, max_slots: Optional[int] = None, max_seq: Optional[int] = None,
+                    stored_dtype=None) -> "Engine":
+        """Random weights drawn on the device, without a folder: the same values, to the
+        bit, as a folder written from the same configuration and seed holds.  ``stored_dtype``
+        is the type that folder would store (default: ``dtype``); a float32 engine over
+        values stored as bfloat16 is what the plain implementation is compared with."""
+        from ..weights.loader import device_type
+
         typed, model = model_for_config(config)
         rt = cls._runtime(dtype, device)
+        stored = rt.dtype if stored_dtype is None else DTYPES[stored_dtype]
         eng = cls._sized(config, model, typed, rt, max_tokens, max_slots, max_seq)
-        expected = model.expected_tensors()
         tensors = {}
-        for name, spec in expected.items():
+        for name, spec in model.expected_tensors().items():
             if spec.optional:
                 continue
-            want = torch.float32 if spec.role == "vector" else (torch.int32 if spec.role == "index" else rt.dtype)
-            tensors.update(random_tensors({name: spec}, seed, want, rt.device))
+            t = random_tensors({name: spec}, seed, stored, rt.device)[name]
+            tensors[name] = t.to(device_type(spec, t.dtype, rt))
         model.load(tensors, rt)
         return eng
 
@@ -231,8 +243,31 @@ class Engine:
         return self.cache.slots.length(slot)
 
     def rollback(self, slot: int, length: int) -> None:
-        """Cuts a sequence back to ``length`` positions; the next step writes from there."""
+        """Cuts a sequence back to ``length`` positions; the next step writes from there.
+
+        Token-indexed memory goes back by its length.  Per-sequence state has already
+        absorbed the dropped positions: a cut to 0 clears it (that is the state of a new
+        sequence); any other cut asks each mixer that keeps state to restore it
+        (``Mixer.rollback_state``) and is refused with a CacheError, leaving everything as it
+        was, unless all of them can."""
         self._ahead = None
+        have = self.cache.slots.length(slot)
+        if not 0 <= length <= have:
+            raise CacheError(f"slot {slot} holds {have} positions, cannot go back to {length}")
+        if length == have:
+            return
+        self.cache.slots.check_rollback(slot, length)
+        saved = {run: state[slot].clone() for run, state in self.cache.state.items()}
+        for run, state in self.cache.state.items():
+            if length == 0:
+                state[slot].zero_()
+                continue
+            mixer = self.model.blocks[self.model.spec.schedule[run].layer].memory_part()
+            if not mixer.rollback_state(state, slot, length):
+                for r, old in saved.items():
+                    self.cache.state[r][slot].copy_(old)
+                raise CacheError(f"slot {slot} cannot go back to {length} positions: the mixer of run {run} keeps per-sequence "
+                                 f"state and cannot restore it (only a cut to 0 is always possible)")
         self.cache.slots.rollback(slot, length)
 
     # -------------------------------------------------------------------------------- step
@@ -289,7 +324,7 @@ class Engine:
             g = self._graphs[bucket] = _DecodeGraph(self, bucket)
         return g
 
-    def _decode_graph_step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+    def _decode_graph_step(self, entries: Sequence[StepEntry], borrow_scores: bool) -> torch.Tensor:
         """A step of one token a sequence, replayed from a CUDA graph captured once per
         padded batch size: the kernels, their order and their buffers are fixed, only the
         integers that name tokens, positions and slots change.
@@ -311,12 +346,13 @@ class Engine:
             packed[:n] = tokens
         else:
             starts = self.check_entries(entries)
-            for slot, start in zip(slots, starts):
-                self.cache.slots.reserve(slot, start + 1, rows=1)
+            self.cache.slots.reserve_many([(slot, start + 1, 1) for slot, start in zip(slots, starts)])
             g = self._graph_for(n)
             packed = g.pack(tokens, starts, slots, n)
         self.cache.sync_tables()
         scores = g.run(packed)[:n]
+        if not borrow_scores:
+            scores = scores.clone()
         for slot, start in zip(slots, starts):
             self.cache.slots.commit(slot, start + 1)
         self.steps_run += 1
@@ -324,28 +360,34 @@ class Engine:
         try:
             nxt = [start + 1 for start in starts]
             if max(nxt) + 1 <= self.max_seq:
-                for slot, start in zip(slots, nxt):
-                    self.cache.slots.reserve(slot, start + 1, rows=1)
+                self.cache.slots.reserve_many([(slot, start + 1, 1) for slot, start in zip(slots, nxt)])
                 self.cache.sync_tables()
                 self._ahead = _Ahead(slots, nxt, g, g.pack(None, nxt, slots, n))
         except CacheError:
             self._ahead = None   # the step itself will say what is wrong, if it comes
         return scores
 
-    def step(self, entries: Sequence[StepEntry], pad_rows_to: int = 1) -> torch.Tensor:
+    def step(self, entries: Sequence[StepEntry], pad_rows_to: int = 1, borrow_scores: bool = False) -> torch.Tensor:
         """Runs the given tokens of every entry as one batch from the cache and returns
         the scores [wanted, vocab] (float32, on the device) at the wanted places, in entry
         order then ``want`` order.  ``pad_rows_to`` adds rows that belong to no sequence;
-        they change no result."""
+        they change no result.
+
+        The returned tensor is the caller's own.  With ``borrow_scores`` a decode step may
+        instead return a view of the one buffer its captured graph writes: valid until the
+        next call of ``step``, which overwrites it in place (the generation loop samples
+        from it at once and saves the copy).
+
+        A step that is refused (a bad token, a slot not held or named twice, a wanted index
+        outside its tokens, a full cache) raises before anything is reserved or run."""
         if self.use_graphs and pad_rows_to == 1 and entries and all(len(e.tokens) == 1 and tuple(e.want) == (0,) for e in entries) \
                 and len({e.slot for e in entries}) == len(entries):
-            return self._decode_graph_step(entries)
+            return self._decode_graph_step(entries, borrow_scores)
         self._ahead = None
         starts = self.check_entries(entries)
-        for e, start in zip(entries, starts):
-            self.cache.slots.reserve(e.slot, start + len(e.tokens), rows=len(e.tokens))
+        plan = plan_step(entries, starts, pad_rows_to)    # its checks (a slot twice, a wanted index) come before any reservation
+        self.cache.slots.reserve_many([(e.slot, start + len(e.tokens), len(e.tokens)) for e, start in zip(entries, starts)])
         self.cache.sync_tables()
-        plan = plan_step(entries, starts, pad_rows_to)
         v = self._stage(plan)
         ctx = StepContext(
             rows=plan.padded_rows, seqs=plan.seqs, tokens=v["tokens"], row_pos=v["row_pos"], row_slot=v["row_slot"],
@@ -358,10 +400,16 @@ class Engine:
         self.steps_run += 1
         return scores
 
+    def raise_on_kernel_error(self) -> None:
+        """For callers that have just synchronised with the device (read scores or token ids
+        back): raises ops.KernelError if a kernel of an earlier step gave up on a bounded
+        wait, in which case that step's results are not valid.  Costs a read of host memory."""
+        ops.check_status(self.rt.device)
+
     # ---------------------------------------------------------------------------- accounts
     def weight_bytes(self) -> int:
         seen, total = set(), 0
-        for _, part in self.model._named_parts():
+        for _, part in self.model.named_parts():
             for v in vars(part).values():
                 if isinstance(v, torch.Tensor) and v.data_ptr() not in seen:
                     seen.add(v.data_ptr())

@@ -142,7 +142,9 @@ class EngineBackend(Backend):
             n = len(positions)
             self._host_steps[:n] = torch.tensor(positions, dtype=torch.int32)
             self._steps[:n].copy_(self._host_steps[:n], non_blocking=True)
-        return self.sampler.sample(scores, self._steps).tolist()
+        ids = self.sampler.sample(scores, self._steps).tolist()   # the step's one synchronisation with the device
+        self.engine.raise_on_kernel_error()
+        return ids
 
     def start(self, indices, prompts, samplings) -> List[int]:
         entries = []
@@ -165,7 +167,7 @@ class EngineBackend(Backend):
         entries = [StepEntry(self._slot[i], (int(t),), want=(0,)) for i, t in zip(indices, tokens)]
         positions = [self.engine.length(self._slot[i]) for i in indices]
         self._set_rows(indices)
-        scores = self.engine.step(entries)
+        scores = self.engine.step(entries, borrow_scores=True)   # sampled from at once, below
         return self._sample(scores, positions)
 
     def finish(self, index: int) -> None:

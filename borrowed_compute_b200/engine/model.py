@@ -10,8 +10,8 @@ import torch
 
 from ..architectures import resolve
 from ..parts import base as P
-from ..parts.base import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, POSITION_ENCODINGS, CacheNeed, ModelSpec, PartSpec,
-                          Runtime, StateNeed, StepContext, TensorSpec)
+from ..parts.base import (BLOCKS, EMBEDDINGS, HEADS, NORMS, POSITION_ENCODINGS, CacheNeed, ModelSpec, PartSpec, Runtime, StateNeed,
+                          StepContext, TensorSpec)
 
 
 def _build(registry: P.Registry, spec: PartSpec):
@@ -28,46 +28,40 @@ class DecoderModel:
                 raise ValueError(f"schedule entry {i} reads the memory of entry {run.memory_of}, which is not an earlier owner")
         self.embedding = _build(EMBEDDINGS, spec.embedding)
         self.position = None if spec.position is None else _build(POSITION_ENCODINGS, spec.position)
-        self.blocks = []
-        for layer in spec.layers:
-            block_cls = BLOCKS.get(layer.block)
-            self.blocks.append(block_cls(_build(NORMS, layer.norm1), _build(MIXERS, layer.mixer), _build(NORMS, layer.norm2),
-                                         _build(FEED_FORWARDS, layer.feed_forward), spec.hidden_size))
+        self.blocks = [BLOCKS.get(layer.block).build(layer, spec.hidden_size) for layer in spec.layers]
         self.final_norm = _build(NORMS, spec.final_norm)
         self.head = _build(HEADS, spec.head)
         self.rt: Optional[Runtime] = None
 
-    def _named_parts(self):
+    def named_parts(self):
+        """(tensor-name prefix, part) of every part of the model; each block lists its own."""
         yield self.spec.embedding.prefix, self.embedding
         if self.position is not None:
             yield self.spec.position.prefix, self.position
         for layer, block in zip(self.spec.layers, self.blocks):
-            yield layer.norm1.prefix, block.norm1
-            yield layer.mixer.prefix, block.mixer
-            yield layer.norm2.prefix, block.norm2
-            yield layer.feed_forward.prefix, block.feed_forward
+            yield from block.named_parts(layer)
         yield self.spec.final_norm.prefix, self.final_norm
         yield self.spec.head.prefix, self.head
 
     def expected_tensors(self) -> Dict[str, TensorSpec]:
         out: Dict[str, TensorSpec] = {}
-        for prefix, part in self._named_parts():
+        for prefix, part in self.named_parts():
             for name, spec in part.tensors().items():
                 out[prefix + name] = spec
         return out
 
     def load(self, tensors: Mapping[str, torch.Tensor], rt: Runtime) -> None:
         self.rt = rt
-        for prefix, part in self._named_parts():
+        for prefix, part in self.named_parts():
             mine = {name: tensors[prefix + name] for name in part.tensors() if prefix + name in tensors}
             part.load(mine, rt)
 
     def memory_needs(self) -> Tuple[List[Optional[CacheNeed]], List[Optional[StateNeed]], List[Optional[int]]]:
         needs, states, memory_of = [], [], []
         for run in self.spec.schedule:
-            mixer = self.blocks[run.layer].mixer
-            needs.append(mixer.cache_need())
-            states.append(mixer.state_need())
+            mixer = self.blocks[run.layer].memory_part()
+            needs.append(None if mixer is None else mixer.cache_need())
+            states.append(None if mixer is None else mixer.state_need())
             memory_of.append(run.memory_of)
         return needs, states, memory_of
 

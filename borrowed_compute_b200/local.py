@@ -51,7 +51,9 @@ class Local:
             raise ValueError(f"position {pos} skips past the {have} cached tokens")
         if pos < have:
             self.engine.rollback(self._slot, pos)
-        return self.engine.step([StepEntry(self._slot, list(tokens), want=tuple(range(len(tokens))))]).cpu()
+        out = self.engine.step([StepEntry(self._slot, list(tokens), want=tuple(range(len(tokens))))]).cpu()
+        self.engine.raise_on_kernel_error()
+        return out
 
     def reset(self) -> None:
         if self._slot is not None:

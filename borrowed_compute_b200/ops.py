@@ -183,6 +183,15 @@ def rope_append(qkv: torch.Tensor, cos_sin: Optional[torch.Tensor], row_pos: tor
           _c_int(page_table.shape[1]), _c_int(n_pages), _c_int(1 if write_cache else 0), _stream())
 
 
+def random_normal(out: torch.Tensor, key: int, std: float) -> None:
+    """out[i] = std * z(key, i) over out's elements in memory order: z a standard normal
+    deviate that depends on the 64-bit key and the index alone (weights/random_init.py has
+    the host's mirror, which gives the same bits)."""
+    _need(out, "out")
+    _call(_fn("bc_random_normal_" + _suffix(out.dtype)), _ptr(out), ctypes.c_longlong(out.numel()), ctypes.c_ulonglong(key & ((1 << 64) - 1)),
+          _c_float(std), _stream())
+
+
 # ---------------------------------------------------------------------------------- products
 
 def gemm_simt(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int) -> None:
@@ -202,8 +211,13 @@ def gemm_simt(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int
     _call(_fn("bc_gemm_simt_" + _suffix(x.dtype)), _ptr(x), _ptr(w), _ptr(out), _c_int(M), _c_int(N), _c_int(K), _c_int(epilogue), _stream())
 
 
+def sm_count() -> int:
+    """Streaming multiprocessors of the current device, as the kernel library sees them."""
+    return int(_fn("bc_sm_count")())
+
+
 _tc_workspace = {}
-TC_SCRATCH_FLOATS = 148 * 256 * 256   # split-K partial tiles: room for one 256 x 256 tile a block on every SM
+TC_SCRATCH_FLOATS = 148 * 256 * 256   # split-K partial tiles: a capacity of 37 MiB (148 tiles of 256 x 256 floats), whatever the device
 
 
 def _tc_scratch(device: torch.device):
@@ -230,10 +244,11 @@ def _tc_tiling(T: int, N: int, epilogue: int):
 
 def gemm_tc_splits(T: int, N: int, K: int, epilogue: int) -> int:
     """How many ways to split K so that a product with few weight tiles still fills the
-    device's 148 SMs: as many as fit, each at least 8 k-steps of 64."""
+    device's SMs: as many as fit, each at least 8 k-steps of 64."""
     bn, rows, tiles = _tc_tiling(T, N, epilogue)
     if tiles == 0:
         return 1
+    sms = sm_count()
     accs = 2 if epilogue == EPI_SWIGLU else 1              # SwiGLU keeps gate and up sums apart until the last split
     fits = TC_SCRATCH_FLOATS // (tiles * accs * rows * bn)   # splits whose partial tiles fit the scratch
     if epilogue == EPI_SWIGLU:
@@ -243,14 +258,14 @@ def gemm_tc_splits(T: int, N: int, K: int, epilogue: int) -> int:
     if bn <= 64:
         # Few tokens: the product streams weights, two blocks fit an SM, and measured rates keep
         # rising up to about two blocks an SM as long as a split still has 8 k-steps of 64.
-        s = max(1, min(296 // tiles, -(-K // 64) // 8, 16, fits))
+        s = max(1, min(2 * sms // tiles, -(-K // 64) // 8, 16, fits))
         # Up to eight splits add up inside a thread-block cluster, which saves the trip through
         # scratch memory; clusters of 2, 4 or 8 place well on the SMs, other sizes measured
         # up to 5 us slower.  So a count up to 12 is rounded down to a power of two.
         if s <= 12:
             s = 1 << (min(s, 8).bit_length() - 1)
         return s
-    return max(1, min(148 // tiles, -(-K // 64) // 8, 16, fits))
+    return max(1, min(sms // tiles, -(-K // 64) // 8, 16, fits))
 
 
 def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int, splits: Optional[int] = None) -> None:
@@ -286,6 +301,119 @@ def gemm_tc_status(reset: bool = True) -> int:
     """Waits for the device and returns the tensor-core kernels' status word: 0, or
     (code << 16 | block) of the first bounded wait that gave up."""
     return int(_fn("bc_gemm_tc_status")(_c_int(1 if reset else 0)))
+
+
+def set_wait_cycles(cycles: int = 0) -> None:
+    """The most clocks a bounded wait inside the tensor-core kernels may take before it gives
+    up and records its status (0: back to the default, about a second)."""
+    for unit in ("gemm_tc", "attention_prefill_tc"):
+        st = _fn(f"bc_{unit}_set_wait_cycles")(ctypes.c_longlong(int(cycles)))
+        if st != 0:
+            raise KernelError(f"setting the wait limit of {unit} failed ({st})")
+
+
+def gemm_tc_test_starve_next_launch() -> None:
+    """Test hook: the next product of at most 128 tokens waits for bytes that never come, so
+    that one of its bounded waits runs out (see csrc/gemm_tc.cu).  Its output stays unwritten."""
+    lib().bc_gemm_tc_test_starve_next_launch()
+
+
+# ------------------------------------------------------------ errors that reach the caller
+
+_STATUS_UNITS = ("the tensor-core product (gemm_tc)", "the tcgen05 prompt attention (attention_prefill_tc)")
+_WAITS = {
+    0: {1: "the loader's wait for a free stage", 2: "the wait for a stage's operands", 3: "the epilogue's wait for the accumulator",
+        4: "the wait for the epilogue to hand the accumulator back"},
+    1: {1: "the loader's wait for a free stage", 2: "the wait for the queries", 3: "the wait for the first pages", 4: "the wait for P",
+        5: "the wait for a page", 6: "the softmax's wait for scores", 7: "the wait for a product that frees P", 8: "the wait for the last product",
+        9: "the wait before a rescale"},
+}
+_bound_devices = set()
+
+
+def bind_status(device: Optional[torch.device] = None) -> None:
+    """Gives the kernels of ``device`` their words of host-visible memory (once a device), so
+    that check_status can look without waiting for the device."""
+    index = torch.cuda.current_device() if device is None or device.index is None else device.index
+    if index in _bound_devices:
+        return
+    with torch.cuda.device(index):
+        _call(_fn("bc_status_bind"))
+    _bound_devices.add(index)
+
+
+def check_status(device: Optional[torch.device] = None) -> None:
+    """Raises KernelError if a bounded wait of a kernel gave up since the last look.  Costs a
+    read of host memory; meaningful after the caller has synchronised with the device (the
+    word is written by the kernel that gave up, before it ends).  The word is cleared, so
+    the next look reports only what happens after this one."""
+    index = torch.cuda.current_device() if device is None or device.index is None else device.index
+    if index not in _bound_devices:
+        return
+    peek = _fn("bc_status_peek")
+    with torch.cuda.device(index):
+        for unit, name in enumerate(_STATUS_UNITS):
+            word = int(peek(_c_int(unit), _c_int(1)))
+            if word != 0:
+                code, block = word >> 16, word & 0xFFFF
+                raise KernelError(f"{name}: {_WAITS[unit].get(code, 'a wait')} (code {code}) ran out in block {block}; "
+                                  f"what that launch should have written is missing, so this step's results are not valid")
+
+
+_self_checked = set()
+
+
+def self_check(device: torch.device) -> None:
+    """Once a device and process: every epilogue of the tensor-core product, and the CUDA-core
+    product, on a 37 x 512 weight with one row and with three, against float64 sums, as the
+    reference checks its products before it trusts a GPU (crates/bc-infer/src/gpu/mod.rs:
+    181-206, same sizes, same inputs rule, same 1e-3 (1 + |want|) bound; there a failure means
+    the CPU serves, here there is no other path, so it raises)."""
+    import numpy as np
+
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    if index in _self_checked:
+        return
+    rows_w, cols = 37, 512
+    rng = np.random.default_rng(7)
+    w = rng.standard_normal((2 * rows_w, cols)).astype(np.float32) * 0.5
+    wb = torch.from_numpy(w).to(device=device, dtype=torch.bfloat16)
+    w64 = wb.float().cpu().numpy().astype(np.float64)
+
+    def bad(got: torch.Tensor, want: np.ndarray, rel: float = 1e-3) -> bool:
+        g = got.float().cpu().numpy().astype(np.float64)
+        return (not np.isfinite(g).all()) or bool((np.abs(g - want) > rel * (1.0 + np.abs(want))).any())
+
+    rounded = 2.0 ** -7    # an output that is itself rounded to bfloat16 carries half an ulp of 2^-8 besides
+    for n in (1, 3):       # one row and a batch take different paths
+        x = (((np.arange(n * cols) * 31 % 97).astype(np.float32) - 48.0) / 50.0).reshape(n, cols)
+        xb = torch.from_numpy(x).to(device=device, dtype=torch.bfloat16)
+        x64 = xb.float().cpu().numpy().astype(np.float64)
+        full = x64 @ w64.T                                                    # [n, 74]: gate rows, then up rows
+        gate, up = full[:, :rows_w], full[:, rows_w:]
+        for name, product in (("tensor-core", gemm_tc), ("CUDA-core", gemm_simt)):
+            stored = torch.empty((n, 2 * rows_w), dtype=torch.bfloat16, device=device)
+            product(xb, wb, stored, EPI_STORE)
+            scores = torch.empty((n, 2 * rows_w), dtype=torch.float32, device=device)
+            product(xb, wb, scores, EPI_STORE_F32)
+            added = torch.full((n, 2 * rows_w), 0.25, dtype=torch.float32, device=device)
+            product(xb, wb, added, EPI_ADD_F32)
+            gated = torch.empty((n, rows_w), dtype=torch.bfloat16, device=device)
+            product(xb, wb, gated, EPI_SWIGLU)
+            checks = {"store": bad(stored, full, rounded), "store_f32": bad(scores, full), "add_f32": bad(added, full + 0.25),
+                      "swiglu": bad(gated, gate / (1.0 + np.exp(-gate)) * up, rounded)}
+            wrong = [k for k, v in checks.items() if v]
+            if wrong:
+                raise KernelError(f"self-check: the {name} product with {n} row(s) is wrong for the epilogue(s) {wrong} on a "
+                                  f"{rows_w} x {cols} weight; this device or this build of the kernels cannot be trusted")
+    x = (((np.arange(3 * cols) * 31 % 97).astype(np.float32) - 48.0) / 50.0).reshape(3, cols)
+    scores = torch.empty((3, 2 * rows_w), dtype=torch.float32, device=device)
+    gemm_simt(torch.from_numpy(x).to(device), torch.from_numpy(w).to(device), scores, EPI_STORE_F32)
+    if bad(scores, x.astype(np.float64) @ w.astype(np.float64).T):
+        raise KernelError("self-check: the float32 CUDA-core product is wrong; this device or this build of the kernels cannot be trusted")
+    torch.cuda.synchronize(device)
+    check_status(device)
+    _self_checked.add(index)
 
 
 def set_attention_prefill_tc_tiles(n: int) -> None:
@@ -336,14 +464,15 @@ def attention_decode_accepts(heads: int, kv_heads: int, head_dim: int, dtype: to
 
 def attention_decode_splits(rows: int, kv_heads: int, max_pages: int) -> int:
     """Splits of the cached positions so that rows * kv_heads * splits blocks come close to,
-    and stay within, one wave of two blocks on each of 148 SMs; never more than a sequence
+    and stay within, one wave of two blocks on each SM; never more than a sequence
     can have pages.  Up to eight splits merge inside a thread-block cluster, which costs
     about 4 us less than the merge through scratch memory; so eight is the cap unless the
     batch is so small that eight leave most SMs idle and sequences can grow so long (beyond
     256 pages) that each split's share of the keys outweighs the dearer merge."""
     blocks = max(1, rows * kv_heads)
-    fill = max(1, min(296 // blocks, max_pages, 64))
-    if fill <= 8 or blocks * 8 >= 148 or max_pages <= 256:
+    sms = sm_count()
+    fill = max(1, min(2 * sms // blocks, max_pages, 64))
+    if fill <= 8 or blocks * 8 >= sms or max_pages <= 256:
         return min(fill, 8)
     return fill
 

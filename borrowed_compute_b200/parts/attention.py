@@ -43,7 +43,7 @@ class GroupedQueryAttention(Mixer):
         }
 
     def cache_need(self) -> Optional[CacheNeed]:
-        return CacheNeed(self.kv_heads, self.head_dim, self.window)
+        return CacheNeed.keys_values(self.kv_heads, self.head_dim, self.window)
 
     def load(self, tensors: Dict[str, torch.Tensor], rt: Runtime) -> None:
         super().load(tensors, rt)

@@ -76,13 +76,22 @@ class PartSpec:
     prefix: str = ""
 
 
-@dataclass(frozen=True)
 class LayerSpec:
-    block: str
-    norm1: PartSpec
-    mixer: PartSpec
-    norm2: PartSpec
-    feed_forward: PartSpec
+    """One layer: the block that arranges it and the block's parts by the role each plays
+    in it.  Which roles a block has (and which registry builds each) is the block's own
+    business (``Block.ROLES``): ``LayerSpec("prenorm", norm1=..., mixer=..., norm2=...,
+    feed_forward=...)`` for the built-in block, other names for another."""
+
+    def __init__(self, block: str, parts: Optional[Mapping[str, PartSpec]] = None, **named: PartSpec):
+        self.block = block
+        self.parts: Dict[str, PartSpec] = dict(parts or {})
+        self.parts.update(named)
+        for role, spec in self.parts.items():
+            if not isinstance(spec, PartSpec):
+                raise TypeError(f"layer part '{role}' must be a PartSpec, got {type(spec).__name__}")
+
+    def __repr__(self) -> str:
+        return f"LayerSpec({self.block!r}, {self.parts!r})"
 
 
 @dataclass(frozen=True)
@@ -148,16 +157,31 @@ class Runtime:
 
 @dataclass
 class CacheNeed:
-    """Token-indexed memory a mixer wants for each cached position: keys and values of
-    ``kv_heads`` heads of ``head_dim``; ``window`` > 0 if only that many latest positions
-    are ever read.  Runs with equal needs share one storage group."""
+    """Token-indexed memory a mixer wants for each cached position, as planes: plane i
+    keeps ``planes[i] = (heads, width)`` values of the compute type a position, stored a
+    page of 64 positions at a time as [pages, heads, 64, width].  Attention asks for two
+    equal planes (keys, values); a mixer that caches one latent vector a token asks for
+    one plane (1, width); planes may differ in shape.  ``window`` > 0 if only that many
+    latest positions are ever read.  Runs with equal needs share one storage group."""
 
-    kv_heads: int
-    head_dim: int
+    planes: Tuple[Tuple[int, int], ...]
     window: int = 0
 
-    def key(self) -> Tuple[int, int, int]:
-        return (self.kv_heads, self.head_dim, self.window)
+    def __post_init__(self):
+        self.planes = tuple((int(h), int(w)) for h, w in self.planes)
+        if not self.planes or any(h <= 0 or w <= 0 for h, w in self.planes):
+            raise ValueError(f"a cache need wants at least one plane of positive sizes, got {self.planes}")
+
+    @staticmethod
+    def keys_values(kv_heads: int, head_dim: int, window: int = 0) -> "CacheNeed":
+        """Keys and values of ``kv_heads`` heads of ``head_dim`` a position."""
+        return CacheNeed(((kv_heads, head_dim), (kv_heads, head_dim)), window)
+
+    def key(self) -> Tuple:
+        return (self.planes, self.window)
+
+    def values_per_token(self) -> int:
+        return sum(h * w for h, w in self.planes)
 
 
 @dataclass
@@ -173,11 +197,19 @@ class StateNeed:
 class RunMemory:
     """What one run of a layer may read and write in the cache this step."""
 
-    k_pages: Optional[torch.Tensor] = None      # [pages, kv_heads, PAGE, head_dim]
-    v_pages: Optional[torch.Tensor] = None
+    planes: Tuple[torch.Tensor, ...] = ()       # one [pages, heads, PAGE, width] tensor per plane of the mixer's CacheNeed
     page_table: Optional[torch.Tensor] = None   # [slots, max_pages] int32
     state: Optional[torch.Tensor] = None        # [slots, *StateNeed.shape]
     writes: bool = True                         # False when reading another run's memory
+
+    @property
+    def k_pages(self) -> Optional[torch.Tensor]:
+        """The first plane: keys, for a mixer that asked for keys and values."""
+        return self.planes[0] if self.planes else None
+
+    @property
+    def v_pages(self) -> Optional[torch.Tensor]:
+        return self.planes[1] if len(self.planes) > 1 else None
 
 
 @dataclass
@@ -258,8 +290,22 @@ class Mixer(Part):
     def state_need(self) -> Optional[StateNeed]:
         return None
 
+    def rollback_state(self, state: torch.Tensor, slot: int, length: int) -> bool:
+        """A sequence is cut back to ``length`` positions.  Token-indexed memory goes back
+        by its length alone, but per-sequence state has already absorbed the positions that
+        are dropped.  A mixer that can put ``state[slot]`` back to what it was after
+        ``length`` positions (from snapshots of its own, or because the state can be
+        rebuilt) does so and returns True.  The default, False, makes the engine refuse the
+        cut with a CacheError, so that state from the future is never left in place."""
+        return False
+
     def forward(self, x: torch.Tensor, residual: torch.Tensor, ctx: StepContext, mem: RunMemory) -> None:
-        """residual[:rows] += mix(x); x is [rows, hidden] in the compute type."""
+        """residual[:rows] += mix(x); x is [rows, hidden] in the compute type.
+
+        A mixer with ``graph_safe = True`` is replayed from a captured graph on decode
+        steps.  The engine warms the step up and captures it with every row marked as
+        padding (slot -1), so a forward must leave memory and state untouched for such rows;
+        real rows then run exactly once a step."""
         raise NotImplementedError
 
 
@@ -286,11 +332,37 @@ class Head(Part):
 
 
 class Block(Part):
-    """Arranges two norms, a mixer and a feed-forward around the residual stream."""
+    """Arranges parts around the residual stream.  ``ROLES`` names the parts a block is
+    made of and the registry that builds each; a LayerSpec must give exactly these.  The
+    built parts are attributes of the block under their role names."""
 
-    def __init__(self, norm1: Norm, mixer: Mixer, norm2: Norm, feed_forward: FeedForward, hidden_size: int):
+    ROLES: Dict[str, Registry] = {}
+
+    def __init__(self, parts: Mapping[str, Part], hidden_size: int):
         super().__init__()
-        self.norm1, self.mixer, self.norm2, self.feed_forward, self.hidden_size = norm1, mixer, norm2, feed_forward, hidden_size
+        self.parts: Dict[str, Part] = dict(parts)
+        self.hidden_size = hidden_size
+        for role, part in self.parts.items():
+            setattr(self, role, part)
+
+    @classmethod
+    def build(cls, spec: LayerSpec, hidden_size: int) -> "Block":
+        missing = [r for r in cls.ROLES if r not in spec.parts]
+        unexpected = [r for r in spec.parts if r not in cls.ROLES]
+        if missing or unexpected:
+            raise ValueError(f"block '{spec.block}' is made of {sorted(cls.ROLES)}; missing {sorted(missing)}, unexpected {sorted(unexpected)}")
+        return cls({role: cls.ROLES[role].get(spec.parts[role].kind)(**dict(spec.parts[role].params)) for role in cls.ROLES}, hidden_size)
+
+    def named_parts(self, spec: LayerSpec):
+        """(tensor-name prefix, part) of every part of this block, in the order of ROLES."""
+        for role in self.ROLES:
+            yield spec.parts[role].prefix, self.parts[role]
+
+    def memory_part(self) -> Optional[Mixer]:
+        """The part whose cache_need() / state_need() the cache serves for a run of this
+        block, and that receives the run's RunMemory: its mixer, if it has one."""
+        part = self.parts.get("mixer")
+        return part if isinstance(part, Mixer) else None
 
     def forward(self, residual: torch.Tensor, ctx: StepContext, mem: RunMemory, rt: Runtime) -> None:
         raise NotImplementedError

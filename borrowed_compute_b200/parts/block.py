@@ -5,11 +5,13 @@ from __future__ import annotations
 
 import torch
 
-from .base import BLOCKS, Block, RunMemory, Runtime, StepContext
+from .base import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, Block, RunMemory, Runtime, StepContext
 
 
 @BLOCKS.register("prenorm")
 class PreNormBlock(Block):
+    ROLES = {"norm1": NORMS, "mixer": MIXERS, "norm2": NORMS, "feed_forward": FEED_FORWARDS}
+
     def forward(self, residual: torch.Tensor, ctx: StepContext, mem: RunMemory, rt: Runtime) -> None:
         h = torch.empty((residual.shape[0], self.hidden_size), dtype=rt.dtype, device=residual.device)
         self.norm1.forward(residual, h)

@@ -135,3 +135,44 @@ def test_random_traffic_keeps_the_books():
         t.release(s)
     t.check()
     assert all(p.available == 40 for p in t.pools) and t.free_slots == 5
+
+
+def test_reserving_for_several_slots_is_all_or_nothing():
+    t = SlotTable(n_slots=3, n_pages=4, max_seq=512, groups=[GroupPlan(), GroupPlan(window=70)])
+    a, b, c = t.acquire(), t.acquire(), t.acquire()
+    before = ([list(r) for r in t.tables[0]], [p.available for p in t.pools])
+    # a wants 2 pages, b wants 3: each alone would fit the 4 pages, together they do not
+    with pytest.raises(CacheError, match="full"):
+        t.reserve_many([(a, 128, 128), (b, 192, 192)])
+    assert ([list(r) for r in t.tables[0]], [p.available for p in t.pools]) == before and not t.dirty
+    t.check()
+    # a slot that is not held, or a length that shrinks, refuses the whole request too
+    with pytest.raises(CacheError, match="not held"):
+        t.reserve_many([(a, 64, 64), (99, 64, 64)])
+    assert [p.available for p in t.pools] == [4, 4]
+    t.reserve_many([(a, 128, 128), (b, 64, 64), (c, 1, 1)])
+    for s, n in ((a, 128), (b, 64), (c, 1)):
+        t.commit(s, n)
+    assert [p.available for p in t.pools] == [0, 0]
+    # what a windowed group gives back behind its window counts as room for the same request
+    t.release(b), t.release(c)
+    t.reserve_many([(a, 256, 1)])          # one more row at position 255: the window no longer reaches the first pages
+    t.commit(a, 256)
+    assert sum(p >= 0 for p in t.tables[1][a]) == 2 and sum(p >= 0 for p in t.tables[0][a]) == 4
+    t.check()
+
+
+def test_check_rollback_changes_nothing():
+    t = SlotTable(n_slots=1, n_pages=8, max_seq=512, groups=[GroupPlan(), GroupPlan(window=70)])
+    s = t.acquire()
+    t.reserve(s, 300, rows=300)
+    t.commit(s, 300)
+    t.reserve(s, 301, rows=1)
+    t.commit(s, 301)
+    t.check_rollback(s, 301)
+    with pytest.raises(CacheError, match="window"):
+        t.check_rollback(s, 100)
+    with pytest.raises(CacheError, match="cannot go back"):
+        t.check_rollback(s, 302)
+    assert t.length(s) == 301
+    t.check()

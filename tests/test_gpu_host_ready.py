@@ -1,0 +1,479 @@
+"""What another architecture would need of the framework, shown with toy parts defined
+here and never in the package: a mixer with state of its own that is replayed from the
+captured decode graph; cuts back refused or restored by the mixer; a block made of another
+set of parts; a mixer whose cached memory is one latent vector a position; attention with
+a window through the engine; the lifetime of a step's scores; and a refused step that
+leaves the cache's bookkeeping as it was."""
+
+from __future__ import annotations
+
+import json
+import os
+
+import numpy as np
+import pytest
+
+import plain_llama
+from conftest import seeded_tokens
+
+pytestmark = pytest.mark.gpu
+
+torch = pytest.importorskip("torch")
+
+HID, VOCAB, MAXPOS = 48, 90, 320
+
+
+def _register():
+    from borrowed_compute_b200.architectures import register_architecture
+    from borrowed_compute_b200.config import LlamaConfig
+    from borrowed_compute_b200.parts import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, Block, CacheNeed, LayerSpec, Mixer, ModelSpec, PartSpec,
+                                             RunSpec, StateNeed, TensorSpec)
+
+    if "toy_device_mean" not in MIXERS.names():
+        @MIXERS.register("toy_device_mean")
+        class DeviceMean(Mixer):
+            """out[row] = mean of this sequence's inputs up to and including row, times W^T.
+            The running sum is per-sequence state.  A decode step touches the device only
+            (graph_safe), a prompt loops over its sequences on the host (prompts are never
+            captured)."""
+
+            def __init__(self, hidden_size, snapshots=0):
+                super().__init__(hidden_size=hidden_size, snapshots=snapshots)
+                self.hidden_size, self.snapshots = hidden_size, snapshots
+
+            def tensors(self):
+                return {"mix.weight": TensorSpec((self.hidden_size, self.hidden_size))}
+
+            def state_need(self):
+                # row 0: the running sum; rows 1..: (with snapshots) the sum after each position
+                return StateNeed((1 + self.snapshots, self.hidden_size), torch.float32)
+
+            def load(self, tensors, rt):
+                super().load(tensors, rt)
+                self.w = tensors["mix.weight"].float()
+
+            def rollback_state(self, state, slot, length):
+                if not self.snapshots or length > self.snapshots:
+                    return False
+                state[slot, 0] = state[slot, length]     # the sum after `length` positions
+                return True
+
+            def forward(self, x, residual, ctx, mem):
+                rows = x.shape[0]
+                xf = x.float()
+                pos = ctx.row_pos[:rows].long()
+                if ctx.decode:
+                    slot = ctx.row_slot[:rows].long()
+                    live = (slot >= 0).float()[:, None]
+                    idx = slot.clamp(min=0)
+                    if mem.writes:
+                        mem.state[:, 0].index_add_(0, idx, xf * live)       # padding rows add zero to slot 0
+                    run = mem.state[idx, 0]
+                    if self.snapshots and mem.writes:
+                        keep = (pos + 1).clamp(max=self.snapshots)
+                        old = mem.state[idx, keep]
+                        mem.state[idx, keep] = torch.where(live > 0, run, old)
+                    residual[:rows] += ((run / (pos.float() + 1.0)[:, None]) @ self.w.T) * live
+                    return
+                for s in range(ctx.seqs):
+                    a, b, slot = ctx.host_seq_rows[s], ctx.host_seq_rows[s + 1], ctx.host_seq_slot[s]
+                    if slot < 0 or a == b:
+                        continue
+                    run = mem.state[slot, 0][None, :] + torch.cumsum(xf[a:b], dim=0)
+                    if mem.writes:
+                        mem.state[slot, 0] = run[-1]
+                        if self.snapshots:
+                            mem.state[slot, pos[a:b] + 1] = run
+                    residual[a:b] += (run / (pos[a:b].float() + 1.0)[:, None]) @ self.w.T
+
+    if "toy_latent_memory" not in MIXERS.names():
+        @MIXERS.register("toy_latent_memory")
+        class LatentMemory(Mixer):
+            """Caches ONE latent vector a position (c = x Wc^T, in one plane of the paged
+            cache) and returns the mean of the cached latents up to the row, times Wo^T."""
+
+            graph_safe = False
+
+            def __init__(self, hidden_size, latent):
+                super().__init__(hidden_size=hidden_size, latent=latent)
+                self.hidden_size, self.latent = hidden_size, latent
+
+            def tensors(self):
+                return {"c.weight": TensorSpec((self.latent, self.hidden_size)), "o.weight": TensorSpec((self.hidden_size, self.latent))}
+
+            def cache_need(self):
+                return CacheNeed(((1, self.latent),))
+
+            def load(self, tensors, rt):
+                super().load(tensors, rt)
+                self.wc, self.wo = tensors["c.weight"].float(), tensors["o.weight"].float()
+
+            def forward(self, x, residual, ctx, mem):
+                (plane,) = mem.planes                                         # [pages, 1, 64, latent]
+                c = x.float() @ self.wc.T
+                for s in range(ctx.seqs):
+                    a, b, slot, start = ctx.host_seq_rows[s], ctx.host_seq_rows[s + 1], ctx.host_seq_slot[s], ctx.host_seq_start[s]
+                    if slot < 0 or a == b:
+                        continue
+                    table = mem.page_table[slot].long()
+                    pos = torch.arange(start, start + b - a, device=x.device)
+                    if mem.writes:
+                        plane[table[pos // 64], 0, pos % 64] = c[a:b].to(plane.dtype)
+                    every = torch.arange(0, start + b - a, device=x.device)
+                    cached = plane[table[every // 64], 0, every % 64].float()
+                    run = torch.cumsum(cached, dim=0)[start:]
+                    residual[a:b] += (run / (pos.float() + 1.0)[:, None]) @ self.wo.T
+
+    if "toy_parallel" not in BLOCKS.names():
+        @BLOCKS.register("toy_parallel")
+        class ParallelBlock(Block):
+            """One norm; the mixer and the feed-forward both read it: x += mix(n(x)) + ff(n(x))."""
+
+            ROLES = {"norm": NORMS, "mixer": MIXERS, "feed_forward": FEED_FORWARDS}
+
+            def forward(self, residual, ctx, mem, rt):
+                h = torch.empty((residual.shape[0], self.hidden_size), dtype=rt.dtype, device=residual.device)
+                self.norm.forward(residual, h)
+                self.mixer.forward(h, residual, ctx, mem)
+                self.feed_forward.forward(h, residual, ctx)
+
+    def common(cfg, layers, schedule):
+        norm = PartSpec("rmsnorm", {"size": cfg.hidden_size, "eps": cfg.rms_norm_eps}, "out_norm.")
+        return ModelSpec(hidden_size=cfg.hidden_size, vocab_size=cfg.vocab_size, max_positions=cfg.max_position_embeddings,
+                         embedding=PartSpec("token_embedding", {"vocab_size": cfg.vocab_size, "hidden_size": cfg.hidden_size}, "emb."),
+                         layers=tuple(layers), schedule=tuple(RunSpec(i) for i in schedule), final_norm=norm,
+                         head=PartSpec("linear_head", {"vocab_size": cfg.vocab_size, "hidden_size": cfg.hidden_size, "tied": True}, "head."))
+
+    def norm(cfg, p):
+        return PartSpec("rmsnorm", {"size": cfg.hidden_size, "eps": cfg.rms_norm_eps}, p)
+
+    def ff(cfg, p):
+        return PartSpec("swiglu", {"hidden_size": cfg.hidden_size, "intermediate_size": cfg.intermediate_size}, p)
+
+    def attention(cfg, p, window=0):
+        position = {"kind": "rotary", "head_dim": cfg.head_dim, "theta": cfg.rope_theta, "pairing": cfg.rope_pairing, "scaling": None,
+                    "max_positions": cfg.max_position_embeddings}
+        return PartSpec("gqa_attention", {"hidden_size": cfg.hidden_size, "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
+                                          "head_dim": cfg.head_dim, "position": position, "window": window}, p)
+
+    def mean_spec(snapshots):
+        def spec(cfg):
+            layers = [LayerSpec("prenorm", norm1=norm(cfg, "l0.n1."), mixer=attention(cfg, "l0.attn."), norm2=norm(cfg, "l0.n2."),
+                                feed_forward=ff(cfg, "l0.ff.")),
+                      LayerSpec("prenorm", norm1=norm(cfg, "l1.n1."),
+                                mixer=PartSpec("toy_device_mean", {"hidden_size": cfg.hidden_size, "snapshots": snapshots}, "l1."),
+                                norm2=norm(cfg, "l1.n2."), feed_forward=ff(cfg, "l1.ff."))]
+            return common(cfg, layers, (0, 1))
+        return spec
+
+    def parallel_spec(cfg):
+        layers = [LayerSpec("toy_parallel", norm=norm(cfg, "l0.n."), mixer=attention(cfg, "l0.attn."), feed_forward=ff(cfg, "l0.ff.")),
+                  LayerSpec("toy_parallel", norm=norm(cfg, "l1.n."),
+                            mixer=PartSpec("toy_latent_memory", {"hidden_size": cfg.hidden_size, "latent": 24}, "l1.mem."),
+                            feed_forward=ff(cfg, "l1.ff."))]
+        return common(cfg, layers, (0, 1))
+
+    def windowed_spec(cfg):
+        layers = [LayerSpec("prenorm", norm1=norm(cfg, f"l{i}.n1."), mixer=attention(cfg, f"l{i}.attn.", window=70 if i == 0 else 0),
+                            norm2=norm(cfg, f"l{i}.n2."), feed_forward=ff(cfg, f"l{i}.ff.")) for i in range(2)]
+        return common(cfg, layers, (0, 1))
+
+    register_architecture("ToyDeviceMeanForCausalLM", LlamaConfig.from_dict, mean_spec(0))
+    register_architecture("ToySnapshotMeanForCausalLM", LlamaConfig.from_dict, mean_spec(MAXPOS))
+    register_architecture("ToyParallelForCausalLM", LlamaConfig.from_dict, parallel_spec)
+    register_architecture("ToyWindowedForCausalLM", LlamaConfig.from_dict, windowed_spec)
+
+
+def config(arch):
+    return {"architectures": [arch], "num_hidden_layers": 2, "hidden_size": HID, "num_attention_heads": 3, "num_key_value_heads": 1,
+            "head_dim": 16, "intermediate_size": 80, "vocab_size": VOCAB, "rope_theta": 10000.0, "rms_norm_eps": 1e-5,
+            "max_position_embeddings": MAXPOS}
+
+
+def build(tmp_path, arch, dtype="float32", seed=9, spread=0.2, **sizes):
+    """An engine over random weights for a toy architecture (matrices of the given
+    spread), and the weights as float64."""
+    from borrowed_compute_b200 import Engine
+    from borrowed_compute_b200.engine.model import expected_tensors_for_config
+    from borrowed_compute_b200.weights import write_safetensors
+
+    _register()
+    cfg = config(arch)
+    expected = expected_tensors_for_config(cfg)
+    r = np.random.default_rng(seed)
+    w = {k: ((1 + 0.1 * r.standard_normal(s.shape)) if s.role == "vector" else r.standard_normal(s.shape) * (1.0 if k == "emb.weight" else spread))
+         .astype(np.float32) for k, s in expected.items() if not s.optional}
+    folder = str(tmp_path / arch)
+    os.makedirs(folder, exist_ok=True)
+    json.dump(cfg, open(os.path.join(folder, "config.json"), "w"))
+    td = torch.float32 if dtype == "float32" else torch.bfloat16
+    write_safetensors(os.path.join(folder, "model.safetensors"), {k: torch.from_numpy(v).to(td) for k, v in w.items()})
+    eng = Engine.from_folder(folder, dtype=dtype, **{"max_tokens": 1024, "max_slots": 4, **sizes})
+    w64 = {k: torch.from_numpy(v).to(td).float().numpy().astype(np.float64) for k, v in w.items()}
+    return eng, w64
+
+
+def attention_layer(x, w, p, n1, n2, window=0, parallel=False):
+    """A toy layer with grouped-query attention in NumPy (3 heads on 1 kv head of 16)."""
+    n = x.shape[0]
+    inv = plain_llama.rope_inv_freq(16, 10000.0, None)
+    h = plain_llama.rms_norm(x, w[n1], 1e-5)
+    q = plain_llama.rope((h @ w[p + "attn.q_proj.weight"].T).reshape(n, 3, 16), range(n), inv, "half")
+    k = plain_llama.rope((h @ w[p + "attn.k_proj.weight"].T).reshape(n, 1, 16), range(n), inv, "half")
+    v = (h @ w[p + "attn.v_proj.weight"].T).reshape(n, 1, 16)
+    if window:
+        att = np.zeros((n, 3, 16))
+        for i in range(n):                       # row i sees positions max(0, i - window + 1) .. i
+            lo = max(0, i - window + 1)
+            for hd in range(3):
+                sc = k[lo:i + 1, 0] @ q[i, hd] / 4.0
+                pr = np.exp(sc - sc.max())
+                att[i, hd] = (pr / pr.sum()) @ v[lo:i + 1, 0]
+    else:
+        att = plain_llama.attention(q, k, v)
+    mixed = att.reshape(n, 48) @ w[p + "attn.o_proj.weight"].T
+    if parallel:
+        return x + mixed + plain_llama.swiglu(h, w[p + "ff.gate_proj.weight"], w[p + "ff.up_proj.weight"], w[p + "ff.down_proj.weight"])
+    x = x + mixed
+    h = plain_llama.rms_norm(x, w[n2], 1e-5)
+    return x + plain_llama.swiglu(h, w[p + "ff.gate_proj.weight"], w[p + "ff.up_proj.weight"], w[p + "ff.down_proj.weight"])
+
+
+def mean_reference(w, tokens):
+    n = len(tokens)
+    x = attention_layer(plain_llama.embed(w["emb.weight"], tokens), w, "l0.", "l0.n1.weight", "l0.n2.weight")
+    h = plain_llama.rms_norm(x, w["l1.n1.weight"], 1e-5)
+    x = x + (np.cumsum(h, axis=0) / np.arange(1, n + 1)[:, None]) @ w["l1.mix.weight"].T
+    h = plain_llama.rms_norm(x, w["l1.n2.weight"], 1e-5)
+    x = x + plain_llama.swiglu(h, w["l1.ff.gate_proj.weight"], w["l1.ff.up_proj.weight"], w["l1.ff.down_proj.weight"])
+    return plain_llama.rms_norm(x, w["out_norm.weight"], 1e-5) @ w["emb.weight"].T
+
+
+def close(got, ref, rel=2e-4):
+    err = np.abs(got - ref)
+    worst = np.unravel_index(int(err.argmax()), err.shape)
+    bound = rel * (1 + np.abs(ref).max())
+    assert err.max() <= bound, f"largest difference {err.max():.4g} at row {worst[0]}, column {worst[1]} (bound {bound:.4g}); " \
+                               f"first row over the bound: {int(np.argmax(err.max(axis=1) > bound))}"
+    return True
+
+
+def test_a_stateful_mixer_is_replayed_from_the_captured_graph(tmp_path):
+    """Decode steps of 1, 2 and 3 sequences (captured sizes 1, 2 and 4) with a mixer that
+    adds to per-sequence state every step: each size's first step runs its rows once, not
+    twice, and the replays agree with the plain whole-sequence run and with eager steps."""
+    from borrowed_compute_b200 import StepEntry
+
+    eng, w = build(tmp_path, "ToyDeviceMeanForCausalLM")
+    assert eng.use_graphs, "every part of this model says it can be captured"
+    seqs = [seeded_tokens(20 + i, n, VOCAB) for i, n in enumerate((40, 30, 21))]
+    refs = [mean_reference(w, s) for s in seqs]
+    prompt = (8, 5, 3)
+
+    def run(use_graphs):
+        eng.use_graphs = use_graphs
+        slots = [eng.acquire() for _ in seqs]
+        first = eng.step([StepEntry(s, t[:p], want=tuple(range(p))) for s, t, p in zip(slots, seqs, prompt)]).cpu().numpy()
+        got, at = [[] for _ in seqs], 0
+        for i, p in enumerate(prompt):
+            got[i].append(first[at:at + p])
+            at += p
+        live, step = [0, 1, 2], 0
+        while live:
+            entries = [StepEntry(slots[i], [seqs[i][prompt[i] + step]], want=(0,)) for i in live]
+            out = eng.step(entries).cpu().numpy()
+            for j, i in enumerate(live):
+                got[i].append(out[j:j + 1])
+            step += 1
+            for i in list(live):
+                if prompt[i] + step == len(seqs[i]):
+                    eng.release(slots[i])
+                    live.remove(i)          # 3 sequences, then 2, then 1: three captured sizes
+        return [np.concatenate(g) for g in got]
+
+    graphed = run(True)
+    assert sorted(eng._graphs) == [1, 2, 4]
+    eager = run(False)
+    for g, e, ref in zip(graphed, eager, refs):
+        assert close(g, ref) and close(e, ref)
+        assert np.array_equal(g, e), "a captured step computes what an eager step computes"
+    eng.cache.slots.check()
+
+
+def test_a_cut_back_is_refused_or_restored_by_the_mixer(tmp_path):
+    from borrowed_compute_b200 import CacheError, StepEntry
+
+    tokens = seeded_tokens(31, 60, VOCAB)
+    # no snapshots: only a cut to nothing is possible
+    eng, w = build(tmp_path, "ToyDeviceMeanForCausalLM")
+    ref = mean_reference(w, tokens)
+    s = eng.acquire()
+    eng.step([StepEntry(s, tokens[:40], want=())])
+    state_before = eng.cache.state[1][s].clone()
+    with pytest.raises(CacheError, match="per-sequence state"):
+        eng.rollback(s, 25)
+    assert eng.length(s) == 40 and torch.equal(eng.cache.state[1][s], state_before), "a refused cut changes nothing"
+    rest = eng.step([StepEntry(s, tokens[40:], want=tuple(range(20)))]).cpu().numpy()
+    assert close(rest, ref[40:])
+    eng.rollback(s, 0)
+    assert eng.length(s) == 0 and float(eng.cache.state[1][s].abs().max()) == 0.0
+    again = eng.step([StepEntry(s, tokens, want=tuple(range(60)))]).cpu().numpy()
+    assert close(again, ref), "after a cut to nothing the sequence starts anew"
+    eng.release(s)
+    # snapshots of its own: the mixer puts its state back, the cache drops the positions
+    eng2, w2 = build(tmp_path, "ToySnapshotMeanForCausalLM")
+    ref2 = mean_reference(w2, tokens)
+    other = tokens[:25] + seeded_tokens(32, 10, VOCAB)
+    ref_other = mean_reference(w2, other)
+    s = eng2.acquire()
+    eng2.step([StepEntry(s, tokens[:30], want=())])
+    for t in tokens[30:40]:
+        eng2.step([StepEntry(s, [t], want=(0,))])
+    eng2.rollback(s, 25)
+    assert eng2.length(s) == 25
+    got = eng2.step([StepEntry(s, other[25:], want=tuple(range(10)))]).cpu().numpy()
+    assert close(got, ref_other[25:]), "the state after a cut is the state of 25 positions"
+    eng2.rollback(s, 25)
+    got = np.concatenate([eng2.step([StepEntry(s, [t], want=(0,))]).cpu().numpy() for t in tokens[25:60]])
+    assert close(got, ref2[25:])
+    eng2.release(s)
+    eng2.cache.slots.check()
+
+
+def test_a_block_of_other_parts_and_a_latent_cache(tmp_path):
+    """A block with one norm and parallel branches, and a mixer that caches one latent
+    vector a position: both registered here, built from config.json, stepped whole, token
+    by token, and in a batch through slots that are used again."""
+    from borrowed_compute_b200 import StepEntry
+
+    eng, w = build(tmp_path, "ToyParallelForCausalLM")
+    assert not eng.use_graphs
+    groups = eng.cache.groups
+    assert len(groups) == 2 and sorted(len(g.need.planes) for g in groups) == [1, 2]
+    latent = next(g for g in groups if len(g.need.planes) == 1)
+    assert tuple(latent.planes[0].shape[2:]) == (1, 64, 24) and eng.cache.bytes_per_token() == (2 * 16 + 24) * 4
+    names = dict(eng.model.named_parts())
+    assert {"l0.n.", "l0.attn.", "l0.ff.", "l1.mem."} <= set(names) and "l0.n2." not in names
+
+    def reference(tokens):
+        n = len(tokens)
+        x = attention_layer(plain_llama.embed(w["emb.weight"], tokens), w, "l0.", "l0.n.weight", None, parallel=True)
+        h = plain_llama.rms_norm(x, w["l1.n.weight"], 1e-5)
+        c = h @ w["l1.mem.c.weight"].T
+        x = x + (np.cumsum(c, axis=0) / np.arange(1, n + 1)[:, None]) @ w["l1.mem.o.weight"].T \
+            + plain_llama.swiglu(h, w["l1.ff.gate_proj.weight"], w["l1.ff.up_proj.weight"], w["l1.ff.down_proj.weight"])
+        return plain_llama.rms_norm(x, w["out_norm.weight"], 1e-5) @ w["emb.weight"].T
+
+    a, b = seeded_tokens(41, 150, VOCAB), seeded_tokens(42, 20, VOCAB)
+    ref_a, ref_b = reference(a), reference(b)
+    s = eng.acquire()
+    whole = eng.step([StepEntry(s, a, want=tuple(range(len(a))))]).cpu().numpy()
+    eng.release(s)
+    assert close(whole, ref_a), "whole"
+    sa, sb = eng.acquire(), eng.acquire()                 # sa is the slot (and takes the pages) that a just gave back
+    first = eng.step([StepEntry(sb, b[:7], want=tuple(range(7))), StepEntry(sa, a[:100], want=tuple(range(100)))]).cpu().numpy()
+    got_b, got_a = [first[:7]], [first[7:]]
+    for i in range(50):
+        entries = [StepEntry(sa, [a[100 + i]], want=(0,))] + ([StepEntry(sb, [b[7 + i]], want=(0,))] if 7 + i < len(b) else [])
+        out = eng.step(entries).cpu().numpy()
+        got_a.append(out[:1])
+        if len(entries) == 2:
+            got_b.append(out[1:])
+        if 7 + i == len(b) - 1:
+            eng.release(sb)
+    eng.release(sa)
+    assert close(np.concatenate(got_a), ref_a) and close(np.concatenate(got_b), ref_b), "batch, then one token each"
+    eng.cache.slots.check()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_windowed_attention_through_the_engine(tmp_path, dtype):
+    """One layer reads only the last 70 positions: a prompt longer than window + a page,
+    then decoding through the captured and staged-ahead step while pages behind the window
+    go back to the pool, against the plain windowed attention; a cut back behind the window
+    is refused."""
+    from borrowed_compute_b200 import CacheError, StepEntry
+
+    # In bfloat16 the rounding noise of this toy is spread evenly over the rows (measured: the
+    # median row is off by 0.4 % of the largest score, the worst by 1.1-1.5 %) and grows with
+    # the spread of its matrices; half the spread keeps it well inside the suite's bound.
+    eng, w = build(tmp_path, "ToyWindowedForCausalLM", dtype=dtype, spread=0.2 if dtype == "float32" else 0.1, max_tokens=640, max_slots=2)
+    assert eng.use_graphs and len(eng.cache.groups) == 2
+
+    def reference(tokens):
+        x = plain_llama.embed(w["emb.weight"], tokens)
+        x = attention_layer(x, w, "l0.", "l0.n1.weight", "l0.n2.weight", window=70)
+        x = attention_layer(x, w, "l1.", "l1.n1.weight", "l1.n2.weight")
+        return plain_llama.rms_norm(x, w["out_norm.weight"], 1e-5) @ w["emb.weight"].T
+
+    a, b = seeded_tokens(51, 300, VOCAB), seeded_tokens(52, 200, VOCAB)
+    ref_a, ref_b = reference(a), reference(b)
+    rel = 2e-4 if dtype == "float32" else 1e-2
+    sa, sb = eng.acquire(), eng.acquire()
+    windowed = next(i for i, g in enumerate(eng.cache.groups) if g.need.window == 70)
+    first = eng.step([StepEntry(sa, a[:150], want=tuple(range(150))), StepEntry(sb, b[:66], want=tuple(range(66)))]).cpu().numpy()
+    got_a, got_b = [first[:150]], [first[150:]]
+    for i in range(150):
+        entries = [StepEntry(sa, [a[150 + i]], want=(0,))] + ([StepEntry(sb, [b[66 + i]], want=(0,))] if 66 + i < len(b) else [])
+        out = eng.step(entries).cpu().numpy()
+        got_a.append(out[:1])
+        if len(entries) == 2:
+            got_b.append(out[1:])
+        if 66 + i == len(b) - 1:
+            eng.release(sb)
+    assert close(np.concatenate(got_a), ref_a, rel) and close(np.concatenate(got_b), ref_b, rel)
+    held = [sum(p >= 0 for p in eng.cache.slots.tables[g][sa]) for g in range(2)]
+    assert held[windowed] == 2 and held[1 - windowed] == 5, "300 positions: five pages, of which the window keeps two"
+    with pytest.raises(CacheError, match="window"):
+        eng.rollback(sa, 100)
+    eng.rollback(sa, 290)                                  # inside what the window still holds
+    again = np.concatenate([eng.step([StepEntry(sa, [t], want=(0,))]).cpu().numpy() for t in a[290:]])
+    assert close(again, ref_a[290:], rel)
+    eng.release(sa)
+    eng.cache.slots.check()
+
+
+def test_scores_of_a_step_are_the_callers_unless_borrowed(tmp_path):
+    from borrowed_compute_b200 import StepEntry
+
+    eng, w = build(tmp_path, "ToyWindowedForCausalLM")
+    tokens = seeded_tokens(61, 12, VOCAB)
+    s = eng.acquire()
+    eng.step([StepEntry(s, tokens[:8], want=())])
+    one = eng.step([StepEntry(s, [tokens[8]], want=(0,))])
+    kept = one.clone()
+    two = eng.step([StepEntry(s, [tokens[9]], want=(0,))])
+    assert one.data_ptr() != two.data_ptr() and torch.equal(one, kept) and not torch.equal(one, two)
+    b1 = eng.step([StepEntry(s, [tokens[10]], want=(0,))], borrow_scores=True)
+    seen = b1.clone()
+    b2 = eng.step([StepEntry(s, [tokens[11]], want=(0,))], borrow_scores=True)
+    assert b1.data_ptr() == b2.data_ptr() and not torch.equal(seen, b2), "a borrowed view lives until the next step"
+    eng.release(s)
+
+
+def test_a_refused_step_leaves_the_cache_as_it_was(tmp_path):
+    from borrowed_compute_b200 import CacheError, StepEntry
+
+    eng, w = build(tmp_path, "ToyWindowedForCausalLM", max_tokens=256, max_slots=3)       # four pages a group
+    a, b = eng.acquire(), eng.acquire()
+    tokens = seeded_tokens(71, 200, VOCAB)
+
+    def books():
+        sl = eng.cache.slots
+        return ([p.available for p in sl.pools], [[list(r) for r in t] for t in sl.tables], sl.live(), [sl.length(s) for s in sl.live()])
+
+    before = books()
+    with pytest.raises(CacheError, match="full"):           # 130 + 130 positions need six pages, four exist
+        eng.step([StepEntry(a, tokens[:130], want=(0,)), StepEntry(b, tokens[:130], want=(0,))])
+    assert books() == before
+    with pytest.raises(ValueError, match="wanted index"):
+        eng.step([StepEntry(a, tokens[:10], want=(10,))])
+    with pytest.raises(ValueError, match="twice"):
+        eng.step([StepEntry(a, tokens[:10], want=(0,)), StepEntry(a, tokens[:10], want=(0,))])
+    with pytest.raises(ValueError, match="vocabulary"):
+        eng.step([StepEntry(a, [1, VOCAB], want=(0,))])
+    assert books() == before
+    out = eng.step([StepEntry(a, tokens[:130], want=(129,)), StepEntry(b, tokens[:60], want=(59,))])
+    assert out.shape == (2, VOCAB) and eng.length(a) == 130 and eng.length(b) == 60
+    eng.release(a), eng.release(b)
+    eng.cache.slots.check()

@@ -283,10 +283,11 @@ def register_toy():
         norm = lambda p: PartSpec("rmsnorm", {"size": cfg.hidden_size, "eps": cfg.rms_norm_eps}, p)
         ff = lambda p: PartSpec("swiglu", {"hidden_size": cfg.hidden_size, "intermediate_size": cfg.intermediate_size}, p)
         layers = (
-            LayerSpec("prenorm", norm("l0.n1."), PartSpec("gqa_attention", {
+            LayerSpec("prenorm", norm1=norm("l0.n1."), mixer=PartSpec("gqa_attention", {
                 "hidden_size": cfg.hidden_size, "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
-                "head_dim": cfg.head_dim, "position": position}, "l0.attn."), norm("l0.n2."), ff("l0.ff.")),
-            LayerSpec("prenorm", norm("l1.n1."), PartSpec("toy_running_mean", {"hidden_size": cfg.hidden_size}, "l1."), norm("l1.n2."), ff("l1.ff.")),
+                "head_dim": cfg.head_dim, "position": position}, "l0.attn."), norm2=norm("l0.n2."), feed_forward=ff("l0.ff.")),
+            LayerSpec("prenorm", norm1=norm("l1.n1."), mixer=PartSpec("toy_running_mean", {"hidden_size": cfg.hidden_size}, "l1."),
+                      norm2=norm("l1.n2."), feed_forward=ff("l1.ff.")),
         )
         # Layer 0 runs three times: twice with a cache of its own, once reading the first run's.
         schedule = (RunSpec(0), RunSpec(1), RunSpec(0), RunSpec(0, memory_of=0), RunSpec(1))
@@ -454,10 +455,10 @@ def register_routed_toy():
     def routed_spec(cfg):
         norm = lambda p: PartSpec("rmsnorm", {"size": cfg.hidden_size, "eps": cfg.rms_norm_eps}, p)
         layers = tuple(
-            LayerSpec("prenorm", norm(f"l{i}.n1."), PartSpec("gqa_attention", {
+            LayerSpec("prenorm", norm1=norm(f"l{i}.n1."), mixer=PartSpec("gqa_attention", {
                 "hidden_size": cfg.hidden_size, "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
-                "head_dim": cfg.head_dim, "position": {"kind": "none"}}, f"l{i}.attn."), norm(f"l{i}.n2."),
-                PartSpec("toy_top1_experts", {"hidden_size": cfg.hidden_size, "inner": cfg.intermediate_size, "experts": 3}, f"l{i}.moe."))
+                "head_dim": cfg.head_dim, "position": {"kind": "none"}}, f"l{i}.attn."), norm2=norm(f"l{i}.n2."),
+                feed_forward=PartSpec("toy_top1_experts", {"hidden_size": cfg.hidden_size, "inner": cfg.intermediate_size, "experts": 3}, f"l{i}.moe."))
             for i in range(cfg.num_hidden_layers))
         return ModelSpec(hidden_size=cfg.hidden_size, vocab_size=cfg.vocab_size, max_positions=cfg.max_position_embeddings,
                          embedding=PartSpec("token_embedding", {"vocab_size": cfg.vocab_size, "hidden_size": cfg.hidden_size}, "emb."),

@@ -112,3 +112,56 @@ def test_random_folder_is_a_function_of_config_and_seed(tmp_path):
     assert torch.equal(one[name], sa.tensor(name))
     tied = TensorSource(write_model_folder(str(tmp_path / "t"), TINY_B, seed=1, dtype=torch.float32))
     assert "lm_head.weight" not in tied.names() and tied.info("model.norm.weight")[0] == torch.float32
+
+
+def test_random_values_are_a_function_of_seed_name_and_index_alone():
+    from borrowed_compute_b200.weights.random_init import normal_deviates, tensor_key
+
+    key = tensor_key(7, "model.layers.0.mlp.up_proj.weight")
+    assert key != tensor_key(8, "model.layers.0.mlp.up_proj.weight") and key != tensor_key(7, "model.layers.0.mlp.gate_proj.weight")
+    z = normal_deviates(key, 200_000)
+    assert z.dtype == np.float32 and np.isfinite(z).all()
+    # a standard normal: moments, and the mass inside one and two deviations
+    assert abs(z.mean()) < 0.01 and abs(z.std() - 1.0) < 0.01
+    assert abs(((z - z.mean()) ** 4).mean() / z.var() ** 2 - 3.0) < 0.1
+    assert abs((np.abs(z) < 1).mean() - 0.6827) < 0.005 and abs((np.abs(z) < 2).mean() - 0.9545) < 0.003
+    # any cut of the index range gives the same values
+    cut = np.concatenate([normal_deviates(key, 1, 0), normal_deviates(key, 4095, 1), normal_deviates(key, 5000, 4096)])
+    assert np.array_equal(cut, z[:9096])
+    # the polynomials stand in for log, cos and sin: against the float64 formula on the same draws
+    h = []
+    for i in range(1, 513):
+        x = (key + i * 0x9E3779B97F4A7C15) & ((1 << 64) - 1)
+        x = ((x ^ (x >> 30)) * 0xBF58476D1CE4E5B9) & ((1 << 64) - 1)
+        x = ((x ^ (x >> 27)) * 0x94D049BB133111EB) & ((1 << 64) - 1)
+        h.append(x ^ (x >> 31))
+    u = np.array([((v >> 40) + 1) / 2.0 ** 24 for v in h])
+    ang = np.array([2.0 * np.pi * ((v >> 16) & 0xFFFFFF) / 2.0 ** 24 for v in h])
+    want = np.sqrt(-2.0 * np.log(u)) * np.cos(ang)
+    assert np.abs(z[:512] - want).max() < 2e-6
+
+
+def test_a_sharded_folder_reads_like_a_single_file(tmp_path):
+    w = make_weights(TINY_A, 3)
+    single = write_folder(str(tmp_path / "single"), TINY_A, w, "bfloat16")
+    sharded = str(tmp_path / "sharded")
+    os.makedirs(sharded)
+    json.dump(TINY_A, open(os.path.join(sharded, "config.json"), "w"))
+    names = sorted(w)
+    parts = {"model-00001-of-00002.safetensors": names[: len(names) // 2], "model-00002-of-00002.safetensors": names[len(names) // 2:]}
+    for fname, mine in parts.items():
+        write_safetensors(os.path.join(sharded, fname), {k: torch.from_numpy(w[k]).to(torch.bfloat16) for k in mine})
+    json.dump({"metadata": {}, "weight_map": {k: f for f, mine in parts.items() for k in mine}},
+              open(os.path.join(sharded, "model.safetensors.index.json"), "w"))
+    a, b = TensorSource(single), TensorSource(sharded)
+    assert sorted(a.names()) == sorted(b.names()) == names
+    for k in names:
+        assert a.info(k) == b.info(k) and torch.equal(a.tensor(k), b.tensor(k))
+    rt = Runtime(torch.device("cpu"), torch.bfloat16)
+    la = load_tensors(expected_tensors_for_config(TINY_A), a, rt)
+    lb = load_tensors(expected_tensors_for_config(TINY_A), b, rt)
+    assert all(torch.equal(la[k], lb[k]) for k in la)
+    # a shard that the index names but the folder lacks is one clear error
+    os.remove(os.path.join(sharded, "model-00002-of-00002.safetensors"))
+    with pytest.raises(WeightsError):
+        TensorSource(sharded)
