@@ -1,14 +1,22 @@
 """Decode and prefill throughput of the Llama-3.1-8B shape on one B200, random weights.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers L] [--impl ours|reference]
+                    [--no-points] [--no-breakdown]
 
 Prints ONE JSON line.  A "step" is one decode step of the whole batch.  ``value`` is decoded
 tokens a second timed on the device (CUDA events around K steps, after W warm-up steps);
-``e2e`` is the same through the Python entry point (host token ids in, host token ids out
-every step); ``prefill`` is one 2,048-token prompt; ``roofline`` sets the decode step's
-mandatory bytes (every weight once, the live requests' cache once) against the measured
-copy bandwidth; ``points`` adds batch 1 and 64.  Every decode step streams all weights
-(16 GB), far more than the 126 MB L2, so nothing is flushed between iterations.
+``e2e`` is the same through the Python entry point (``Local.generate``: host token ids in,
+host token ids out every step); ``prefill`` is one 2,048-token prompt; ``roofline`` sets the
+decode step's mandatory bytes (every weight once, the live requests' cache once) against the
+measured copy bandwidth.  ``points`` adds decoding at batch 1 and 64 (device-timed and end to
+end) and two more workloads of other shapes: the Llama-2-13B shape (one kv head a head) with
+16 prompts of unequal lengths, and the Llama-3.2-3B shape (tied head) at batch 64 sampled at
+temperature 1.0 through the entry point.  ``classes`` times every kernel class of one decode
+step and one prompt step launch by launch and sets each against its own bytes or operations.
+``checked`` says that the tokens of the end-to-end run equal those of the same prompts
+stepped without captured graphs; the line is not printed otherwise.  Every decode step
+streams all weights (16 GB), far more than the 126 MB L2, so nothing is flushed between
+iterations.
 
 The reference (Harshil089/Borrowed-Compute) is a Rust workspace; no Rust toolchain exists
 here, so ``--impl reference`` reports itself unavailable.
@@ -17,6 +25,7 @@ here, so ``--impl reference`` reports itself unavailable.
 from __future__ import annotations
 
 import argparse
+import gc
 import json
 import os
 import statistics
@@ -28,13 +37,28 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-# BASELINE.json configs[2]: the Llama-3.1-8B shape.
+
+def _llama3_scaling(factor: float) -> dict:
+    return {"rope_type": "llama3", "factor": factor, "low_freq_factor": 1.0, "high_freq_factor": 4.0, "original_max_position_embeddings": 8192}
+
+
+# The headline: the Llama-3.1-8B shape.
 CONFIG_8B = {
     "architectures": ["LlamaForCausalLM"], "num_hidden_layers": 32, "hidden_size": 4096, "num_attention_heads": 32,
     "num_key_value_heads": 8, "head_dim": 128, "intermediate_size": 14336, "vocab_size": 128256, "rope_theta": 500000.0,
-    "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
-                     "original_max_position_embeddings": 8192},
-    "rms_norm_eps": 1e-5, "tie_word_embeddings": False, "max_position_embeddings": 8192,
+    "rope_scaling": _llama3_scaling(8.0), "rms_norm_eps": 1e-5, "tie_word_embeddings": False, "max_position_embeddings": 8192,
+}
+# The Llama-2-13B shape: every head has a kv head of its own.
+CONFIG_13B = {
+    "architectures": ["LlamaForCausalLM"], "num_hidden_layers": 40, "hidden_size": 5120, "num_attention_heads": 40,
+    "num_key_value_heads": 40, "head_dim": 128, "intermediate_size": 13824, "vocab_size": 32000, "rope_theta": 10000.0,
+    "rms_norm_eps": 1e-5, "tie_word_embeddings": False, "max_position_embeddings": 4096,
+}
+# The Llama-3.2-3B shape: the head is the embedding table.
+CONFIG_3B = {
+    "architectures": ["LlamaForCausalLM"], "num_hidden_layers": 28, "hidden_size": 3072, "num_attention_heads": 24,
+    "num_key_value_heads": 8, "head_dim": 128, "intermediate_size": 8192, "vocab_size": 128256, "rope_theta": 500000.0,
+    "rope_scaling": _llama3_scaling(32.0), "rms_norm_eps": 1e-5, "tie_word_embeddings": True, "max_position_embeddings": 16384,
 }
 CONTEXT = 8192
 PROMPT = 2048
@@ -102,25 +126,237 @@ class ClockSampler:
         return {"sm_mhz": int(statistics.median(mhz)), "sm_max_mhz": mx, "reasons": sorted(reasons), "samples": len(mhz)}
 
 
-def model_numbers(cfg: dict, layers: int):
+# ------------------------------------------------------------------------ bytes and operations
+def model_numbers(cfg: dict, layers: int) -> dict:
     E, H, G, D, F, V = (cfg["hidden_size"], cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"],
                         cfg["intermediate_size"], cfg["vocab_size"])
-    layer_params = E * (H + 2 * G) * D + H * D * E + 3 * E * F
-    return {"layer_params": layer_params, "head_params": V * E, "norm_params": (2 * layers + 1) * E,
-            "kv_bytes_per_token": layers * 2 * G * D * 2, "E": E, "H": H, "D": D, "V": V}
+    qkv, o, gate_up, down = E * (H + 2 * G) * D, H * D * E, 2 * E * F, E * F
+    return {"qkv": qkv, "o": o, "gate_up": gate_up, "down": down, "layer_params": qkv + o + gate_up + down, "head_params": V * E,
+            "norm_params": (2 * layers + 1) * E, "kv_bytes_per_token": layers * 2 * G * D * 2, "E": E, "H": H, "G": G, "D": D, "F": F, "V": V}
 
 
-def decode_bytes(cfg, layers, batch, context) -> float:
+def decode_bytes(cfg, layers, batch, cached_tokens) -> float:
+    """What a decode step has to read: every weight it uses once (a tied head is the
+    embedding table, read once as the head), the norms, the batch's embedding rows, and
+    the cache of the live requests (``cached_tokens`` positions in all)."""
     n = model_numbers(cfg, layers)
     weights = 2.0 * (layers * n["layer_params"] + n["head_params"]) + 4.0 * n["norm_params"] + 2.0 * batch * n["E"]
-    return weights + float(batch) * context * n["kv_bytes_per_token"]
+    return weights + float(cached_tokens) * n["kv_bytes_per_token"]
 
 
-def prefill_flops(cfg, layers, tokens) -> float:
+def prefill_flops(cfg, layers, lengths) -> float:
+    """Operations of one prompt step over sequences of ``lengths`` tokens, scores at each one's last token."""
     n = model_numbers(cfg, layers)
+    tokens = sum(lengths)
     linear = 2.0 * tokens * layers * n["layer_params"]
-    attention = layers * 2.0 * 2.0 * n["H"] * n["D"] * tokens * (tokens + 1) / 2.0
-    return linear + attention + 2.0 * n["head_params"]
+    attention = sum(layers * 2.0 * 2.0 * n["H"] * n["D"] * t * (t + 1) / 2.0 for t in lengths)
+    return linear + attention + 2.0 * n["head_params"] * len(lengths)
+
+
+def class_costs(cfg, layers, batch, cached_tokens, prompt_tokens) -> dict:
+    """What each kernel class of a decode step has to move (bytes) and of a one-sequence
+    prompt step has to compute (operations; bytes for the classes that only move data)."""
+    n = model_numbers(cfg, layers)
+    E, H, G, D, F, V = n["E"], n["H"], n["G"], n["D"], n["F"], n["V"]
+    B, T = batch, prompt_tokens
+    qkv_w = (H + 2 * G) * D
+    decode = {
+        "embedding": B * E * 6.0,
+        "norm": (2 * layers + 1) * (B * E * 6.0 + E * 4.0),
+        "qkv product": layers * (2.0 * n["qkv"] + 2.0 * B * (E + qkv_w)),
+        "attention": float(cached_tokens) * n["kv_bytes_per_token"] + layers * 2.0 * B * (qkv_w + H * D),
+        "output product": layers * (2.0 * n["o"] + B * (2.0 * H * D + 8.0 * E)),
+        "gate/up product": layers * (2.0 * n["gate_up"] + 2.0 * B * (E + F)),
+        "down product": layers * (2.0 * n["down"] + B * (2.0 * F + 8.0 * E)),
+        "head product": 2.0 * n["head_params"] + B * (2.0 * E + 4.0 * V),
+        "sampling": B * V * 4.0,
+    }
+    prefill = {
+        "embedding": ("bytes", T * E * 6.0),
+        "norm": ("bytes", 2 * layers * T * E * 6.0 + E * 6.0),
+        "qkv product": ("flops", layers * 2.0 * T * n["qkv"]),
+        "rotary + append": ("bytes", layers * 2.0 * T * (2.0 * (H + G) * D + 2.0 * G * D + 2.0 * G * D)),
+        "attention": ("flops", layers * 4.0 * H * D * T * (T + 1) / 2.0),
+        "output product": ("flops", layers * 2.0 * T * n["o"]),
+        "gate/up product": ("flops", layers * 2.0 * T * n["gate_up"]),
+        "down product": ("flops", layers * 2.0 * T * n["down"]),
+        "head product": ("bytes", 2.0 * n["head_params"]),
+    }
+    return {"decode": decode, "prefill": prefill}
+
+
+# ------------------------------------------------------------------------------- measuring
+def free_device_memory():
+    import torch
+
+    gc.collect()
+    torch.cuda.empty_cache()
+
+
+def timed_decode(eng, prompts, steps, warmup, rng, vocab, sample_clocks=False, prompts_a_step=8):
+    """Device time of ``steps`` decode steps of the given sequences after their prompts.
+    Returns also the prompt step's time when all prompts go in one step."""
+    import torch
+
+    from borrowed_compute_b200 import Sampling, ops
+    from borrowed_compute_b200.engine import StepEntry
+    from borrowed_compute_b200.sampling import RowSampler
+
+    batch = len(prompts)
+    slots = [eng.acquire() for _ in range(batch)]
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for i in range(0, batch, prompts_a_step):   # prompts in steps of a few, to bound activation memory
+        eng.step([StepEntry(s, p, want=()) for s, p in zip(slots[i:i + prompts_a_step], prompts[i:i + prompts_a_step])])
+    b.record()
+    sampler = RowSampler(eng.rt.device, batch)
+    sampler.set_rows([Sampling()] * batch)
+    steps_t = torch.zeros(batch, dtype=torch.int32, device=eng.rt.device)
+    toks = [[int(t) for t in rng.integers(0, vocab, batch)] for _ in range(steps + warmup)]
+
+    def one(i):
+        scores = eng.step([StepEntry(s, (toks[i][j],), want=(0,)) for j, s in enumerate(slots)], borrow_scores=True)
+        sampler.sample(scores, steps_t)
+
+    for i in range(warmup):
+        one(i)
+    torch.cuda.synchronize()
+    prompt_ms = a.elapsed_time(b)
+    before = ops.launches
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    clocks = ClockSampler() if sample_clocks else None
+    if clocks:
+        clocks.__enter__()
+        time.sleep(0.3)
+    torch.cuda.synchronize()
+    start.record()
+    for i in range(warmup, warmup + steps):
+        one(i)
+    stop.record()
+    torch.cuda.synchronize()
+    if clocks:
+        time.sleep(0.2)
+        clocks.__exit__()
+    ms = start.elapsed_time(stop)
+    cached = sum(len(p) for p in prompts) + batch * (warmup + steps / 2.0)     # positions the live requests hold, mid-run
+    for s in slots:
+        eng.release(s)
+    eng.raise_on_kernel_error()
+    return {"ms_per_step": ms / steps, "tok_s": batch * steps / (ms / 1000.0), "cached_tokens": cached, "prompt_ms": prompt_ms,
+            "clocks": clocks.summary() if clocks else None, "eager_launches": ops.launches - before}
+
+
+def breakdown(eng, cfg, layers, batch, pk, rng):
+    """Every kernel class of one decode step (``batch`` sequences after 2,048-token prompts)
+    and of one 2,048-token prompt step, launch by launch, against its own bytes or operations."""
+    from borrowed_compute_b200 import Sampling
+    from borrowed_compute_b200.engine import StepEntry, StepProfile
+    from borrowed_compute_b200.sampling import RowSampler
+    import torch
+
+    vocab = cfg["vocab_size"]
+    slots = [eng.acquire() for _ in range(batch)]
+    prompts = [[int(t) for t in rng.integers(0, vocab, PROMPT)] for _ in range(batch)]
+    for i in range(0, batch, 8):
+        eng.step([StepEntry(s, p, want=()) for s, p in zip(slots[i:i + 8], prompts[i:i + 8])])
+    sampler = RowSampler(eng.rt.device, batch)
+    sampler.set_rows([Sampling()] * batch)
+    steps_t = torch.zeros(batch, dtype=torch.int32, device=eng.rt.device)
+
+    def one():
+        scores = eng.step([StepEntry(s, (int(rng.integers(0, vocab)),), want=(0,)) for s in slots])
+        sampler.sample(scores, steps_t)
+
+    reps = 5
+    with StepProfile(eng) as warm:
+        one()
+    with StepProfile(eng) as prof:
+        for _ in range(reps):
+            one()
+    decode = prof.classes(reps)
+    for s in slots:
+        eng.release(s)
+    slot = eng.acquire()
+    p = prompts[0]
+    with StepProfile(eng) as warm:   # noqa: F841
+        eng.step([StepEntry(slot, p, want=(PROMPT - 1,))])
+    eng.rollback(slot, 0)
+    with StepProfile(eng) as prof:
+        for _ in range(3):
+            eng.step([StepEntry(slot, p, want=(PROMPT - 1,))])
+            eng.rollback(slot, 0)
+    prefill = prof.classes(3)
+    eng.release(slot)
+    costs = class_costs(cfg, layers, batch, batch * (PROMPT + 3), PROMPT)
+    out = {"decode": {}, "prefill": {}, "how": "eager steps, CUDA events around every launch (no overlap between launches): shares, not a step's time"}
+    for cls, m in sorted(decode.items(), key=lambda kv: -kv[1]["us"]):
+        row = {"us": round(m["us"], 1), "launches": round(m["launches"], 1)}
+        if cls in costs["decode"]:
+            gbs = costs["decode"][cls] / (m["us"] * 1e-6) / 1e9
+            row.update({"bytes": int(costs["decode"][cls]), "gb_s": round(gbs, 1), "frac": round(gbs / pk["hbm_gbs"], 3)})
+        out["decode"][cls] = row
+    for cls, m in sorted(prefill.items(), key=lambda kv: -kv[1]["us"]):
+        row = {"us": round(m["us"], 1), "launches": round(m["launches"], 1)}
+        if cls in costs["prefill"]:
+            kind, amount = costs["prefill"][cls]
+            if kind == "flops":
+                tf = amount / (m["us"] * 1e-6) / 1e12
+                row.update({"flops": float(amount), "tflops": round(tf, 1), "frac": round(tf / pk["bf16_tflops"], 3)})
+            else:
+                gbs = amount / (m["us"] * 1e-6) / 1e9
+                row.update({"bytes": int(amount), "gb_s": round(gbs, 1), "frac": round(gbs / pk["hbm_gbs"], 3)})
+        out["prefill"][cls] = row
+    out["decode_sum_us"] = round(sum(m["us"] for m in decode.values()), 1)
+    out["prefill_sum_us"] = round(sum(m["us"] for m in prefill.values()), 1)
+    return out
+
+
+def bench_13b(pk, rng) -> dict:
+    """The Llama-2-13B shape: 16 prompts of unequal lengths (uniform in 64 .. 2,048, seeded)
+    in ONE ragged prompt step, then 128 decode steps, device-timed."""
+    from borrowed_compute_b200 import Local
+
+    cfg, layers = CONFIG_13B, CONFIG_13B["num_hidden_layers"]
+    lengths = [int(n) for n in rng.integers(64, 2049, 16)]
+    steps, warmup = 128, 4
+    max_tokens = sum(-(-(n + steps + warmup + 8) // 64) * 64 for n in lengths)
+    model = Local.random(cfg, seed=0, dtype="bfloat16", max_tokens=max_tokens, max_slots=16, max_seq=cfg["max_position_embeddings"])
+    prompts = [[int(t) for t in rng.integers(0, cfg["vocab_size"], n)] for n in lengths]
+    r = timed_decode(model.engine, prompts, steps, warmup, rng, cfg["vocab_size"], prompts_a_step=16)
+    need = decode_bytes(cfg, layers, 16, r["cached_tokens"])
+    gbs = need / (r["ms_per_step"] / 1000.0) / 1e9
+    flops = prefill_flops(cfg, layers, lengths)
+    out = {"llama2_13b_mha_decode_b16": round(r["tok_s"], 1), "llama2_13b_mha_ms_per_step": round(r["ms_per_step"], 4),
+           "llama2_13b_mha_bytes_per_step": int(need), "llama2_13b_mha_hbm_frac": round(gbs / pk["hbm_gbs"], 4),
+           "llama2_13b_mha_prompt_tokens": sum(lengths), "llama2_13b_mha_prefill_tok_s": round(sum(lengths) / (r["prompt_ms"] / 1000.0), 1),
+           "llama2_13b_mha_prefill_frac": round(flops / (r["prompt_ms"] / 1000.0) / (pk["bf16_tflops"] * 1e12), 4)}
+    del model
+    free_device_memory()
+    return out
+
+
+def bench_3b(pk, rng) -> dict:
+    """The Llama-3.2-3B shape (tied head): 64 prompts of 1,024 tokens, then 512 tokens each
+    sampled at temperature 1.0, through the entry point (the sampler runs every step)."""
+    from borrowed_compute_b200 import Local, Sampling
+
+    cfg, layers = CONFIG_3B, CONFIG_3B["num_hidden_layers"]
+    batch, prompt, new = 64, 1024, 512
+    model = Local.random(cfg, seed=0, dtype="bfloat16", max_tokens=batch * (-(-(prompt + new + 8) // 64) * 64), max_slots=batch,
+                         max_seq=prompt + new + 8)
+    prompts = [[int(t) for t in rng.integers(0, cfg["vocab_size"], prompt)] for _ in range(batch)]
+    model.generate(prompts[:2], 4, Sampling(temperature=1.0, seed=1), stop_ids=())      # first-use set-up outside the timed call
+    out, stats = model.generate(prompts, new, Sampling(temperature=1.0, top_p=1.0, seed=7), stop_ids=())
+    assert all(len(o) == new for o in out)
+    tok_s = stats.decode_tokens_per_second
+    ms = 1000.0 * batch / tok_s
+    need = decode_bytes(cfg, layers, batch, batch * (prompt + new / 2.0))
+    res = {"llama32_3b_sampled_e2e_b64": round(tok_s, 1), "llama32_3b_sampled_ms_per_step": round(ms, 4),
+           "llama32_3b_sampled_bytes_per_step": int(need), "llama32_3b_sampled_hbm_frac": round(need / (ms / 1000.0) / 1e9 / pk["hbm_gbs"], 4),
+           "llama32_3b_prefill_tok_s": round(batch * prompt / (stats.first_token_ms / 1000.0), 1)}
+    del model
+    free_device_memory()
+    return res
 
 
 def run_ours(args) -> dict:
@@ -129,7 +365,7 @@ def run_ours(args) -> dict:
 
     from borrowed_compute_b200 import Local, Sampling, ops
     from borrowed_compute_b200.engine import StepEntry
-    from borrowed_compute_b200.sampling import RowSampler
+    from borrowed_compute_b200.engine import engine as engine_module
 
     global PROMPT
     PROMPT = args.prompt
@@ -137,6 +373,7 @@ def run_ours(args) -> dict:
     full_layers = cfg["num_hidden_layers"]
     cfg["num_hidden_layers"] = args.layers or full_layers
     layers = cfg["num_hidden_layers"]
+    vocab = cfg["vocab_size"]
     pk = peaks()
     rng = np.random.default_rng(0)
     biggest = max(args.batch, 64 if not args.no_points else args.batch)
@@ -147,50 +384,10 @@ def run_ours(args) -> dict:
     torch.cuda.synchronize()
 
     def prompts(batch):
-        return [[int(t) for t in rng.integers(0, cfg["vocab_size"], PROMPT)] for _ in range(batch)]
+        return [[int(t) for t in rng.integers(0, vocab, PROMPT)] for _ in range(batch)]
 
-    def timed_decode(batch, steps, warmup, sample_clocks=False):
-        """Device time of `steps` decode steps of `batch` sequences after 2,048-token prompts."""
-        slots = [eng.acquire() for _ in range(batch)]
-        ps = prompts(batch)
-        for i in range(0, batch, 8):   # prompts in steps of at most 8, to bound activation memory
-            eng.step([StepEntry(s, p, want=()) for s, p in zip(slots[i:i + 8], ps[i:i + 8])])
-        sampler = RowSampler(eng.rt.device, batch)
-        sampler.set_rows([Sampling()] * batch)
-        steps_t = torch.zeros(batch, dtype=torch.int32, device=eng.rt.device)
-        toks = [[int(t) for t in rng.integers(0, cfg["vocab_size"], batch)] for _ in range(steps + warmup)]
-
-        def one(i):
-            scores = eng.step([StepEntry(s, (toks[i][j],), want=(0,)) for j, s in enumerate(slots)])
-            sampler.sample(scores, steps_t)
-
-        for i in range(warmup):
-            one(i)
-        torch.cuda.synchronize()
-        before = ops.launches
-        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        clocks = ClockSampler() if sample_clocks else None
-        if clocks:
-            clocks.__enter__()
-            time.sleep(0.3)
-        torch.cuda.synchronize()
-        start.record()
-        for i in range(warmup, warmup + steps):
-            one(i)
-        stop.record()
-        torch.cuda.synchronize()
-        if clocks:
-            time.sleep(0.2)
-            clocks.__exit__()
-        ms = start.elapsed_time(stop)
-        context = PROMPT + warmup + steps / 2.0
-        for s in slots:
-            eng.release(s)
-        return {"ms_per_step": ms / steps, "tok_s": batch * steps / (ms / 1000.0), "context": context,
-                "clocks": clocks.summary() if clocks else None, "eager_launches": ops.launches - before}
-
-    # --- the headline: decode at the requested batch
-    main = timed_decode(args.batch, args.steps, args.warmup, sample_clocks=True)
+    # --- the headline: decode at the requested batch, timed on the device
+    main = timed_decode(eng, prompts(args.batch), args.steps, args.warmup, rng, vocab, sample_clocks=True)
     # kernels a step: count them on one eager (uncaptured) step
     eng.use_graphs = False
     s = eng.acquire()
@@ -201,7 +398,7 @@ def run_ours(args) -> dict:
     eng.release(s)
     eng.use_graphs = True
 
-    need = decode_bytes(cfg, layers, args.batch, main["context"])
+    need = decode_bytes(cfg, layers, args.batch, main["cached_tokens"])
     achieved = need / (main["ms_per_step"] / 1000.0) / 1e9
     roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
                 "frac": round(achieved / pk["hbm_gbs"], 4), "bytes_per_step": int(need), "peak_source": pk["source"]}
@@ -224,39 +421,67 @@ def run_ours(args) -> dict:
         eng.rollback(slot, 0)
     eng.release(slot)
     pms = min(times)
-    flops = prefill_flops(cfg, layers, PROMPT)
+    flops = prefill_flops(cfg, layers, [PROMPT])
     prefill = {"value": round(PROMPT / (pms / 1000.0), 1), "tokens": PROMPT, "ms": round(pms, 3),
                "frac": round(flops / (pms / 1000.0) / (pk["bf16_tflops"] * 1e12), 4), "tflops": round(flops / (pms / 1000.0) / 1e12, 1)}
 
     # --- end to end through the Python entry point: host ids in, host ids out, every step
-    e2e_steps = args.steps
-    out, stats = model.generate(prompts(args.batch), e2e_steps + 1, Sampling(), stop_ids=())
-    e2e_tok_s = stats.decode_tokens_per_second
-    rows = eng._bucket(args.batch)
-    e2e = {"value": round(e2e_tok_s, 1), "unit": "tokens/s", "h2d_bytes_per_step": (7 * rows + 1) * 4,
-           "d2h_bytes_per_step": args.batch * 4, "generated": stats.generated, "passes": stats.passes,
-           "first_token_ms": round(stats.first_token_ms, 1)}
+    def end_to_end(batch, steps):
+        ps = prompts(batch)
+        traffic = engine_module.TRAFFIC
+        out, stats = model.generate(ps, steps + 1, Sampling(), stop_ids=())
+        h2d, d2h = traffic["h2d_decode"], traffic["d2h_decode"]
+        out, stats = model.generate(ps, steps + 1, Sampling(), stop_ids=())      # the second call: graphs captured, clocks settled
+        per_step = max(stats.passes, 1)
+        return ps, out, stats, (traffic["h2d_decode"] - h2d) / per_step, (traffic["d2h_decode"] - d2h) / per_step
+
+    ps, out, stats, h2d, d2h = end_to_end(args.batch, args.steps)
+    e2e = {"value": round(stats.decode_tokens_per_second, 1), "unit": "tokens/s", "h2d_bytes_per_step": int(round(h2d)),
+           "d2h_bytes_per_step": int(round(d2h)), "generated": stats.generated, "passes": stats.passes,
+           "first_token_ms": round(stats.first_token_ms, 1), "of_device_timed": round(stats.decode_tokens_per_second / main["tok_s"], 4)}
+    # --- the check: the same prompts stepped launch by launch (no captured graph, no step begun ahead) give the same tokens
+    eng.use_graphs = False
+    plain_out, _ = model.generate(ps, args.steps + 1, Sampling(), stop_ids=())
+    eng.use_graphs = True
+    if plain_out != out:
+        bad = next(i for i, (x, y) in enumerate(zip(out, plain_out)) if x != y)
+        raise AssertionError(f"bench: sequence {bad} generated {out[bad][:8]}... through captured steps and {plain_out[bad][:8]}... step by step")
+    if len({tuple(o) for o in out}) < len(out) or any(not 0 <= t < vocab for o in out for t in o):
+        raise AssertionError("bench: the generated sequences are not distinct sequences of token ids")
+
+    classes = None if args.no_breakdown else breakdown(eng, cfg, layers, args.batch, pk, rng)
 
     points = {}
     if not args.no_points:
         for b in (1, 64):
-            r = timed_decode(b, max(16, args.steps // 2), max(3, args.warmup // 2))
+            r = timed_decode(eng, prompts(b), max(16, args.steps // 2), max(3, args.warmup // 2), rng, vocab)
             points[f"decode_b{b}"] = round(r["tok_s"], 1)
-            need_b = decode_bytes(cfg, layers, b, r["context"])
+            need_b = decode_bytes(cfg, layers, b, r["cached_tokens"])
             points[f"decode_b{b}_hbm_frac"] = round(need_b / (r["ms_per_step"] / 1000.0) / 1e9 / pk["hbm_gbs"], 4)
+            _, _, st, _, _ = end_to_end(b, max(16, args.steps // 2))
+            points[f"e2e_b{b}"] = round(st.decode_tokens_per_second, 1)
+            points[f"e2e_b{b}_of_device_timed"] = round(st.decode_tokens_per_second / r["tok_s"], 4)
+    del model, eng
+    free_device_memory()
+    if not args.no_points and not args.layers:
+        points.update(bench_13b(pk, rng))
+        points.update(bench_3b(pk, rng))
 
     config = {"model": "llama-3.1-8b-shape", "layers": layers, "layers_full": full_layers, "hidden": cfg["hidden_size"],
               "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
               "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"], "global_batch": args.batch,
               "seq_len": CONTEXT, "prompt_len": PROMPT, "parallelism": "single-gpu", "l2": "inputs larger than L2 (16 GB of weights a step)"}
-    return {
+    line = {
         "metric": "decode tokens/s (Llama-3.1-8B shape, bf16, batch %d, 2,048-token prompts)" % args.batch,
         "value": round(main["tok_s"], 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": round(main["ms_per_step"], 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic: seeded uniform token ids, random N(0,0.02) weights", "config": config,
         "clocks": main["clocks"], "e2e": e2e, "gpu_launches": launches_per_step * args.steps, "launches_per_step": launches_per_step,
-        "prefill": prefill, "roofline": roofline, "points": points, "impl": "ours",
+        "prefill": prefill, "roofline": roofline, "points": points, "checked": True, "impl": "ours",
     }
+    if classes is not None:
+        line["classes"] = classes
+    return line
 
 
 def main() -> int:
@@ -268,7 +493,8 @@ def main() -> int:
     ap.add_argument("--prompt", type=int, default=PROMPT, help="prompt tokens before the timed decode steps")
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration has (0: all)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--no-points", action="store_true", help="skip the batch 1 and 64 points")
+    ap.add_argument("--no-points", action="store_true", help="skip batch 1 and 64 and the two other shapes")
+    ap.add_argument("--no-breakdown", action="store_true", help="skip the per-class timing of one decode and one prompt step")
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable": "the reference is a Rust workspace (no setup.py or pyproject) "

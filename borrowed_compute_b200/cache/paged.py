@@ -78,10 +78,11 @@ class PagedCache:
     def release(self, slot: int) -> None:
         self.slots.release(slot)
 
-    def sync_tables(self) -> None:
-        """Brings the device page tables up to date with the host's bookkeeping."""
+    def sync_tables(self) -> int:
+        """Brings the device page tables up to date with the host's bookkeeping; returns
+        the bytes copied to the device."""
         if not self.slots.dirty:
-            return
+            return 0
         touched = set()
         if self._copied is not None:
             self._copied.synchronize()   # the last copy out of the pinned tables is done
@@ -95,6 +96,7 @@ class PagedCache:
             if self._copied is None:
                 self._copied = torch.cuda.Event()
             self._copied.record()
+        return sum(self.groups[g].host_table.numel() * 4 for g in touched)
 
     # -- what a run sees
     def memory(self, run: int) -> RunMemory:

@@ -28,6 +28,17 @@ from ..weights import TensorSource, load_tensors, random_tensors, read_config_js
 from .batch import StepEntry, StepPlan, plan_step
 from .model import DecoderModel, model_for_config
 
+# Bytes copied between host and device since import, counted where the copies are issued
+# (the benchmark reports them per step): all of them, and those of decode steps alone.
+TRAFFIC = {"h2d": 0, "d2h": 0, "h2d_decode": 0, "d2h_decode": 0}
+
+
+def count_traffic(direction: str, n_bytes: int, decode: bool) -> None:
+    TRAFFIC[direction] += n_bytes
+    if decode:
+        TRAFFIC[direction + "_decode"] += n_bytes
+
+
 DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32,
           torch.bfloat16: torch.bfloat16, torch.float32: torch.float32}
 
@@ -75,11 +86,15 @@ class _DecodeGraph:
         out[at["want_rows"]:at["want_rows"] + rows] = np.arange(rows, dtype=np.int32)
         return out
 
-    def _upload(self, packed: np.ndarray) -> None:
+    def _upload(self, packed: np.ndarray, keep_tokens: bool = False) -> None:
+        """Sends the step's integers; with ``keep_tokens`` all but the tokens, which then stay
+        as something on the device (the last step's sampler) left them."""
         if self.copied is not None:
             self.copied.synchronize()   # the last copy out of the pinned buffer is done
-        self.host.copy_(torch.from_numpy(packed))
-        self.ints.copy_(self.host, non_blocking=True)
+        first = self.rows if keep_tokens else 0     # the tokens come first in the layout
+        self.host[first:].copy_(torch.from_numpy(packed[first:]))
+        self.ints[first:].copy_(self.host[first:], non_blocking=True)
+        count_traffic("h2d", 4 * (self.host.numel() - first), True)
         if self.copied is None:
             self.copied = torch.cuda.Event()
         self.copied.record()
@@ -98,7 +113,7 @@ class _DecodeGraph:
                           extras={"graph": True})
         return self.engine.model.forward(ctx, self.engine.cache, v["want_rows"], rows)
 
-    def run(self, packed: np.ndarray) -> torch.Tensor:
+    def run(self, packed: np.ndarray, keep_tokens: bool = False) -> torch.Tensor:
         if self.graph is None:
             # Warm-up and capture run on padding rows only (every slot -1), which change nothing
             # that outlives the step: the real rows then run exactly once, in the replay below.
@@ -120,7 +135,7 @@ class _DecodeGraph:
                 if was_enabled:
                     gc.enable()
             self.graph = graph
-        self._upload(packed)
+        self._upload(packed, keep_tokens)
         self.graph.replay()
         return self.scores
 
@@ -147,6 +162,7 @@ class Engine:
         self._staged: Optional[torch.cuda.Event] = None
         self._graphs: Dict[int, "_DecodeGraph"] = {}
         self._ahead: Optional[_Ahead] = None
+        self.last_graph: Optional[_DecodeGraph] = None   # the captured step the last call of step() replayed, if it did
         # Decode steps replay a captured CUDA graph unless a part plans on the host.
         self.use_graphs = all(part.graph_safe for _, part in model.named_parts())
         self.steps_run = 0
@@ -283,6 +299,7 @@ class Engine:
             self._staged.synchronize()   # the last copy out of the pinned buffer is done
         self._host_ints[:n].copy_(torch.from_numpy(packed))
         self._ints[:n].copy_(self._host_ints[:n], non_blocking=True)
+        count_traffic("h2d", 4 * n, plan.decode)
         if self._staged is None:
             self._staged = torch.cuda.Event()
         self._staged.record()
@@ -324,7 +341,24 @@ class Engine:
             g = self._graphs[bucket] = _DecodeGraph(self, bucket)
         return g
 
-    def _decode_graph_step(self, entries: Sequence[StepEntry], borrow_scores: bool) -> torch.Tensor:
+    def can_step_again(self, slots: Sequence[int]) -> bool:
+        """Whether ``step_again`` can follow now: the last step was a captured decode step of
+        exactly these slots, in this order, and the step after it is staged."""
+        a = self._ahead
+        return a is not None and self.last_graph is a.graph and a.slots == tuple(slots) and \
+            all(self.cache.slots.length(s) == p for s, p in zip(a.slots, a.starts))
+
+    def step_again(self, borrow_scores: bool = False) -> torch.Tensor:
+        """One more token for exactly the sequences of the last (captured) decode step, each
+        fed the id that lies at its row of ``last_graph.views["tokens"]`` on the device:
+        whoever sampled from the last step's scores wrote it there, and the host need not
+        have seen it.  Check ``can_step_again`` first."""
+        a = self._ahead
+        if a is None or self.last_graph is not a.graph:
+            raise RuntimeError("no staged step to go on from: the last step was not a captured decode step")
+        return self._decode_graph_step([StepEntry(s, (0,), want=(0,)) for s in a.slots], borrow_scores, tokens_on_device=True)
+
+    def _decode_graph_step(self, entries: Sequence[StepEntry], borrow_scores: bool, tokens_on_device: bool = False) -> torch.Tensor:
         """A step of one token a sequence, replayed from a CUDA graph captured once per
         padded batch size: the kernels, their order and their buffers are fixed, only the
         integers that name tokens, positions and slots change.
@@ -343,14 +377,18 @@ class Engine:
                 if not 0 <= t < self.vocab_size:
                     raise ValueError(f"token {t} is outside the vocabulary")
             starts, g, packed = ahead.starts, ahead.graph, ahead.packed
-            packed[:n] = tokens
+            if not tokens_on_device:
+                packed[:n] = tokens
+        elif tokens_on_device:
+            raise RuntimeError("the staged step does not fit these sequences any more")
         else:
             starts = self.check_entries(entries)
             self.cache.slots.reserve_many([(slot, start + 1, 1) for slot, start in zip(slots, starts)])
             g = self._graph_for(n)
             packed = g.pack(tokens, starts, slots, n)
-        self.cache.sync_tables()
-        scores = g.run(packed)[:n]
+        count_traffic("h2d", self.cache.sync_tables(), True)
+        scores = g.run(packed, keep_tokens=tokens_on_device)[:n]
+        self.last_graph = g
         if not borrow_scores:
             scores = scores.clone()
         for slot, start in zip(slots, starts):
@@ -361,7 +399,7 @@ class Engine:
             nxt = [start + 1 for start in starts]
             if max(nxt) + 1 <= self.max_seq:
                 self.cache.slots.reserve_many([(slot, start + 1, 1) for slot, start in zip(slots, nxt)])
-                self.cache.sync_tables()
+                count_traffic("h2d", self.cache.sync_tables(), True)
                 self._ahead = _Ahead(slots, nxt, g, g.pack(None, nxt, slots, n))
         except CacheError:
             self._ahead = None   # the step itself will say what is wrong, if it comes
@@ -383,11 +421,11 @@ class Engine:
         if self.use_graphs and pad_rows_to == 1 and entries and all(len(e.tokens) == 1 and tuple(e.want) == (0,) for e in entries) \
                 and len({e.slot for e in entries}) == len(entries):
             return self._decode_graph_step(entries, borrow_scores)
-        self._ahead = None
+        self._ahead, self.last_graph = None, None
         starts = self.check_entries(entries)
         plan = plan_step(entries, starts, pad_rows_to)    # its checks (a slot twice, a wanted index) come before any reservation
         self.cache.slots.reserve_many([(e.slot, start + len(e.tokens), len(e.tokens)) for e, start in zip(entries, starts)])
-        self.cache.sync_tables()
+        count_traffic("h2d", self.cache.sync_tables(), plan.decode)
         v = self._stage(plan)
         ctx = StepContext(
             rows=plan.padded_rows, seqs=plan.seqs, tokens=v["tokens"], row_pos=v["row_pos"], row_slot=v["row_slot"],

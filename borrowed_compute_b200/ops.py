@@ -98,10 +98,38 @@ launches = 0   # kernels launched through this module since import (a captured g
 _KERNELS_PER_CALL = {"bc_argmax": 2}   # launchers that start more than one kernel
 
 
+# Timing of single launches, for engine.profile.StepProfile: while `timeline` is a list every
+# call records CUDA events around itself and appends (class, launcher, start, end).  The
+# class is `label` if a part set one for the product it is about to run, else the launcher's.
+timeline: Optional[list] = None
+label = ""
+_CLASS_OF = {
+    "bc_embed": "embedding", "bc_rmsnorm": "norm", "bc_swiglu": "activation", "bc_rope_append": "rotary + append",
+    "bc_attention_rows": "attention", "bc_attention_decode": "attention", "bc_attention_prefill": "attention",
+    "bc_argmax": "sampling", "bc_sample": "sampling", "bc_gemm": "product", "bc_random": "random weights",
+}
+
+
+def _class_of(name: str) -> str:
+    if label:
+        return label
+    for prefix, cls in _CLASS_OF.items():
+        if name.startswith(prefix):
+            return cls
+    return name
+
+
 def _call(fn, *args) -> None:
     global launches
     launches += _KERNELS_PER_CALL.get(fn.__name__, 1)
-    status = fn(*args)
+    if timeline is not None:
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        status = fn(*args)
+        end.record()
+        timeline.append((_class_of(fn.__name__), fn.__name__, start, end))
+    else:
+        status = fn(*args)
     if status != 0:
         msg = lib().bc_last_error()
         raise KernelError(f"{fn.__name__} failed ({status}): {msg.decode() if msg else ''}")

@@ -56,7 +56,7 @@ class GroupedQueryAttention(Mixer):
         rows = x.shape[0]
         H, G, D = self.heads, self.kv_heads, self.head_dim
         qkv = torch.empty((rows, (H + 2 * G) * D), dtype=x.dtype, device=x.device)
-        products.linear(x, self.w_qkv, qkv, products.EPI_STORE)
+        products.linear(x, self.w_qkv, qkv, products.EPI_STORE, "qkv product")
         table = self.position.rotary()
         att = torch.empty((rows, H * D), dtype=x.dtype, device=x.device)
         if ctx.decode and ops.attention_decode_accepts(H, G, D, qkv.dtype):
@@ -68,7 +68,7 @@ class GroupedQueryAttention(Mixer):
             ops.rope_append(qkv, None if table is None else table.cos_sin, ctx.row_pos, ctx.row_slot, mem.page_table,
                             mem.k_pages, mem.v_pages, H, G, D, 0 if table is None else table.pairing, write_cache=mem.writes)
             self.attend(qkv, att, ctx, mem)
-        products.linear(att, self.w_o, residual, products.EPI_ADD_F32)
+        products.linear(att, self.w_o, residual, products.EPI_ADD_F32, "output product")
 
     def attend(self, qkv: torch.Tensor, out: torch.Tensor, ctx: StepContext, mem: RunMemory) -> None:
         H, G, D = self.heads, self.kv_heads, self.head_dim

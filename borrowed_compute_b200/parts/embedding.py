@@ -52,4 +52,4 @@ class LinearHead(Head):
         w = tied if self.tied else self.weight
         if w is None:
             raise RuntimeError("a tied head needs the embedding's table")
-        products.linear(x, w, out, products.EPI_STORE_F32)
+        products.linear(x, w, out, products.EPI_STORE_F32, "head product")

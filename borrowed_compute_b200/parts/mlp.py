@@ -34,5 +34,5 @@ class SwiGLU(FeedForward):
 
     def forward(self, x: torch.Tensor, residual: torch.Tensor, ctx: StepContext) -> None:
         h = torch.empty((x.shape[0], self.intermediate_size), dtype=x.dtype, device=x.device)
-        products.linear(x, self.w_gate_up, h, products.EPI_SWIGLU)
-        products.linear(h, self.w_down, residual, products.EPI_ADD_F32)
+        products.linear(x, self.w_gate_up, h, products.EPI_SWIGLU, "gate/up product")
+        products.linear(h, self.w_down, residual, products.EPI_ADD_F32, "down product")

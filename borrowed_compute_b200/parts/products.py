@@ -16,7 +16,15 @@ from ..ops import EPI_ADD_F32, EPI_STORE, EPI_STORE_F32, EPI_SWIGLU  # noqa: F40
 force_simt = False
 
 
-def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int) -> None:
+def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int, what: str = "") -> None:
+    """``what`` names the product for a profile of the step ("qkv", "head", ...)."""
+    if ops.timeline is not None and what:
+        ops.label = what
+        try:
+            linear(x, w, out, epilogue)
+        finally:
+            ops.label = ""
+        return
     if x.dtype == torch.bfloat16 and not force_simt and hasattr(ops, "gemm_tc") and ops.gemm_tc_accepts(x, w):
         ops.gemm_tc(x, w, out, epilogue)
     else:

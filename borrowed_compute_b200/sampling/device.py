@@ -2,7 +2,7 @@
 
 from __future__ import annotations
 
-from typing import Sequence
+from typing import Optional, Sequence
 
 import torch
 
@@ -31,11 +31,12 @@ class RowSampler:
         self.top_p[:n].copy_(torch.tensor([s.top_p for s in samplings], dtype=torch.float32))
         self.seed[:n].copy_(torch.tensor([s.seed_as_int64 for s in samplings], dtype=torch.int64))
 
-    def sample(self, scores: torch.Tensor, step: torch.Tensor) -> torch.Tensor:
+    def sample(self, scores: torch.Tensor, step: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Token ids [rows] int32 for scores [rows, vocab]; ``step[r]`` is the position of
-        the row sampled (crates/bc-mesh/src/engine.rs:347-350)."""
+        the row sampled (crates/bc-mesh/src/engine.rs:347-350).  The ids go to ``out`` if
+        given (int32, at least ``rows`` long), else to a buffer of this sampler's."""
         rows = scores.shape[0]
-        out = self.out[:rows]
+        out = self.out[:rows] if out is None else out[:rows]
         if self.all_greedy:
             ops.argmax(scores, out)
         else:

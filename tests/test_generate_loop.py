@@ -103,3 +103,83 @@ def test_plan_step_flattens_and_pads():
         plan_step([StepEntry(0, [])], [0])
     with pytest.raises(ValueError, match="outside"):
         plan_step([StepEntry(0, [1, 2], want=(2,))], [0])
+
+
+class Chaining(Scripted):
+    """The same script, but a pass can be begun before the last one's ids are read: it is
+    then fed the ids the backend itself holds, as an engine feeds them on the device."""
+
+    def __init__(self, max_batch, context=0, refuse_every=0):
+        super().__init__(max_batch, context)
+        self.held, self.last, self.unread, self.refuse_every, self.asked = {}, None, 0, refuse_every, 0
+
+    def start(self, indices, prompts, samplings):
+        first = super().start(indices, prompts, samplings)
+        self.last = None
+        return first
+
+    def begin(self, indices, tokens):
+        from borrowed_compute_b200.engine.generate import Pending
+
+        assert set(indices) <= self.live
+        if tokens is None:
+            self.asked += 1
+            if self.last != tuple(indices) or (self.refuse_every and self.asked % self.refuse_every == 0):
+                return None                                  # cannot follow on: the loop must read the ids first
+            tokens = [self.held[i] for i in indices]
+            self.log.append(("chained", tuple(indices)))
+        else:
+            assert self.unread == 0, "a pass fed by the host while ids of an earlier one are unread"
+            self.log.append(("advance", tuple(indices)))
+        ids = [(t + 1) % 50 for t in tokens]
+        self.held.update(zip(indices, ids))
+        self.last = tuple(indices)
+        self.unread += 1
+        assert self.unread <= 2, "more than one pass ahead of the host"
+        owner = self
+
+        class Later(Pending):
+            def ids(self):
+                owner.unread -= 1
+                return ids
+
+        return Later()
+
+    def finish(self, index):
+        super().finish(index)
+        self.last = None
+
+
+@pytest.mark.parametrize("refuse_every", [0, 3])
+def test_passes_begun_ahead_give_the_same_tokens(refuse_every):
+    import random
+
+    rnd = random.Random(4)
+    for trial in range(40):
+        n = rnd.randint(1, 7)
+        prompts = [[rnd.randrange(50) for _ in range(rnd.randint(1, 4))] for _ in range(n)]
+        max_tokens = rnd.randint(0, 9)
+        stops = [rnd.randrange(50) for _ in range(rnd.randint(0, 6))]
+        plain = Scripted(max_batch=3)
+        want, want_stats = run_generation(plain, prompts, max_tokens, [Sampling()] * n, stop_ids=stops)
+        ahead = Chaining(max_batch=3, refuse_every=refuse_every)
+        got, stats = run_generation(ahead, prompts, max_tokens, [Sampling()] * n, stop_ids=stops)
+        assert got == want and not ahead.live and ahead.unread == 0
+        assert stats.generated == want_stats.generated and stats.passes >= want_stats.passes
+        assert sorted(e[1] for e in ahead.log if e[0] == "finish") == list(range(n)), "every sequence is finished exactly once"
+
+
+def test_a_pass_begun_ahead_is_never_a_sequences_last_by_count():
+    b = Chaining(max_batch=2)
+    out, stats = run_generation(b, [[1], [10]], 4, [Sampling()] * 2)
+    assert out == [[2, 3, 4, 5], [11, 12, 13, 14]]
+    # token 1 comes from the prompts; tokens 2, 3 and 4 from three passes, the last of which is not run ahead of
+    assert [e[0] for e in b.log if e[0] in ("advance", "chained")] == ["advance", "chained", "chained"]
+    assert stats.passes == 3
+    # a stop id is seen one pass late: the sequence's row of the pass in flight runs for nothing, then it leaves
+    b = Chaining(max_batch=2)
+    out, stats = run_generation(b, [[1], [10]], 9, [Sampling()] * 2, stop_ids=[13])
+    assert out == [[2, 3, 4, 5, 6, 7, 8, 9, 10], [11, 12]]
+    steps = [e for e in b.log if e[0] in ("advance", "chained", "finish")]
+    assert steps[:4] == [("advance", (0, 1)), ("chained", (0, 1)), ("chained", (0, 1)), ("finish", 1)]
+    assert steps[4] == ("advance", (0,)) and not b.live
