@@ -6,7 +6,9 @@
 // online softmax as crates/bc-infer/src/gpu/kernels.h:271-324).  How: a block takes
 // (row, kv head, split).  The heads that share the kv head (H / G of them, at most 16)
 // are the 16 rows of an m16n8k16 tensor-core tile, so a 64-position page of keys is read
-// once for all of them.  Pages stream through shared memory by cp.async (three stages);
+// once for all of them.  Pages stream through a ring of three stages of shared memory: for head
+// sizes 64 and 128 as TMA boxes (cp.async.bulk.tensor out of the cache seen as a matrix, one
+// thread asking, an mbarrier a stage counting the bytes), else by cp.async;
 // each of the four warps takes 16 of a page's 64 positions: S = Q K^T, a running maximum
 // and sum in float, P V accumulated in float.  The four warps' partial results are merged
 // in a fixed order; with several splits each block leaves (sum, maximum, normaliser) in
@@ -18,6 +20,8 @@
 
 #include "common.cuh"
 #include "mma_tiles.cuh"
+#include "tc_ptx.cuh"
+#include "tma_host.cuh"
 
 namespace cg = cooperative_groups;
 
@@ -25,9 +29,13 @@ namespace cg = cooperative_groups;
 #define AD_STAGES 3
 #define AD_MAX_GROUP 16
 
-template <int D>
+// Byte offset of 16-byte chunk c of row r in a page as TMA writes it: blocks of [64 rows][64
+// elements] with the 128-byte swizzle (chunk xor row within each 128-byte row).
+__device__ __forceinline__ int tma_tile_offset(int r, int c) { return (c >> 3) * 8192 + r * 128 + (((c & 7) ^ (r & 7)) << 4); }
+
+template <int D, bool TMA>
 __global__ void __launch_bounds__(AD_THREADS)
-attention_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
+attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, const bf16* __restrict__ q, int q_stride, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
                         const int* __restrict__ page_table, const int* __restrict__ row_pos, const int* __restrict__ row_slot,
                         bf16* __restrict__ out, float* __restrict__ scratch, int* __restrict__ counters, int H, int G, int max_pages,
                         int n_pages, int window, float scale_log2, const float2* __restrict__ cos_sin, int pairing, int fuse,
@@ -36,8 +44,17 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __
     constexpr int TILE_BYTES = 64 * D * 2;     // one page of one kv head
     constexpr int KD = D / 16;                 // k-steps of Q K^T
     constexpr int ND = D / 8;                  // 8-wide dimension blocks of the output
-    extern __shared__ __align__(128) uint8_t smem[];
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);   // TMA's swizzle wants 1024-byte alignment
     __shared__ int is_last;
+    __shared__ __align__(8) uint64_t full_bars[AD_STAGES];
+    auto offset = [](int r, int c) { return TMA ? tma_tile_offset(r, c) : tile_offset<D>(r, c); };
+    const uint32_t full0 = smem_u32(&full_bars[0]);
+    if (TMA && threadIdx.x == 0) {
+        for (int s = 0; s < AD_STAGES; s++) mbar_init(full0 + 8 * s, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (TMA) __syncthreads();
 
     // Slots, positions and page tables are in place before the step starts, and the pages read
     // here were written by earlier steps: the first pages are asked for before the wait for
@@ -63,12 +80,33 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __
     const int n_tiles = max(0, t_end - t_begin);
     const int* pages = page_table + (size_t)slot * max_pages;
 
+    // A tile without a page (behind a window, or past what the sequence holds) is neither
+    // fetched nor multiplied: what another sequence left in some page never meets this row.
+    auto page_of = [&](int tile) {
+        const int page = tile < max_pages ? pages[tile] : -1;
+        return page >= 0 && page < n_pages ? page : -1;
+    };
     auto load_tile = [&](int tile, int stage) {
-        int page = tile < max_pages ? pages[tile] : -1;
-        if (page < 0 || page >= n_pages) page = 0;   // never read: every position of such a tile is masked below
+        const int page = page_of(tile);
+        const uint32_t kb = ad_smem(smem + (size_t)stage * 2 * TILE_BYTES), vb = kb + TILE_BYTES;
+        if (TMA) {
+            if (threadIdx.x != 0) return;
+            if (page < 0) {
+                mbar_arrive(full0 + 8 * stage);   // nothing comes: the stage's phase ends at once
+                return;
+            }
+            const int y = (page * G + g) * BC_PAGE;
+            mbar_expect_tx(full0 + 8 * stage, 2 * TILE_BYTES);
+#pragma unroll
+            for (int b = 0; b < D / 64; b++) {
+                tma_load_2d(kb + b * 8192, &map_k, full0 + 8 * stage, b * 64, y);
+                tma_load_2d(vb + b * 8192, &map_v, full0 + 8 * stage, b * 64, y);
+            }
+            return;
+        }
+        if (page < 0) return;
         const bf16* ks = k_cache + ((size_t)page * G + g) * BC_PAGE * D;
         const bf16* vs = v_cache + ((size_t)page * G + g) * BC_PAGE * D;
-        const uint32_t kb = ad_smem(smem + (size_t)stage * 2 * TILE_BYTES), vb = kb + TILE_BYTES;
         for (int i = threadIdx.x; i < 64 * CHUNKS; i += AD_THREADS) {
             const int row = i / CHUNKS, c = i - row * CHUNKS;
             cp_async16(kb + tile_offset<D>(row, c), ks + (size_t)row * D + c * 8);
@@ -77,14 +115,17 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __
     };
 
     // The first pages are asked for at once, before the wait and before the query is fetched
-    // and rotated.  Only the row's own page (the last one of the last split) must wait: this
-    // step writes the row's key and value into it, this block (fuse 2) or a kernel before it.
+    // and rotated.  The row's own page (the last one of the last split) gets the row's key and
+    // value in this step.  Where this block writes them itself (fuse 2) the page is fetched
+    // early like the others, with whatever the row's place holds, and the row is then put into
+    // the copy in shared memory by hand; where a kernel before this one wrote them, the page
+    // is fetched after the wait for that kernel.
     const bool appends = fuse == 2 && n_tiles > 0 && t_end == end_tile;
     int asked = 0;   // stages of the first ring asked for so far, in order
     for (; asked < AD_STAGES - 1; asked++) {
-        if (t_begin + asked == end_tile - 1) break;
+        if (fuse != 2 && t_begin + asked == end_tile - 1) break;
         if (asked < n_tiles) load_tile(t_begin + asked, asked);
-        cp_async_commit();
+        if (!TMA) cp_async_commit();
     }
     pdl_wait();
 
@@ -137,37 +178,9 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __
                 }
         }
     }
-    // The block whose split holds the row's own position also appends the row's key (rotated)
-    // and value to the cache, before it starts reading pages.
-    if (appends) {
-        const int pi = pos / BC_PAGE;
-        const int page = pi < max_pages ? pages[pi] : -1;
-        if (page >= 0 && page < n_pages) {
-            const bf16* kr = q + (size_t)r * q_stride + k_off + (size_t)g * D;
-            const bf16* vr = q + (size_t)r * q_stride + v_off + (size_t)g * D;
-            bf16* kd_ = k_write + (((size_t)page * G + g) * BC_PAGE + pos % BC_PAGE) * D;
-            bf16* vd_ = v_write + (((size_t)page * G + g) * BC_PAGE + pos % BC_PAGE) * D;
-            const float2* cs = cos_sin ? cos_sin + (size_t)pos * (D / 2) : nullptr;
-            for (int i = threadIdx.x; i < D / 2; i += AD_THREADS) {
-                const int a = pairing ? 2 * i : i, b = pairing ? 2 * i + 1 : i + D / 2;
-                const float x0 = __bfloat162float(kr[a]), x1 = __bfloat162float(kr[b]);
-                float y0 = x0, y1 = x1;
-                if (cs) {
-                    const float2 c = cs[i];
-                    y0 = __fsub_rn(__fmul_rn(x0, c.x), __fmul_rn(x1, c.y));
-                    y1 = __fadd_rn(__fmul_rn(x0, c.y), __fmul_rn(x1, c.x));
-                }
-                kd_[a] = __float2bfloat16_rn(y0);
-                kd_[b] = __float2bfloat16_rn(y1);
-            }
-            for (int d = threadIdx.x; d < D; d += AD_THREADS) vd_[d] = vr[d];
-        }
-        __threadfence();
-        __syncthreads();
-    }
     for (; asked < AD_STAGES - 1; asked++) {
         if (asked < n_tiles) load_tile(t_begin + asked, asked);
-        cp_async_commit();
+        if (!TMA) cp_async_commit();
     }
 
     float o[ND][4];
@@ -175,22 +188,76 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __
     for (int i = 0; i < ND; i++) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.0f, l1 = 0.0f;   // rows gq and gq + 8
 
+    bool waits_ok = true;
     for (int it = 0; it < n_tiles; it++) {
-        cp_async_wait<AD_STAGES - 2>();
-        __syncthreads();
+        if (TMA) {
+            waits_ok = mbar_wait(full0 + 8 * (it % AD_STAGES), (it / AD_STAGES) & 1, 1);
+            if (__syncthreads_or(!waits_ok)) {   // also: everybody is done with the stage that is filled next
+                waits_ok = false;
+                break;
+            }
+        } else {
+            cp_async_wait<AD_STAGES - 2>();
+            __syncthreads();
+        }
         if (it + AD_STAGES - 1 < n_tiles) load_tile(t_begin + it + AD_STAGES - 1, (it + AD_STAGES - 1) % AD_STAGES);
-        cp_async_commit();
+        if (!TMA) cp_async_commit();
         const int tile = t_begin + it;
-        const bool page_ok = tile < max_pages && pages[tile] >= 0 && pages[tile] < n_pages;
+        const bool page_ok = page_of(tile) >= 0;
+        if (!page_ok) continue;
         const uint32_t kb = ad_smem(smem + (size_t)(it % AD_STAGES) * 2 * TILE_BYTES), vb = kb + TILE_BYTES;
         const int key0 = 16 * warp;   // this warp's 16 positions of the page
+        if (tile == end_tile - 1) {
+            // The row's own page.  What lies past the row's position in it belongs to nobody (a
+            // sequence that held the page before may have left anything there, not-a-numbers
+            // too, and 0 x NaN is NaN in the product with the values): those value rows are
+            // cleared in the copy.  And the block that appends puts the row itself there: its
+            // key, rotated with the same four roundings as everywhere, and its value; the same
+            // go to the cache for the steps to come.
+            uint8_t* kt = smem + (size_t)(it % AD_STAGES) * 2 * TILE_BYTES;
+            uint8_t* vt = kt + TILE_BYTES;
+            const int pr = pos % BC_PAGE;
+            for (int i = threadIdx.x; i < (BC_PAGE - 1 - pr) * CHUNKS; i += AD_THREADS) {
+                const int row = pr + 1 + i / CHUNKS, c = i % CHUNKS;
+                *reinterpret_cast<uint4*>(vt + offset(row, c)) = make_uint4(0u, 0u, 0u, 0u);
+            }
+            if (appends) {
+                const int page = page_of(tile);
+                const bf16* kr = q + (size_t)r * q_stride + k_off + (size_t)g * D;
+                const bf16* vr = q + (size_t)r * q_stride + v_off + (size_t)g * D;
+                bf16* kd_ = k_write + (((size_t)page * G + g) * BC_PAGE + pr) * D;
+                bf16* vd_ = v_write + (((size_t)page * G + g) * BC_PAGE + pr) * D;
+                const float2* cs = cos_sin ? cos_sin + (size_t)pos * (D / 2) : nullptr;
+                for (int i = threadIdx.x; i < D / 2; i += AD_THREADS) {
+                    const int a = pairing ? 2 * i : i, b = pairing ? 2 * i + 1 : i + D / 2;
+                    const float x0 = __bfloat162float(kr[a]), x1 = __bfloat162float(kr[b]);
+                    float y0 = x0, y1 = x1;
+                    if (cs) {
+                        const float2 c = cs[i];
+                        y0 = __fsub_rn(__fmul_rn(x0, c.x), __fmul_rn(x1, c.y));
+                        y1 = __fadd_rn(__fmul_rn(x0, c.y), __fmul_rn(x1, c.x));
+                    }
+                    const bf16 ka = __float2bfloat16_rn(y0), kb_ = __float2bfloat16_rn(y1);
+                    kd_[a] = ka;
+                    kd_[b] = kb_;
+                    *reinterpret_cast<bf16*>(kt + offset(pr, a >> 3) + (a & 7) * 2) = ka;
+                    *reinterpret_cast<bf16*>(kt + offset(pr, b >> 3) + (b & 7) * 2) = kb_;
+                }
+                for (int d = threadIdx.x; d < D; d += AD_THREADS) {
+                    const bf16 val = vr[d];
+                    vd_[d] = val;
+                    *reinterpret_cast<bf16*>(vt + offset(pr, d >> 3) + (d & 7) * 2) = val;
+                }
+            }
+            __syncthreads();
+        }
 
         float s[2][4] = {};
 #pragma unroll
         for (int kd = 0; kd < KD; kd++) {
             uint32_t b0, b1, b2, b3;
             const int j = lane >> 3, rr = lane & 7;
-            ldmatrix_x4(kb + tile_offset<D>(key0 + (j >> 1) * 8 + rr, kd * 2 + (j & 1)), b0, b1, b2, b3);
+            ldmatrix_x4(kb + offset(key0 + (j >> 1) * 8 + rr, kd * 2 + (j & 1)), b0, b1, b2, b3);
             mma_16816(s[0], qf[kd], b0, b1);
             mma_16816(s[1], qf[kd], b2, b3);
         }
@@ -232,12 +299,12 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __
             o[nd + 1][0] *= c0; o[nd + 1][1] *= c0; o[nd + 1][2] *= c1; o[nd + 1][3] *= c1;
             uint32_t b0, b1, b2, b3;
             const int j = lane >> 3, rr = lane & 7;
-            ldmatrix_x4_trans(vb + tile_offset<D>(key0 + (j & 1) * 8 + rr, nd + (j >> 1)), b0, b1, b2, b3);
+            ldmatrix_x4_trans(vb + offset(key0 + (j & 1) * 8 + rr, nd + (j >> 1)), b0, b1, b2, b3);
             mma_16816(o[nd], pf, b0, b1);
             mma_16816(o[nd + 1], pf, b2, b3);
         }
     }
-    cp_async_wait<0>();
+    if (!TMA) cp_async_wait<0>();
     l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
     l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
@@ -305,16 +372,35 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __
         cg::cluster_group cl = cg::this_cluster();
         cl.sync();
         const int total = group * D, share = (total + n_splits - 1) / n_splits;
+        // All reads of the peers' shared memory (a good tenth of a microsecond each) are asked
+        // for before any is used; the splits are added in their order as ever.
+        const float *ppm[8], *ppl[8], *ppo[8];
+#pragma unroll
+        for (int sp = 0; sp < 8; sp++) {
+            const int from = sp < n_splits ? sp : 0;
+            ppm[sp] = cl.map_shared_rank(pm, from);
+            ppl[sp] = cl.map_shared_rank(pl, from);
+            ppo[sp] = cl.map_shared_rank(po, from);
+        }
         for (int i = split * share + threadIdx.x; i < min(total, (split + 1) * share); i += AD_THREADS) {
             const int hr = i / D, d = i - hr * D;
+            float ms[8], ls[8], os[8];
+#pragma unroll
+            for (int sp = 0; sp < 8; sp++) {
+                const bool has = sp < n_splits;
+                ms[sp] = has ? ppm[sp][hr] : -INFINITY;
+                ls[sp] = has ? ppl[sp][hr] : 0.0f;
+                os[sp] = has ? ppo[sp][i] : 0.0f;
+            }
             float M = -INFINITY;
-            for (int sp = 0; sp < n_splits; sp++) M = fmaxf(M, cl.map_shared_rank(pm, sp)[hr]);
+#pragma unroll
+            for (int sp = 0; sp < 8; sp++) M = fmaxf(M, ms[sp]);
             float L = 0.0f, O = 0.0f;
-            for (int sp = 0; sp < n_splits; sp++) {
-                const float ms = cl.map_shared_rank(pm, sp)[hr];
-                const float f = ms == -INFINITY ? 0.0f : exp2f(ms - M);
-                L += cl.map_shared_rank(pl, sp)[hr] * f;
-                O += cl.map_shared_rank(po, sp)[i] * f;
+#pragma unroll
+            for (int sp = 0; sp < 8; sp++) {
+                const float f = ms[sp] == -INFINITY ? 0.0f : exp2f(ms[sp] - M);
+                L += ls[sp] * f;
+                O += os[sp] * f;
             }
             out[((size_t)r * H + g * group + hr) * D + d] = __float2bfloat16_rn(L > 0.0f ? O / L : 0.0f);
         }
@@ -358,16 +444,21 @@ struct FusedRope {
     bool allow_cluster;     // splits may run as a thread-block cluster (else they go through scratch memory)
 };
 
-template <int D>
-static int launch(const void* q, int q_stride, const void* k_cache, const void* v_cache, const int* page_table, const int* row_pos,
-                  const int* row_slot, void* out, float* scratch, int* counters, int rows, int H, int G, int max_pages, int n_pages,
-                  int window, float scale, int n_splits, FusedRope fr, cudaStream_t s) {
+// Whether pages come by TMA where the head size allows (the default) or by cp.async
+// everywhere; both give the same bits.  For measurements and tests.
+static int g_ad_tma = 1;
+extern "C" void bc_attention_decode_set_tma(int on) { g_ad_tma = on != 0; }
+
+template <int D, bool TMA>
+static int launch_as(const CUtensorMap& mk, const CUtensorMap& mv, const void* q, int q_stride, const void* k_cache, const void* v_cache,
+                     const int* page_table, const int* row_pos, const int* row_slot, void* out, float* scratch, int* counters, int rows, int H,
+                     int G, int max_pages, int n_pages, int window, float scale, int n_splits, FusedRope fr, cudaStream_t s) {
     constexpr int TILE_BYTES = 64 * D * 2;
     constexpr int MERGE_BYTES = (2 * 4 * 16 + 4 * 16 * D + 16 * D + 32) * 4;
-    constexpr int SMEM = AD_STAGES * 2 * TILE_BYTES > MERGE_BYTES ? AD_STAGES * 2 * TILE_BYTES : MERGE_BYTES;
+    constexpr int SMEM = (AD_STAGES * 2 * TILE_BYTES > MERGE_BYTES ? AD_STAGES * 2 * TILE_BYTES : MERGE_BYTES) + 1024;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+        cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<D, TMA>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
         if (e != cudaSuccess) {
             bc_set_error("attention_decode: cannot set shared memory to %d: %s", SMEM, cudaGetErrorString(e));
             return (int)e;
@@ -379,16 +470,36 @@ static int launch(const void* q, int q_stride, const void* k_cache, const void* 
     // distributed shared memory; more go through the caller's scratch memory.
     const bool clustered = n_splits > 1 && n_splits <= 8 && fr.allow_cluster;
     if (clustered)
-        bc_launch_clustered(attention_decode_kernel<D>, grid, dim3(AD_THREADS), (size_t)SMEM, s, dim3(n_splits, 1, 1), (const bf16*)q, q_stride,
-                            (const bf16*)k_cache, (const bf16*)v_cache, page_table, row_pos, row_slot, (bf16*)out, scratch, counters, H, G,
+        bc_launch_clustered(attention_decode_kernel<D, TMA>, grid, dim3(AD_THREADS), (size_t)SMEM, s, dim3(n_splits, 1, 1), mk, mv, (const bf16*)q,
+                            q_stride, (const bf16*)k_cache, (const bf16*)v_cache, page_table, row_pos, row_slot, (bf16*)out, scratch, counters, H, G,
                             max_pages, n_pages, window, scale * 1.4426950408889634f, (const float2*)fr.cos_sin, fr.pairing, fr.fuse,
                             fr.k_off, fr.v_off, (bf16*)k_cache, (bf16*)v_cache, 1);
     else
-        bc_launch(attention_decode_kernel<D>, grid, dim3(AD_THREADS), (size_t)SMEM, s, (const bf16*)q, q_stride, (const bf16*)k_cache,
+        bc_launch(attention_decode_kernel<D, TMA>, grid, dim3(AD_THREADS), (size_t)SMEM, s, mk, mv, (const bf16*)q, q_stride, (const bf16*)k_cache,
                   (const bf16*)v_cache, page_table, row_pos, row_slot, (bf16*)out, scratch, counters, H, G, max_pages, n_pages, window,
                   scale * 1.4426950408889634f, (const float2*)fr.cos_sin, fr.pairing, fr.fuse, fr.k_off, fr.v_off, (bf16*)k_cache,
                   (bf16*)v_cache, 0);
     BC_LAUNCH_STATUS();
+}
+
+template <int D>
+static int launch(const void* q, int q_stride, const void* k_cache, const void* v_cache, const int* page_table, const int* row_pos,
+                  const int* row_slot, void* out, float* scratch, int* counters, int rows, int H, int G, int max_pages, int n_pages,
+                  int window, float scale, int n_splits, FusedRope fr, cudaStream_t s) {
+    CUtensorMap mk = {}, mv = {};
+    if constexpr (D == 64 || D == 128) {
+        // Pages by TMA: the cache as a matrix of [pages * kv heads * 64 positions, D], boxes of 64 x 64.
+        if (g_ad_tma && bc_encode_tiled_fn() && (uintptr_t)k_cache % 16 == 0 && (uintptr_t)v_cache % 16 == 0) {
+            const long long cache_rows = (long long)n_pages * G * BC_PAGE;
+            int st = bc_cached_cache_map(&mk, k_cache, cache_rows, D, "attention_decode");
+            if (st == BC_OK) st = bc_cached_cache_map(&mv, v_cache, cache_rows, D, "attention_decode");
+            if (st != BC_OK) return st;
+            return launch_as<D, true>(mk, mv, q, q_stride, k_cache, v_cache, page_table, row_pos, row_slot, out, scratch, counters, rows, H, G,
+                                      max_pages, n_pages, window, scale, n_splits, fr, s);
+        }
+    }
+    return launch_as<D, false>(mk, mv, q, q_stride, k_cache, v_cache, page_table, row_pos, row_slot, out, scratch, counters, rows, H, G, max_pages,
+                               n_pages, window, scale, n_splits, fr, s);
 }
 
 // Whether this kernel takes the sizes (else the caller uses the one-warp-a-row kernel).
@@ -471,12 +582,13 @@ static int launch_static(float* scratch, int* counters, const void* q, int q_str
                          int n_pages, int window, float scale, int n_splits, int device, cudaStream_t s) {
     constexpr int TILE_BYTES = 64 * D * 2;
     constexpr int MERGE_BYTES = (2 * 4 * 16 + 4 * 16 * D + 16 * D + 32) * 4;
-    constexpr int SMEM = AD_STAGES * 2 * TILE_BYTES > MERGE_BYTES ? AD_STAGES * 2 * TILE_BYTES : MERGE_BYTES;
+    constexpr int SMEM = (AD_STAGES * 2 * TILE_BYTES > MERGE_BYTES ? AD_STAGES * 2 * TILE_BYTES : MERGE_BYTES) + 1024;
+    const CUtensorMap none = {};   // this entry point fetches pages by cp.async: it needs no tensor maps
     {
         // First call for this head size on this device: let the kernel use the shared memory it needs.
         std::lock_guard<std::mutex> lock(g_static_mutex);
         if (!(g_static_configured[device] & (1u << (D / 16)))) {
-            cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+            cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<D, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
             if (e != cudaSuccess) {
                 bc_set_error("attention_decode_static: cannot set shared memory to %d: %s", SMEM, cudaGetErrorString(e));
                 return (int)e;
@@ -484,7 +596,7 @@ static int launch_static(float* scratch, int* counters, const void* q, int q_str
             g_static_configured[device] |= 1u << (D / 16);
         }
     }
-    bc_launch(attention_decode_kernel<D>, dim3(n_splits, G, rows), dim3(AD_THREADS), (size_t)SMEM, s, (const bf16*)q, q_stride,
+    bc_launch(attention_decode_kernel<D, false>, dim3(n_splits, G, rows), dim3(AD_THREADS), (size_t)SMEM, s, none, none, (const bf16*)q, q_stride,
               (const bf16*)k_cache, (const bf16*)v_cache, page_table, row_pos, row_slot, (bf16*)out, scratch, counters, H, G, max_pages,
               n_pages, window, scale * 1.4426950408889634f, (const float2*)nullptr, 0, 0, 0, 0, (bf16*)nullptr, (bf16*)nullptr, 0);
     BC_LAUNCH_STATUS();
@@ -550,3 +662,7 @@ extern "C" int bc_attention_decode_static_bf16(const void* q, int q_stride, cons
     bc_set_error("attention_decode_static: no kernel for head size %d", head_dim);
     return BC_ERR_ARG;
 }
+
+// This unit's status word (0, or where a bounded wait for a page gave up), its wait limit and its
+// word of host memory: bc_attention_decode_status / _set_wait_cycles / _bind_host_word.
+TC_STATUS_EXPORTS(attention_decode)

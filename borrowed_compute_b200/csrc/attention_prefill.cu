@@ -79,10 +79,13 @@ attention_prefill_kernel(const bf16* __restrict__ q, int q_stride, const bf16* _
     const int first_pos = window > 0 && start + tok0 + 1 > window ? start + tok0 + 1 - window : 0;
     const int t_begin = first_pos / BC_PAGE, t_end = (start + tok_end - 1) / BC_PAGE + 1;
     const int n_tiles = t_end - t_begin;
+    const int last_pos = start + n_new - 1;               // the last position the sequence holds after this step
 
+    // A tile without a page is neither fetched nor multiplied: what another sequence left in
+    // some page never meets these rows.
     auto load_tile = [&](int tile, int stage) {
-        int page = tile < max_pages ? pages[tile] : -1;
-        if (page < 0 || page >= n_pages) page = 0;   // never used: every position of such a tile is masked below
+        const int page = tile < max_pages ? pages[tile] : -1;
+        if (page < 0 || page >= n_pages) return;
         const bf16* ks = k_cache + ((size_t)page * G + g) * BC_PAGE * D;
         const bf16* vs = v_cache + ((size_t)page * G + g) * BC_PAGE * D;
         const uint32_t kb = ad_smem(smem + (size_t)stage * 2 * TILE_BYTES), vb = kb + TILE_BYTES;
@@ -111,7 +114,18 @@ attention_prefill_kernel(const bf16* __restrict__ q, int q_stride, const bf16* _
         cp_async_commit();
         const int tile = t_begin + it;
         const bool page_ok = tile < max_pages && pages[tile] >= 0 && pages[tile] < n_pages;
+        if (!page_ok) continue;
         const uint32_t kb = ad_smem(smem + (size_t)(it % AP_STAGES) * 2 * TILE_BYTES), vb = kb + TILE_BYTES;
+        if (tile == last_pos / BC_PAGE && last_pos % BC_PAGE != BC_PAGE - 1) {
+            // The sequence's last page: what lies past its last position belongs to nobody (a
+            // sequence that held the page before may have left not-a-numbers there, and 0 x NaN
+            // is NaN in the product with the values): those value rows are cleared in the copy.
+            uint8_t* vt = smem + (size_t)(it % AP_STAGES) * 2 * TILE_BYTES + TILE_BYTES;
+            const int first = last_pos % BC_PAGE + 1;
+            for (int i = threadIdx.x; i < (BC_PAGE - first) * CHUNKS; i += AP_THREADS)
+                *reinterpret_cast<uint4*>(vt + tile_offset<D>(first + i / CHUNKS, i % CHUNKS)) = make_uint4(0u, 0u, 0u, 0u);
+            __syncthreads();
+        }
 
         // S = Q K^T for this warp's 16 rows against the page's 64 positions.
         float s[8][4];

@@ -28,11 +28,9 @@
 // the second query tile) are the softmax and write the output.  Every wait is bounded
 // (about a second); a wait that gives up records where in a status word, and the block
 // frees its TMEM and returns.
-#include <mutex>
-#include <unordered_map>
-
 #include "mma_tiles.cuh"
 #include "tc_ptx.cuh"
+#include "tma_host.cuh"
 
 #define APT_ROWS 128        // query rows of one tile: the M of the MMAs, the lanes of TMEM
 #define APT_PAGES_KEPT 256
@@ -93,6 +91,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     const int first_pos = window > 0 && start + tok0 + 1 > window ? start + tok0 + 1 - window : 0;
     const int t_begin = first_pos / BC_PAGE, t_end = (start + tok_end - 1) / BC_PAGE + 1;
     const int n_tiles = t_end - t_begin;
+    const int last_pos = start + n_new - 1;               // the last position the sequence holds after this step
 
     const uint32_t kv_full0 = smem_u32(&bars[0]), kv_empty0 = smem_u32(&bars[STAGES]), q_full = smem_u32(&bars[2 * STAGES]);
     // Per query tile t and buffer b: scores ready, P written, product done.
@@ -140,8 +139,14 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             for (int j = 0; j < n_tiles; j++) {
                 const int s = j % STAGES;
                 if (j >= STAGES && !mbar_wait(kv_empty0 + 8 * s, ((j / STAGES) & 1) ^ 1, 1)) break;
-                int page = page_at(j);
-                if (page < 0) page = 0;   // never used: every position of such a tile is masked
+                const int page = page_at(j);
+                if (page < 0) {
+                    // No page: nothing is fetched (what another sequence left in some page never
+                    // meets these rows); the stage's phase ends at once, the scores of whatever the
+                    // stage still holds are masked, and its values are cleared before they are used.
+                    mbar_arrive(kv_full0 + 8 * s);
+                    continue;
+                }
                 const int y = (page * G + g) * BC_PAGE;
                 const uint32_t dst = smem_u32(kv_smem + (size_t)s * STAGE_BYTES);
                 mbar_expect_tx(kv_full0 + 8 * s, STAGE_BYTES);
@@ -292,6 +297,19 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 *reinterpret_cast<uint4*>(p_row + ((c8 ^ (lane & 7)) << 4)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
             }
             l += sum;
+            // Value rows that hold no position of this sequence: the whole page if there is none,
+            // else what lies past the sequence's last position in its last page (a sequence that
+            // held the page before may have left not-a-numbers there, and 0 x NaN is NaN in the
+            // product).  The first query tile's threads clear them in the copy, before the
+            // product of this page is let go.
+            const int first_bad = !page_ok ? 0 : min(BC_PAGE, max(0, last_pos - tile * BC_PAGE + 1));
+            if (t == 0 && first_bad < BC_PAGE) {
+                uint8_t* v_tile = kv_smem + (size_t)(j % STAGES) * STAGE_BYTES + DB * KV_BLOCK;
+                for (int c = 32 * q + lane; c < (BC_PAGE - first_bad) * DB * 8; c += 128) {
+                    const int vrow = first_bad + c / (DB * 8), within = c % (DB * 8);
+                    *reinterpret_cast<uint4*>(v_tile + (within >> 3) * KV_BLOCK + vrow * 128 + (within & 7) * 16) = make_uint4(0u, 0u, 0u, 0u);
+                }
+            }
             fence_proxy_async();
             tc_fence_before();
             mbar_arrive(p_full(t, j & 1));
@@ -329,66 +347,6 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 }
 
 // -------------------------------------------------------------------------------- the host
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
-                                  CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_fn() {
-    static EncodeTiledFn fn = nullptr;
-    static std::once_flag once;
-    std::call_once(once, [] {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
-            fn = (EncodeTiledFn)p;
-    });
-    return fn;
-}
-
-// The cache as a matrix [pages * kv heads * 64 positions, D], cut into boxes of 64 x 64.
-static int cache_map(CUtensorMap* map, const void* base, long long rows, int D) {
-    cuuint64_t dims[2] = {(cuuint64_t)D, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)D * 2};
-    cuuint32_t box[2] = {64, BC_PAGE};
-    cuuint32_t elem[2] = {1, 1};
-    CUresult r = encode_fn()(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
-                             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) {
-        bc_set_error("attention_prefill_tc: cuTensorMapEncodeTiled failed (%d) for a cache of %lld rows of %d", (int)r, rows, D);
-        return BC_ERR_DRIVER;
-    }
-    return BC_OK;
-}
-
-// Cache maps are made once per (pointer, shape) and kept: the cache's storage does not move.
-struct CacheKey {
-    const void* p;
-    long long rows;
-    int D;
-    bool operator==(const CacheKey& o) const { return p == o.p && rows == o.rows && D == o.D; }
-};
-struct CacheKeyHash {
-    size_t operator()(const CacheKey& k) const { return std::hash<const void*>()(k.p) ^ ((size_t)k.rows * 1000003u) ^ (size_t)k.D; }
-};
-static std::unordered_map<CacheKey, CUtensorMap, CacheKeyHash> g_cache_maps;
-static std::mutex g_cache_maps_mutex;
-
-static int cached_cache_map(CUtensorMap* out, const void* base, long long rows, int D) {
-    std::lock_guard<std::mutex> lock(g_cache_maps_mutex);
-    CacheKey key{base, rows, D};
-    auto it = g_cache_maps.find(key);
-    if (it == g_cache_maps.end()) {
-        CUtensorMap m;
-        int st = cache_map(&m, base, rows, D);
-        if (st != BC_OK) return st;
-        if (g_cache_maps.size() > 4096) g_cache_maps.clear();
-        it = g_cache_maps.emplace(key, m).first;
-    }
-    *out = it->second;
-    return BC_OK;
-}
-
 // The queries as a tensor [rows][heads][D] inside the fused projection (a row is q_stride
 // elements long), cut into boxes of [tokens][heads of a group][64].
 static int query_map(CUtensorMap* map, const void* q, int q_stride, int total_rows, int H, int D, int group, int tokens_per_tile) {
@@ -396,7 +354,7 @@ static int query_map(CUtensorMap* map, const void* q, int q_stride, int total_ro
     cuuint64_t strides[2] = {(cuuint64_t)D * 2, (cuuint64_t)q_stride * 2};
     cuuint32_t box[3] = {64, (cuuint32_t)group, (cuuint32_t)tokens_per_tile};
     cuuint32_t elem[3] = {1, 1, 1};
-    CUresult r = encode_fn()(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(q), dims, strides, box, elem,
+    CUresult r = bc_encode_tiled_fn()(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(q), dims, strides, box, elem,
                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
@@ -451,7 +409,7 @@ static int g_apt_sms() {
 // Whether this kernel takes the sizes (else the caller uses the mma.sync kernel or the
 // one-warp-a-row kernel): head size 64 or 128, at most 128 heads a kv head.
 extern "C" int bc_attention_prefill_tc_accepts(int H, int G, int D) {
-    return G > 0 && H % G == 0 && H / G <= APT_ROWS && (D == 64 || D == 128) && encode_fn() != nullptr;
+    return G > 0 && H % G == 0 && H / G <= APT_ROWS && (D == 64 || D == 128) && bc_encode_tiled_fn() != nullptr;
 }
 
 // The interface of bc_attention_prefill_bf16, plus total_rows: how many rows q has in all
@@ -478,8 +436,8 @@ extern "C" int bc_attention_prefill_tc_bf16(const void* q, int q_stride, int tot
     int st = query_map(&mq, q, q_stride, total_rows, H, D, group, nt * APT_ROWS / group);
     if (st != BC_OK) return st;
     const long long cache_rows = (long long)n_pages * G * BC_PAGE;
-    if ((st = cached_cache_map(&mk, k_cache, cache_rows, D)) != BC_OK) return st;
-    if ((st = cached_cache_map(&mv, v_cache, cache_rows, D)) != BC_OK) return st;
+    if ((st = bc_cached_cache_map(&mk, k_cache, cache_rows, D, "attention_prefill_tc")) != BC_OK) return st;
+    if ((st = bc_cached_cache_map(&mv, v_cache, cache_rows, D, "attention_prefill_tc")) != BC_OK) return st;
 #define APT_GO(DD, NN) return launch<DD, NN>(mq, mk, mv, page_table, seq_rows, seq_slot, seq_start, out, seqs, max_new, H, G, max_pages, n_pages, window, scale, s)
     if (D == 64 && nt == 1) APT_GO(64, 1);
     if (D == 64) APT_GO(64, 2);

@@ -25,6 +25,9 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_NAME = "libbc_b200_kernels.so"
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ARCH_FLAGS + ["-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=default"]
+# More flags for a build of one's own (say -DBC_TC_TRACE for time stamps inside the product kernels); such a build
+# has another stamp than the plain one, so give it a folder of its own with BC_B200_BUILD_DIR.
+NVCC_FLAGS += os.environ.get("BC_B200_NVCC_EXTRA", "").split()
 ABI_VERSION = 1
 
 _lib: Optional[ctypes.CDLL] = None

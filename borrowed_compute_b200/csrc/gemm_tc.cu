@@ -32,6 +32,7 @@
 // Every wait is bounded: after about a second without progress a thread records where it
 // gave up in a status word, stops waiting, and the block frees its TMEM and returns.
 #include <mutex>
+#include <type_traits>
 #include <unordered_map>
 
 #include <cooperative_groups.h>
@@ -53,7 +54,24 @@ struct TcParams {
     int n_tiles, t_tiles;   // blocks along the weight rows and along the tokens
     int pair_tokens;        // the paired kernel: tokens a tile (64, 128, 192 or 256)
     int starve;             // test hook: the first stage expects 16 bytes that never come, so a bounded wait runs out
+    long long* trace;       // measurement builds (-DBC_TC_TRACE): sixteen time stamps a block, else null
 };
+
+// Time stamps of a block's life, for measurement builds only (compiled out otherwise):
+// 0 entry, 1 set up, 2 first ring of weights asked for, 3 the preceding kernel is done, 4 first
+// stage full, 5 all MMAs issued, 6 accumulator seen, 7 end, 8 partial tile written, 9 after
+// the first cluster barrier, 10 columns finished, 11 after the second cluster barrier.
+#ifdef BC_TC_TRACE
+__device__ __forceinline__ void tc_stamp(const TcParams& p, int what) {
+    if (!p.trace) return;
+    long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    p.trace[((size_t)blockIdx.x + (size_t)gridDim.x * blockIdx.z) * 16 + what] = t;
+}
+#define TC_STAMP(what) tc_stamp(p, what)
+#else
+#define TC_STAMP(what)
+#endif
 
 // Blocks that run at the same time should share operands: the block index walks up to
 // TC_RASTER token tiles first, then the weight tiles, then the next band of token tiles.
@@ -95,6 +113,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[16]), acc_bar = smem_u32(&bars[32]);
 
     if (threadIdx.x == 0) {
+        TC_STAMP(0);
         gave_up = 0;
         for (int s = 0; s < stages; s++) {
             mbar_init(full0 + 8 * s, 1);
@@ -112,6 +131,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     pdl_launch_dependents();
     if (warp == 0) {
         if (lane == 0) {
+            TC_STAMP(1);
             // Weights are written by no kernel, so the first ring of weight tiles is asked
             // for before the wait on the preceding kernel; activations only after it.
             const int ahead = min(stages, k_iters);
@@ -127,7 +147,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 load_w(a, full0 + 8 * i, k, n0);
                 if (N_ACC == 2) load_w(a + A_BYTES, full0 + 8 * i, k, second_row);
             }
+            TC_STAMP(2);
             pdl_wait();
+            TC_STAMP(3);
             for (int i = 0; i < ahead; i++) {
                 const uint32_t a = smem_u32(smem + (size_t)i * STAGE_BYTES);
                 tma_load_2d(a + N_ACC * A_BYTES, &map_x, full0 + 8 * i, (k_first + i) * TC_BK, t0);
@@ -154,6 +176,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 const int s = i % stages;
                 ok = mbar_wait(full0 + 8 * s, (i / stages) & 1, 2);
                 if (!ok) break;
+                if (i == 0) TC_STAMP(4);
                 tc_fence_after();
                 const uint32_t a = smem_u32(smem + (size_t)s * STAGE_BYTES);
                 const uint64_t da = smem_desc(a), db = smem_desc(a + N_ACC * A_BYTES);
@@ -169,6 +192,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 *reinterpret_cast<volatile int*>(&gave_up) = 1;
                 __threadfence_block();
             }
+            TC_STAMP(5);
             mma_commit(acc_bar);   // also after a wait that ran out: the epilogue warps must not be left waiting
         }
     } else {
@@ -188,6 +212,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         pdl_wait();   // the output, the scratch and the counters may still be in use by the preceding kernel
         if (lane == 0) ok = mbar_wait(acc_bar, 0, 3) && *reinterpret_cast<volatile int*>(&gave_up) == 0;
         ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (warp == 2 && lane == 0) TC_STAMP(6);
         tc_fence_after();
         const uint32_t taddr = tmem + ((uint32_t)(32 * q) << 16);
         bool finish = !split;   // this warp writes the output
@@ -291,23 +316,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             }
         }
     }
+    if (warp == 2 && lane == 0) TC_STAMP(8);
     if (p.clustered) {
         // Split-K inside a cluster: block z of the cluster finishes the token columns z, z + S,
         // ..: it adds the S partial tiles in the order 0, 1, 2 .. straight out of the blocks'
         // shared memory.  The same sums as through scratch memory, without the round trip.
         cg::cluster_group cl = cg::this_cluster();
         cl.sync();
+        if (warp == 2 && lane == 0) TC_STAMP(9);
         if (warp >= 2) {
             const int q = warp & 3, row = 32 * q + lane, n = n0 + row;
             const int S = (int)gridDim.z, rank = (int)blockIdx.z;
             const float* base = reinterpret_cast<const float*>(smem) + row;
-            for (int c = rank; c < BN && t0 + c < p.T; c += S) {
-                float v = 0.0f, u = 0.0f;
-                for (int z = 0; z < S; z++) {
-                    const float* theirs = cl.map_shared_rank(base, z);
-                    v += theirs[(size_t)c * TC_BM];
-                    if (EPI == EPI_SWIGLU) u += theirs[(size_t)(BN + c) * TC_BM];
-                }
+            auto write = [&](int c, float v, float u) {
                 if (n < p.N) {
                     const size_t o = (size_t)(t0 + c) * p.N + n;
                     if (EPI == EPI_STORE) ((bf16*)p.out)[o] = __float2bfloat16_rn(v);
@@ -315,12 +336,62 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                     if (EPI == EPI_ADD_F32) atomicAdd(&((float*)p.out)[o], v);
                     if (EPI == EPI_SWIGLU) ((bf16*)p.out)[o] = __float2bfloat16_rn(silu_mul(v, u));
                 }
-            }
+            };
+            // A read of a peer's shared memory takes a good tenth of a microsecond, so all the
+            // reads of two token columns are asked for at once and only then added up, in the
+            // order of the splits as ever (a loop that adds each value as it comes waits for
+            // every read in turn).
+            auto finish = [&](auto splits) {
+                constexpr int SS = decltype(splits)::value;
+                const float* peer[SS];
+#pragma unroll
+                for (int z = 0; z < SS; z++) peer[z] = cl.map_shared_rank(base, z);
+                const int last = min(BN, p.T - t0);
+                for (int c = rank; c < last; c += 2 * SS) {
+                    const int c2 = c + SS;
+                    const bool two = c2 < last;
+                    float v1[SS], u1[SS], v2[SS], u2[SS];
+#pragma unroll
+                    for (int z = 0; z < SS; z++) {
+                        v1[z] = peer[z][(size_t)c * TC_BM];
+                        v2[z] = two ? peer[z][(size_t)c2 * TC_BM] : 0.0f;
+                        if (EPI == EPI_SWIGLU) {
+                            u1[z] = peer[z][(size_t)(BN + c) * TC_BM];
+                            u2[z] = two ? peer[z][(size_t)(BN + c2) * TC_BM] : 0.0f;
+                        }
+                    }
+                    float a = 0.0f, b = 0.0f, ua = 0.0f, ub = 0.0f;
+#pragma unroll
+                    for (int z = 0; z < SS; z++) {
+                        a += v1[z];
+                        b += v2[z];
+                        if (EPI == EPI_SWIGLU) ua += u1[z], ub += u2[z];
+                    }
+                    write(c, a, ua);
+                    if (two) write(c2, b, ub);
+                }
+            };
+            if (S == 8) finish(std::integral_constant<int, 8>());
+            else if (S == 4) finish(std::integral_constant<int, 4>());
+            else if (S == 2) finish(std::integral_constant<int, 2>());
+            else
+                for (int c = rank; c < BN && t0 + c < p.T; c += S) {
+                    float v = 0.0f, u = 0.0f;
+                    for (int z = 0; z < S; z++) {
+                        const float* theirs = cl.map_shared_rank(base, z);
+                        v += theirs[(size_t)c * TC_BM];
+                        if (EPI == EPI_SWIGLU) u += theirs[(size_t)(BN + c) * TC_BM];
+                    }
+                    write(c, v, u);
+                }
         }
+        if (warp == 2 && lane == 0) TC_STAMP(10);
         cl.sync();   // no block may leave while a peer still reads its shared memory
+        if (warp == 2 && lane == 0) TC_STAMP(11);
     }
     tc_fence_before();
     __syncthreads();
+    if (threadIdx.x == 0) TC_STAMP(7);
     if (warp == 1) {
         tc_fence_after();
         tmem_dealloc(tmem, TMEM_COLS);
@@ -782,6 +853,13 @@ extern "C" int bc_gemm_tc_workspace(int T, int N, int epilogue, int splits, long
 static int g_tc_starve = 0;
 extern "C" void bc_gemm_tc_test_starve_next_launch() { g_tc_starve = 1; }
 
+#ifdef BC_TC_TRACE
+// Measurement builds: launch i of the one-block kernel stamps into buf + i * 1024 * 16.
+static long long* g_tc_trace = nullptr;
+static int g_tc_trace_launches = 0, g_tc_trace_next = 0;
+extern "C" void bc_gemm_tc_set_trace(long long* buf, int launches) { g_tc_trace = buf, g_tc_trace_launches = launches, g_tc_trace_next = 0; }
+#endif
+
 // X [T, K] bf16, W [N, K] bf16 (SwiGLU: [2N, K], gate rows then up rows); out [T, N] bf16 or
 // float by epilogue.  K must be a multiple of 8 (a TMA row stride is a multiple of 16
 // bytes); pointers 16-byte aligned.  splits > 1 needs the workspace above.
@@ -817,6 +895,10 @@ extern "C" int bc_gemm_tc_bf16(const void* X, const void* W, void* out, int T, i
     p.pair_tokens = 256;
     p.starve = paired ? 0 : g_tc_starve;
     if (!paired) g_tc_starve = 0;
+    p.trace = nullptr;
+#ifdef BC_TC_TRACE
+    if (!paired && g_tc_trace && g_tc_trace_next < g_tc_trace_launches) p.trace = g_tc_trace + (size_t)(g_tc_trace_next++) * 1024 * 16;
+#endif
     if (paired) {
         switch (epilogue) {
             case EPI_STORE: return launch_pair<EPI_STORE>(mw, mx, p, s);

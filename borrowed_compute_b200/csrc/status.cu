@@ -46,10 +46,12 @@ extern "C" int bc_sm_count() {
 // prompt attention.
 extern "C" int bc_gemm_tc_bind_host_word(int*);
 extern "C" int bc_attention_prefill_tc_bind_host_word(int*);
+extern "C" int bc_attention_decode_bind_host_word(int*);
 extern "C" int bc_gemm_tc_status(int);
 extern "C" int bc_attention_prefill_tc_status(int);
+extern "C" int bc_attention_decode_status(int);
 
-#define BC_STATUS_UNITS 2
+#define BC_STATUS_UNITS 3
 static int* g_status_words[64];   // per device: BC_STATUS_UNITS ints of mapped host memory
 
 extern "C" int bc_status_bind() {
@@ -70,6 +72,7 @@ extern "C" int bc_status_bind() {
     for (int i = 0; i < 16; i++) host[i] = 0;
     int st = bc_gemm_tc_bind_host_word(seen_by_device + 0);
     if (st == 0) st = bc_attention_prefill_tc_bind_host_word(seen_by_device + 1);
+    if (st == 0) st = bc_attention_decode_bind_host_word(seen_by_device + 2);
     if (st != 0) {
         bc_set_error("status_bind: cannot hand the status words to the kernels: %s", cudaGetErrorString((cudaError_t)st));
         return st;
@@ -88,7 +91,8 @@ extern "C" int bc_status_peek(int unit, int reset) {
     if (v != 0 && reset) {
         g_status_words[dev][unit] = 0;
         if (unit == 0) bc_gemm_tc_status(1);
-        else bc_attention_prefill_tc_status(1);
+        else if (unit == 1) bc_attention_prefill_tc_status(1);
+        else bc_attention_decode_status(1);
     }
     return v;
 }

@@ -245,6 +245,8 @@ def sm_count() -> int:
 
 
 _tc_workspace = {}
+_TC_FILL = float(os.environ.get("BC_B200_TC_FILL", "2"))      # measurement knobs: blocks an SM a split product aims at,
+_TC_MIN_K = int(os.environ.get("BC_B200_TC_MIN_K", "8"))       # and the fewest k-steps of 64 a split keeps
 TC_SCRATCH_FLOATS = 148 * 256 * 256   # split-K partial tiles: a capacity of 37 MiB (148 tiles of 256 x 256 floats), whatever the device
 
 
@@ -286,7 +288,7 @@ def gemm_tc_splits(T: int, N: int, K: int, epilogue: int) -> int:
     if bn <= 64:
         # Few tokens: the product streams weights, two blocks fit an SM, and measured rates keep
         # rising up to about two blocks an SM as long as a split still has 8 k-steps of 64.
-        s = max(1, min(2 * sms // tiles, -(-K // 64) // 8, 16, fits))
+        s = max(1, min(int(_TC_FILL * sms) // tiles, -(-K // 64) // _TC_MIN_K, 16, fits))
         # Up to eight splits add up inside a thread-block cluster, which saves the trip through
         # scratch memory; clusters of 2, 4 or 8 place well on the SMs, other sizes measured
         # up to 5 us slower.  So a count up to 12 is rounded down to a power of two.
@@ -334,7 +336,7 @@ def gemm_tc_status(reset: bool = True) -> int:
 def set_wait_cycles(cycles: int = 0) -> None:
     """The most clocks a bounded wait inside the tensor-core kernels may take before it gives
     up and records its status (0: back to the default, about a second)."""
-    for unit in ("gemm_tc", "attention_prefill_tc"):
+    for unit in ("gemm_tc", "attention_prefill_tc", "attention_decode"):
         st = _fn(f"bc_{unit}_set_wait_cycles")(ctypes.c_longlong(int(cycles)))
         if st != 0:
             raise KernelError(f"setting the wait limit of {unit} failed ({st})")
@@ -348,13 +350,14 @@ def gemm_tc_test_starve_next_launch() -> None:
 
 # ------------------------------------------------------------ errors that reach the caller
 
-_STATUS_UNITS = ("the tensor-core product (gemm_tc)", "the tcgen05 prompt attention (attention_prefill_tc)")
+_STATUS_UNITS = ("the tensor-core product (gemm_tc)", "the tcgen05 prompt attention (attention_prefill_tc)", "the decode attention (attention_decode)")
 _WAITS = {
     0: {1: "the loader's wait for a free stage", 2: "the wait for a stage's operands", 3: "the epilogue's wait for the accumulator",
         4: "the wait for the epilogue to hand the accumulator back"},
     1: {1: "the loader's wait for a free stage", 2: "the wait for the queries", 3: "the wait for the first pages", 4: "the wait for P",
         5: "the wait for a page", 6: "the softmax's wait for scores", 7: "the wait for a product that frees P", 8: "the wait for the last product",
         9: "the wait before a rescale"},
+    2: {1: "the wait for a page of keys and values"},
 }
 _bound_devices = set()
 
@@ -482,6 +485,12 @@ def attention_rows(q: torch.Tensor, q_stride: int, k_cache: torch.Tensor, v_cach
 
 
 _decode_scratch = {}
+
+
+def set_attention_decode_tma(on: bool) -> None:
+    """Whether the decode attention fetches pages by TMA where the head size (64, 128) allows
+    (the default) or by cp.async everywhere; both give the same bits.  For measurements and tests."""
+    lib().bc_attention_decode_set_tma(_c_int(1 if on else 0))
 
 
 def attention_decode_accepts(heads: int, kv_heads: int, head_dim: int, dtype: torch.dtype) -> bool:

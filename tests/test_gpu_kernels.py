@@ -110,6 +110,25 @@ def test_gemm_simt(dtype, M, N, K):
     assert np.abs(f64(out) - ref).max() <= out_tol(dtype, ref)
 
 
+def poison(kp, vp, table, lengths, drop_before=None):
+    """Everything in the pool that belongs to no position of any sequence becomes
+    not-a-number: pages nobody holds, and what lies past a sequence's end in its last page
+    (a sequence that held the page before may have left anything there).  ``drop_before[s]``
+    also takes the pages wholly before that position away from sequence s (as a windowed
+    cache gives them back) and poisons them.  A kernel must not let any of it near a result."""
+    owned = np.zeros(kp.shape[:1] + (64,), dtype=bool)
+    for s, n in enumerate(lengths):
+        first = 0 if drop_before is None else (drop_before[s] // 64)
+        for i in range(-(-n // 64)):
+            if i < first:
+                table[s, i] = -1
+                continue
+            owned[table[s, i], : min(64, n - 64 * i)] = True
+    for a in (kp, vp):
+        a[~owned[:, None, :].repeat(a.shape[1], axis=1)] = np.nan
+    return kp, vp
+
+
 def paged(values, page_ids, G, D, n_pages, dtype):
     """Lays values [tokens, G, D] of one sequence out in pages [n_pages, G, 64, D]."""
     pages = np.zeros((n_pages, G, 64, D), dtype=np.float32)
@@ -229,6 +248,7 @@ def test_attention_rows(dtype, window):
     # Rows: the last position of every sequence, two earlier positions of the longest, and padding.
     row_slot = np.array([0, 1, 2, 3, 4, 4, -1, 4], dtype=np.int32)
     row_pos = np.array([0, 31, 63, 64, 199, 63, 0, 128], dtype=np.int32)
+    poison(kp, vp, table, lengths)
     q = (r.standard_normal((8, H * D)) * 2).astype(np.float32)
     out = torch.full((8, H * D), 9.0, dtype=dtype, device="cuda")
     ops.attention_rows(dev(q, dtype), H * D, dev(kp, dtype), dev(vp, dtype), dev(table), dev(row_pos), dev(row_slot), out,
@@ -347,11 +367,24 @@ def test_attention_decode(H, G, D, splits, window):
     row_slot = np.array([0, 1, -1, 2, 3, 4, 5], dtype=np.int32)
     row_pos = np.array([n - 1 for n in lengths[:2]] + [0] + [n - 1 for n in lengths[2:]], dtype=np.int32)
     q = (r.standard_normal((7, H * D)) * 1.5).astype(np.float32)
+    # what no position owns is not-a-number; under a window the pages behind it are gone, as in a windowed cache
+    poison(kp, vp, table, lengths, drop_before=[max(0, n - window) for n in lengths] if window else None)
     args = (dev(q, torch.bfloat16), H * D, dev(kp, torch.bfloat16), dev(vp, torch.bfloat16), dev(table), dev(row_pos), dev(row_slot))
     out = torch.full((7, H * D), 9.0, dtype=torch.bfloat16, device="cuda")
     twin = torch.empty_like(out)
     ops.attention_decode(*args, out, H, G, D, window=window, splits=splits)
     ops.attention_rows(*args, twin, H, G, D, window=window)
+    assert bool(torch.isfinite(out.float()).all()) and bool(torch.isfinite(twin.float()).all())
+    if D in (64, 128):     # pages by TMA or by cp.async: the same bits
+        ops.set_attention_decode_tma(False)
+        try:
+            other = torch.empty_like(out)
+            ops.attention_decode(*args, other, H, G, D, window=window, splits=splits)
+        finally:
+            ops.set_attention_decode_tma(True)
+        assert torch.equal(out, other), "pages fetched by TMA and by cp.async must give the same bits"
+        torch.cuda.synchronize()
+        ops.check_status()
     again = torch.empty_like(out)
     ops.attention_decode(*args, again, H, G, D, window=window, splits=splits)
     assert torch.equal(out, again), "the same launch twice must give the same bits"
@@ -412,6 +445,9 @@ def run_attention_prefill(H, G, D, window, use_tc, cached, new, q_scale=1.5):
         kp += paged(k, pages, G, D, n_pages, torch.bfloat16)
         vp += paged(v, pages, G, D, n_pages, torch.bfloat16)
         qs_.append((r.standard_normal((n, H * D)) * q_scale).astype(np.float32))
+    # what no position owns is not-a-number; under a window the pages behind the first new row's window are gone
+    poison(kp, vp, table, [c + n for c, n in zip(cached, new)],
+           drop_before=[max(0, c + 1 - window) for c in cached] if window else None)
     # sequence order in the step: 0, 1, a padding sequence, then the rest
     order = [0, 1, -1] + list(range(2, len(new)))
     seq_rows, seq_slot, seq_start, rows = [0], [], [], []
@@ -430,6 +466,7 @@ def run_attention_prefill(H, G, D, window, use_tc, cached, new, q_scale=1.5):
                           dev(np.array(seq_start, dtype=np.int32)), out, len(order), max(new), H, G, D, window=window, use_tc=use_tc)
     if use_tc:
         assert ops.attention_prefill_tc_status() == 0
+    assert bool(torch.isfinite(out.float()).all()), "something nobody owns reached a result"
     got, qst = f64(out), stored(q, torch.bfloat16)
     at = 0
     for s in order:
@@ -478,7 +515,7 @@ def test_attention_prefill_on_tcgen05(H, G, D, window, q_scale, tiles):
         ops.set_attention_prefill_tc_tiles(0)
 
 
-@pytest.mark.parametrize("H,G,D", [(6, 3, 48), (4, 4, 16), (16, 1, 32), (32, 8, 128), (8, 2, 64)])
+@pytest.mark.parametrize("H,G,D", [(6, 3, 48), (4, 4, 16), (16, 1, 32), (32, 8, 128), (8, 2, 64), (40, 40, 128)])
 @pytest.mark.parametrize("pairing", [0, 1])
 def test_attention_decode_with_rotation_and_append_fused(H, G, D, pairing):
     """fuse=2 on the raw projection must leave the same cache and give the same output,
@@ -493,8 +530,12 @@ def test_attention_decode_with_rotation_and_append_fused(H, G, D, pairing):
     for s, n in enumerate(lengths):
         for i in range(-(-n // 64)):
             table[s, i] = int(free.pop())
-    kp = dev((r.standard_normal((n_pages, G, 64, D)) * 0.7).astype(np.float32), torch.bfloat16)
-    vp = dev((r.standard_normal((n_pages, G, 64, D)) * 0.7).astype(np.float32), torch.bfloat16)
+    kp_host = (r.standard_normal((n_pages, G, 64, D)) * 0.7).astype(np.float32)
+    vp_host = (r.standard_normal((n_pages, G, 64, D)) * 0.7).astype(np.float32)
+    # The rows about to be appended (position n - 1 of every sequence) and all that no position
+    # owns hold not-a-numbers: the appended row must replace them, the rest must stay away.
+    poison(kp_host, vp_host, table, [n - 1 for n in lengths])
+    kp, vp = dev(kp_host, torch.bfloat16), dev(vp_host, torch.bfloat16)
     rows = len(lengths) + 1
     row_slot = dev(np.array(list(range(len(lengths))) + [-1], dtype=np.int32))
     row_pos = dev(np.array([n - 1 for n in lengths] + [3], dtype=np.int32))
@@ -510,13 +551,22 @@ def test_attention_decode_with_rotation_and_append_fused(H, G, D, pairing):
     q2, k2, v2 = qkv.clone(), kp.clone(), vp.clone()
     got = torch.empty_like(want)
     ops.attention_decode(q2, (H + 2 * G) * D, k2, v2, tab, row_pos, row_slot, got, H, G, D, splits=3, fuse=2, cos_sin=cos_sin, pairing=pairing)
-    assert torch.equal(k1, k2) and torch.equal(v1, v2), "the fused append left another cache"
+    same = lambda a, b: torch.equal(torch.nan_to_num(a.float(), nan=123.0), torch.nan_to_num(b.float(), nan=123.0))
+    assert same(k1, k2) and same(v1, v2), "the fused append left another cache"
     assert torch.equal(q2, qkv), "the fused kernel must not write the projection"
-    assert torch.equal(got, want)
+    assert bool(torch.isfinite(want[:-1].float()).all()) and torch.equal(got, want)
+    if D in (64, 128):
+        ops.set_attention_decode_tma(False)
+        try:
+            q4, k4, v4, other = qkv.clone(), kp.clone(), vp.clone(), torch.empty_like(want)
+            ops.attention_decode(q4, (H + 2 * G) * D, k4, v4, tab, row_pos, row_slot, other, H, G, D, splits=3, fuse=2, cos_sin=cos_sin, pairing=pairing)
+        finally:
+            ops.set_attention_decode_tma(True)
+        assert torch.equal(other, got) and same(k4, k2) and same(v4, v2), "pages by TMA and by cp.async"
     # fuse=1 rotates but leaves the cache alone (a run that reads another run's cache)
     k3, v3 = k1.clone(), v1.clone()
     ops.attention_decode(qkv.clone(), (H + 2 * G) * D, k3, v3, tab, row_pos, row_slot, got, H, G, D, splits=2, fuse=1, cos_sin=cos_sin, pairing=pairing)
-    assert torch.equal(k3, k1) and torch.equal(v3, v1)
+    assert same(k3, k1) and same(v3, v1)
     ops.attention_decode(q1, (H + 2 * G) * D, k1, v1, tab, row_pos, row_slot, want, H, G, D, splits=2)
     assert torch.equal(got, want)
 
