@@ -44,6 +44,9 @@ def main(argv=None) -> int:
     g.add_argument("--stop-ids", default=None, help="token ids that end a sequence (default: the model's eos ids)")
     g.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     g.add_argument("--max-batch", type=int, default=None, help="most sequences that run together; more run as later batches")
+    g.add_argument("--max-seq", type=int, default=None, help="positions a sequence can reach (default: the longest prompt plus --max-tokens)")
+    g.add_argument("--include-stop", action="store_true", help="a stop id that ends a sequence is printed as its last id")
+    g.add_argument("--stats", action="store_true", help="print the call's Stats as one JSON line on standard output, after the tokens")
     g.add_argument("--device", default="cuda:0")
     r = sub.add_parser("random", help="write a model folder of random weights for a config.json")
     r.add_argument("config", help="a config.json")
@@ -74,14 +77,23 @@ def main(argv=None) -> int:
     from .sampling import Sampling
 
     longest = max(len(p) for p in prompts) + args.max_tokens
+    if args.max_seq is not None:
+        if args.max_seq < longest:
+            ap.error(f"--max-seq {args.max_seq} is less than the longest prompt plus --max-tokens ({longest})")
+        longest = args.max_seq
     batch = min(len(prompts), args.max_batch or len(prompts))
     model = Local.load(args.model, dtype=args.dtype, device=args.device, max_seq=longest, max_slots=batch,
                        max_tokens=batch * (-(-longest // 64) * 64))
     seed = args.seed if args.seed is not None else time.time_ns() & ((1 << 64) - 1)
     stops = None if args.stop_ids is None else [int(t) for t in args.stop_ids.replace(",", " ").split()]
-    out, stats = model.generate(prompts, args.max_tokens, Sampling(args.temperature, args.top_p, seed), stop_ids=stops, max_batch=batch)
+    out, stats = model.generate(prompts, args.max_tokens, Sampling(args.temperature, args.top_p, seed), stop_ids=stops, max_batch=batch,
+                                include_stop=args.include_stop)
     for tokens in out:
         print(",".join(str(t) for t in tokens))
+    if args.stats:
+        print(json.dumps({"prompt_tokens": stats.prompt_tokens, "generated": stats.generated, "passes": stats.passes,
+                          "first_token_ms": round(stats.first_token_ms, 3), "total_ms": round(stats.total_ms, 3),
+                          "decode_tokens_per_second": round(stats.decode_tokens_per_second, 2)}))
     print(f"bc: {stats.prompt_tokens} prompt tokens, first token after {stats.first_token_ms:.0f} ms; {stats.generated} tokens in "
           f"{stats.passes} passes, {stats.decode_tokens_per_second:.1f} tokens/s", file=sys.stderr)
     return 0

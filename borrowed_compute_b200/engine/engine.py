@@ -24,7 +24,7 @@ from .. import ops
 from ..cache import PAGE, PagedCache
 from ..config.errors import CacheError
 from ..parts.base import Runtime, StepContext
-from ..weights import TensorSource, load_tensors, random_tensors, read_config_json
+from ..weights import TensorSource, load_tensors, random_tensors, read_config_json, read_generation_stop_ids
 from .batch import StepEntry, StepPlan, plan_step
 from .model import DecoderModel, model_for_config
 
@@ -155,6 +155,7 @@ class Engine:
         self.config, self.model, self.typed_config, self.rt = dict(config), model, typed_config, rt
         self.vocab_size = model.spec.vocab_size
         self.max_seq = max_seq
+        self.stop_ids: tuple = tuple(model.spec.stop_ids)    # ids that end a sequence by default: config.json's, plus generation_config.json's
         needs, states, memory_of = model.memory_needs()
         self.cache = PagedCache(rt, needs, states, memory_of, max_tokens=max_tokens, n_slots=max_slots, max_seq=max_seq)
         self._ints: Optional[torch.Tensor] = None
@@ -164,7 +165,7 @@ class Engine:
         self._ahead: Optional[_Ahead] = None
         self.last_graph: Optional[_DecodeGraph] = None   # the captured step the last call of step() replayed, if it did
         # Decode steps replay a captured CUDA graph unless a part plans on the host.
-        self.use_graphs = all(part.graph_safe for _, part in model.named_parts())
+        self.use_graphs = all(part.graph_safe for _, part in model.named_parts()) and not ops.bounds_check
         self.steps_run = 0
 
     # ------------------------------------------------------------------------ construction
@@ -198,13 +199,17 @@ class Engine:
 
     @classmethod
     def from_folder(cls, folder: str, dtype="bfloat16", device="cuda:0", max_tokens: Optional[int] = None,
-                    max_slots: Optional[int] = None, max_seq: Optional[int] = None) -> "Engine":
-        """Loads ``config.json`` and the safetensors of a model folder."""
+                    max_slots: Optional[int] = None, max_seq: Optional[int] = None, progress=None) -> "Engine":
+        """Loads ``config.json`` and the safetensors of a model folder; ``progress(done,
+        total)`` is called after every tensor brought to the device (the reference reports
+        bytes fetched as it goes, crates/bc-infer/src/lib.rs:33-47)."""
         config = read_config_json(folder)
         typed, model = model_for_config(config)
         rt = cls._runtime(dtype, device)
         eng = cls._sized(config, model, typed, rt, max_tokens, max_slots, max_seq)
-        model.load(load_tensors(model.expected_tensors(), TensorSource(folder), rt), rt)
+        model.load(load_tensors(model.expected_tensors(), TensorSource(folder), rt, progress), rt)
+        more = read_generation_stop_ids(folder, eng.vocab_size)
+        eng.stop_ids = tuple(dict.fromkeys(eng.stop_ids + more))
         return eng
 
     @classmethod

@@ -87,8 +87,10 @@ class Backend:
 
 def run_generation(backend: Backend, prompts: Sequence[Sequence[int]], max_tokens: int, samplings: Sequence[Sampling],
                    stop_ids: Sequence[int] = (), on_token: Optional[Callable[[int, int], None]] = None,
-                   clock: Callable[[], float] = time.perf_counter) -> tuple:
-    """Generates up to ``max_tokens`` after each prompt.  Returns (tokens per prompt, Stats)."""
+                   clock: Callable[[], float] = time.perf_counter, include_stop: bool = False) -> tuple:
+    """Generates up to ``max_tokens`` after each prompt.  Returns (tokens per prompt, Stats).
+    A stop id ends its sequence and is left out of it, or, with ``include_stop``, is its last
+    id (counted against ``max_tokens`` like any other)."""
     if len(samplings) != len(prompts):
         raise ValueError("one Sampling per prompt")
     if max_tokens < 0:
@@ -105,9 +107,13 @@ def run_generation(backend: Backend, prompts: Sequence[Sequence[int]], max_token
 
     def push(i: int, tok: int) -> bool:
         """Takes a token for sequence i; False once the sequence has ended."""
-        if tok in stops or len(out[i]) >= max_tokens:
+        if len(out[i]) >= max_tokens or (tok in stops and not include_stop):
             return False
         out[i].append(tok)
+        if tok in stops:
+            if on_token is not None:
+                on_token(i, tok)
+            return False
         if on_token is not None:
             on_token(i, tok)
         return len(out[i]) < max_tokens

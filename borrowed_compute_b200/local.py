@@ -26,9 +26,12 @@ class Local:
 
     @classmethod
     def load(cls, source: str, dtype: str = "bfloat16", device: str = "cuda:0", max_tokens: Optional[int] = None,
-             max_slots: Optional[int] = None, max_seq: Optional[int] = None) -> "Local":
-        """Loads a model folder (config.json + safetensors)."""
-        return cls(Engine.from_folder(source, dtype=dtype, device=device, max_tokens=max_tokens, max_slots=max_slots, max_seq=max_seq))
+             max_slots: Optional[int] = None, max_seq: Optional[int] = None,
+             progress: Optional[Callable[[int, int], None]] = None) -> "Local":
+        """Loads a model folder (config.json + safetensors); ``progress(done, total)`` reports
+        the tensors brought to the device as it goes (lib.rs:33-47, ``load_with``)."""
+        return cls(Engine.from_folder(source, dtype=dtype, device=device, max_tokens=max_tokens, max_slots=max_slots, max_seq=max_seq,
+                                      progress=progress))
 
     @classmethod
     def random(cls, config: Mapping[str, Any], seed: int = 0, dtype: str = "bfloat16", device: str = "cuda:0",
@@ -38,7 +41,7 @@ class Local:
 
     @property
     def stop_ids(self) -> Tuple[int, ...]:
-        return tuple(self.engine.model.spec.stop_ids)
+        return tuple(self.engine.stop_ids)
 
     def scores(self, tokens: Sequence[int], pos: int) -> torch.Tensor:
         """Scores after each of ``tokens``, placed at ``pos..`` of this object's own
@@ -63,15 +66,19 @@ class Local:
     def generate(self, prompts: Union[Sequence[int], Sequence[Sequence[int]]], max_tokens: int,
                  sampling: Union[Sampling, Sequence[Sampling], None] = None,
                  on_token: Optional[Callable[[int, int], None]] = None, stop_ids: Optional[Sequence[int]] = None,
-                 max_batch: Optional[int] = None) -> Tuple[Any, Stats]:
+                 max_batch: Optional[int] = None, include_stop: bool = False) -> Tuple[Any, Stats]:
         """Generates up to ``max_tokens`` after each prompt.  One prompt (a list of ids)
         gives one list back, several give a list of lists.  ``stop_ids`` default to the
-        model's end-of-sequence ids; a stop id ends a sequence and is not returned."""
+        model's end-of-sequence ids (config.json's and generation_config.json's); a stop id
+        ends a sequence and is not returned, unless ``include_stop`` asks for it as the
+        sequence's last id (the reference's self-fed runs return it so,
+        crates/bc-mesh/src/engine.rs:355)."""
         single = len(prompts) > 0 and isinstance(prompts[0], int)
         batch: List[Sequence[int]] = [prompts] if single else list(prompts)
         if sampling is None:
             sampling = Sampling()
         samplings = [sampling] * len(batch) if isinstance(sampling, Sampling) else list(sampling)
         backend = EngineBackend(self.engine, max_batch=max_batch)
-        out, stats = run_generation(backend, batch, max_tokens, samplings, self.stop_ids if stop_ids is None else stop_ids, on_token)
+        out, stats = run_generation(backend, batch, max_tokens, samplings, self.stop_ids if stop_ids is None else stop_ids, on_token,
+                                    include_stop=include_stop)
         return (out[0] if single else out), stats

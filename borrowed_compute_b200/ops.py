@@ -94,6 +94,43 @@ def _suffix(dtype: torch.dtype) -> str:
     raise KernelError(f"no kernels for {dtype}: float32 and bfloat16 only")
 
 
+# ------------------------------------------------------------------ the bounds-checked mode
+# With BC_B200_BOUNDS_CHECK=1 (or ``bounds_check = True``) every launcher that takes indices
+# (tokens, slots, positions, page tables, gathered rows) first brings them to the host and
+# holds each against the extent of what it indexes; a bad one raises KernelError naming the
+# tensor, the index and the extent, and nothing is launched.  The kernels themselves guard
+# tokens, slots and pages on every build; this mode also catches what they would only skip
+# (a position past the table, a gathered row past the rows) and what they trust (a slot past
+# the table's rows).  It synchronises on every launch, so it is for finding a fault, not for
+# serving; an engine built in this mode steps without captured graphs.  It stands in for a
+# memory checker run under the kernels, which cannot be had everywhere.
+bounds_check = os.environ.get("BC_B200_BOUNDS_CHECK", "0") == "1"
+
+
+def _bounds(what: str, values: Optional[torch.Tensor], extent: int, count: Optional[int] = None, lowest: int = 0) -> None:
+    """Every one of the first ``count`` values lies in [lowest, extent)."""
+    if not bounds_check or values is None or torch.cuda.is_current_stream_capturing():
+        return
+    v = values.reshape(-1)[: values.numel() if count is None else count]
+    if v.numel() == 0:
+        return
+    bad = ((v < lowest) | (v >= extent)).nonzero()
+    if bad.numel():
+        i = int(bad[0])
+        raise KernelError(f"bounds check: {what}[{i}] = {int(v[i])} is outside [{lowest}, {extent})")
+
+
+def _bounds_paged(who: str, rows: int, row_pos: torch.Tensor, row_slot: torch.Tensor, page_table: torch.Tensor, n_pages: int) -> None:
+    """Slots name rows of the page table (or are -1: padding), positions fit the table's
+    width, and every page the table names exists."""
+    if not bounds_check or torch.cuda.is_current_stream_capturing():
+        return
+    _bounds(f"{who}: row_slot", row_slot, page_table.shape[0], rows, lowest=-1)
+    live = row_slot.reshape(-1)[:rows] >= 0
+    _bounds(f"{who}: row_pos", row_pos.reshape(-1)[:rows][live], page_table.shape[1] * PAGE)
+    _bounds(f"{who}: page_table", page_table, n_pages, lowest=-1)
+
+
 launches = 0   # kernels launched through this module since import (a captured graph replays them uncounted)
 _KERNELS_PER_CALL = {"bc_argmax": 2}   # launchers that start more than one kernel
 
@@ -151,6 +188,7 @@ def embed(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor) -> None:
     rows, (V, E) = tokens.numel(), table.shape
     if out.shape != (rows, E):
         raise KernelError(f"embed: out is {tuple(out.shape)}, wanted {(rows, E)}")
+    _bounds("embed: tokens", tokens, V)
     _call(_fn("bc_embed_" + _suffix(table.dtype)), _ptr(table), _ptr(tokens), _ptr(out), _c_int(rows), _c_int(E), _c_int(V), _stream())
 
 
@@ -167,6 +205,7 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, eps: float
         _need(gather, "gather", torch.int32)
         if gather.numel() != rows:
             raise KernelError("rmsnorm: gather and out differ in rows")
+        _bounds("rmsnorm: gather", gather, x.shape[0])
     elif x.shape[0] != rows:
         raise KernelError("rmsnorm: x and out differ in rows")
     _call(_fn("bc_rmsnorm_" + _suffix(out.dtype)), _ptr(x), _ptr(weight), _ptr(out), _ptr(gather), _c_int(rows), _c_int(E),
@@ -206,6 +245,9 @@ def rope_append(qkv: torch.Tensor, cos_sin: Optional[torch.Tensor], row_pos: tor
         _need(cos_sin, "cos_sin", torch.float32)
         if tuple(cos_sin.shape[1:]) != (head_dim // 2, 2):
             raise KernelError(f"rope_append: cos_sin is {tuple(cos_sin.shape)}, wanted [positions, {head_dim // 2}, 2]")
+    _bounds_paged("rope_append", rows, row_pos, row_slot, page_table, n_pages)
+    if cos_sin is not None and bounds_check and not torch.cuda.is_current_stream_capturing():
+        _bounds("rope_append: row_pos (against the rotary table)", row_pos.reshape(-1)[:rows][row_slot.reshape(-1)[:rows] >= 0], cos_sin.shape[0])
     _call(_fn("bc_rope_append_" + _suffix(qkv.dtype)), _ptr(qkv), _ptr(cos_sin), _ptr(row_pos), _ptr(row_slot), _ptr(page_table),
           _ptr(k_cache), _ptr(v_cache), _c_int(rows), _c_int(heads), _c_int(kv_heads), _c_int(head_dim), _c_int(pairing),
           _c_int(page_table.shape[1]), _c_int(n_pages), _c_int(1 if write_cache else 0), _stream())
@@ -479,6 +521,7 @@ def attention_rows(q: torch.Tensor, q_stride: int, k_cache: torch.Tensor, v_cach
         raise KernelError(f"attention: cache is {tuple(k_cache.shape)}, wanted [pages, {kv_heads}, {PAGE}, {head_dim}]")
     if scale is None:
         scale = 1.0 / float(head_dim) ** 0.5
+    _bounds_paged("attention_rows", rows, row_pos, row_slot, page_table, k_cache.shape[0])
     _call(_fn("bc_attention_rows_" + _suffix(q.dtype)), _ptr(q), _c_int(q_stride), _ptr(k_cache), _ptr(v_cache), _ptr(page_table),
           _ptr(row_pos), _ptr(row_slot), _ptr(out), _c_int(rows), _c_int(heads), _c_int(kv_heads), _c_int(head_dim),
           _c_int(page_table.shape[1]), _c_int(k_cache.shape[0]), _c_int(window), _c_float(scale), _stream())
@@ -564,6 +607,9 @@ def attention_decode(q: torch.Tensor, q_stride: int, k_cache: torch.Tensor, v_ca
         _need(cos_sin, "cos_sin", torch.float32)
         if tuple(cos_sin.shape[1:]) != (head_dim // 2, 2):
             raise KernelError(f"attention_decode: cos_sin is {tuple(cos_sin.shape)}, wanted [positions, {head_dim // 2}, 2]")
+        if bounds_check and not torch.cuda.is_current_stream_capturing():
+            _bounds("attention_decode: row_pos (against the rotary table)", row_pos.reshape(-1)[:rows][row_slot.reshape(-1)[:rows] >= 0], cos_sin.shape[0])
+    _bounds_paged("attention_decode", rows, row_pos, row_slot, page_table, k_cache.shape[0])
     _call(_fn("bc_attention_decode_fused_bf16"), _ptr(q), _c_int(q_stride), _ptr(k_cache), _ptr(v_cache), _ptr(page_table), _ptr(row_pos),
           _ptr(row_slot), _ptr(out), _ptr(scratch), _ptr(counters), _c_int(rows), _c_int(heads), _c_int(kv_heads), _c_int(head_dim),
           _c_int(page_table.shape[1]), _c_int(k_cache.shape[0]), _c_int(window), _c_float(scale), _c_int(splits), _ptr(cos_sin),
@@ -608,6 +654,13 @@ def attention_prefill(q: torch.Tensor, q_stride: int, k_cache: torch.Tensor, v_c
         raise KernelError("attention_prefill: fewer sequence entries than sequences")
     if scale is None:
         scale = 1.0 / float(head_dim) ** 0.5
+    if bounds_check and not torch.cuda.is_current_stream_capturing():
+        _bounds("attention_prefill: seq_slot", seq_slot, page_table.shape[0], seqs, lowest=-1)
+        _bounds("attention_prefill: seq_rows", seq_rows, out.shape[0] + 1, seqs + 1)
+        live = seq_slot.reshape(-1)[:seqs] >= 0
+        ends = (seq_start.reshape(-1)[:seqs] + seq_rows.reshape(-1)[1:seqs + 1] - seq_rows.reshape(-1)[:seqs])[live]
+        _bounds("attention_prefill: a sequence's last position + 1", ends, page_table.shape[1] * PAGE + 1)
+        _bounds("attention_prefill: page_table", page_table, k_cache.shape[0], lowest=-1)
     if use_tc is None:
         use_tc = attention_prefill_tc_accepts(heads, kv_heads, head_dim, q, q_stride)
     if use_tc:

@@ -36,6 +36,29 @@ def read_config_json(folder: str) -> Dict[str, Any]:
     return cfg
 
 
+def read_generation_stop_ids(folder: str, vocab_size: int) -> tuple:
+    """The end-of-sequence ids of ``generation_config.json``, if the folder has one: an
+    integer or a list of them.  Published folders name there the ids that end a reply
+    (several, for chat models), beside the one of config.json."""
+    path = os.path.join(folder, "generation_config.json")
+    if not os.path.isfile(path):
+        return ()
+    try:
+        with open(path) as f:
+            eos = json.load(f).get("eos_token_id")
+    except (OSError, json.JSONDecodeError, AttributeError) as e:
+        raise ConfigError(f"cannot read {path}: {e}") from e
+    if eos is None:
+        return ()
+    ids = [eos] if isinstance(eos, int) and not isinstance(eos, bool) else eos
+    if not isinstance(ids, (list, tuple)) or not all(isinstance(e, int) and not isinstance(e, bool) for e in ids):
+        raise ConfigError(f"{path}: 'eos_token_id' must be an integer or a list of integers, got {eos!r}")
+    for e in ids:
+        if not 0 <= e < vocab_size:
+            raise ConfigError(f"{path}: eos_token_id {e} is outside the vocabulary of {vocab_size}")
+    return tuple(ids)
+
+
 def check_tensors(expected: Mapping[str, TensorSpec], have: Mapping[str, Tuple[torch.dtype, Tuple[int, ...]]], where: str) -> None:
     """Raises one WeightsError naming all that is missing, unexpected or misshapen."""
     missing = [n for n, s in expected.items() if n not in have and not s.optional]

@@ -76,3 +76,21 @@ def test_expected_tensors_follow_the_config():
     assert b["lm_head.weight"].optional                       # tied: the folder may or may not store it
     assert a["model.norm.weight"].role == "vector" and a["model.embed_tokens.weight"].role == "matrix"
     assert len(a) == 1 + 2 * 9 + 2 and len(b) == 1 + 3 * 9 + 2
+
+
+def test_generation_config_adds_stop_ids(tmp_path):
+    import json
+
+    from borrowed_compute_b200.weights import read_generation_stop_ids
+
+    assert read_generation_stop_ids(str(tmp_path), 100) == ()
+    (tmp_path / "generation_config.json").write_text(json.dumps({"eos_token_id": [7, 9], "temperature": 0.6}))
+    assert read_generation_stop_ids(str(tmp_path), 100) == (7, 9)
+    (tmp_path / "generation_config.json").write_text(json.dumps({"eos_token_id": 5}))
+    assert read_generation_stop_ids(str(tmp_path), 100) == (5,)
+    (tmp_path / "generation_config.json").write_text(json.dumps({"eos_token_id": 100}))
+    with pytest.raises(ConfigError, match="outside the vocabulary"):
+        read_generation_stop_ids(str(tmp_path), 100)
+    (tmp_path / "generation_config.json").write_text(json.dumps({"eos_token_id": "x"}))
+    with pytest.raises(ConfigError, match="integer"):
+        read_generation_stop_ids(str(tmp_path), 100)

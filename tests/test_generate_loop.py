@@ -183,3 +183,14 @@ def test_a_pass_begun_ahead_is_never_a_sequences_last_by_count():
     steps = [e for e in b.log if e[0] in ("advance", "chained", "finish")]
     assert steps[:4] == [("advance", (0, 1)), ("chained", (0, 1)), ("chained", (0, 1)), ("finish", 1)]
     assert steps[4] == ("advance", (0,)) and not b.live
+
+
+def test_a_stop_id_can_be_kept_as_the_last_id():
+    for backend in (Scripted(max_batch=4), Chaining(max_batch=4)):
+        seen = []
+        out, stats = run_generation(backend, [[1], [10], [30]], 8, [Sampling()] * 3, stop_ids=[13, 31], include_stop=True,
+                                    on_token=lambda i, t: seen.append((i, t)))
+        assert out == [[2, 3, 4, 5, 6, 7, 8, 9], [11, 12, 13], [31]] and not backend.live
+        assert stats.generated == 12 and sorted(seen) == sorted((i, t) for i, o in enumerate(out) for t in o)
+    out, _ = run_generation(Scripted(max_batch=1), [[10]], 2, [Sampling()], stop_ids=[13], include_stop=True)
+    assert out == [[11, 12]], "the count ends a sequence before a stop id that lies past it"

@@ -125,3 +125,35 @@ def test_command_line(locals_, tmp_path):
     got = [[int(t) for t in line.split(",")] for line in res.stdout.strip().splitlines()]
     assert got == [plain_llama.generate(cfg, weights, p, 6) for p in prompts]
     assert "prompt tokens, first token after" in res.stderr and "tokens/s" in res.stderr
+
+
+def test_command_line_options_and_generation_config(locals_, tmp_path):
+    """--max-seq, --stats and --include-stop; stop ids from generation_config.json; load progress."""
+    import json
+    import shutil
+
+    from borrowed_compute_b200 import Local
+
+    _, cfg, weights, folder = locals_("A", "float32")
+    free = plain_llama.generate(cfg, weights, [5, 17, 3], 6)
+    mine = str(tmp_path / "with_generation_config")
+    shutil.copytree(folder, mine)
+    with open(os.path.join(mine, "generation_config.json"), "w") as f:
+        json.dump({"eos_token_id": [free[3]]}, f)
+    seen = []
+    model = Local.load(mine, dtype="float32", max_tokens=256, progress=lambda done, total: seen.append((done, total)))
+    assert free[3] in model.stop_ids and cfg["eos_token_id"] in model.stop_ids
+    assert seen and seen[-1][0] == seen[-1][1] == len(seen)
+    cut = free[:free.index(free[3])]
+    assert model.generate([5, 17, 3], 6)[0] == cut
+    assert model.generate([5, 17, 3], 6, include_stop=True)[0] == cut + [free[3]]
+    res = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "bc-infer"), "generate", mine, "5,17,3", "--max-tokens", "6", "--dtype", "float32",
+                          "--max-seq", "64", "--stats", "--include-stop"], capture_output=True, text=True, timeout=300)
+    assert res.returncode == 0, res.stderr
+    lines = res.stdout.strip().splitlines()
+    assert [int(t) for t in lines[0].split(",")] == cut + [free[3]]
+    stats = json.loads(lines[1])
+    assert stats["prompt_tokens"] == 3 and stats["generated"] == len(cut) + 1 and stats["total_ms"] >= stats["first_token_ms"] > 0
+    res = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "bc-infer"), "generate", mine, "5,17,3", "--max-tokens", "6", "--max-seq", "5"],
+                         capture_output=True, text=True, timeout=300)
+    assert res.returncode != 0 and "--max-seq" in res.stderr

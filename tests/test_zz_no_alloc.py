@@ -4,8 +4,9 @@ It serves callers that cannot hand the kernel scratch memory because they cannot
 any: the whole GPU already sits in an arena of theirs, or they run where an allocation is
 forbidden or would stall the device.  Its scratch is an array inside the library's device
 image.  Here it is called through its exported C symbol, twice in a row with different
-inputs, and each result is held against the ordinary entry point's (which gets scratch from
-the caller) on the same inputs; free device memory must not move across a call, and a
+inputs, and each result is held against the formula in float64 and against the ordinary
+entry point's (which gets scratch from the caller) on the same inputs; free device memory
+must not move across a call, and a
 launch too large for the built-in array must be refused with a clear error.  The file's
 name makes pytest collect it last."""
 
@@ -41,6 +42,29 @@ def make_case(seed, H, G, D, lengths, n_pages=40):
                 pos=cuda(row_pos), slot=cuda(row_slot), rows=rows, H=H, G=G, D=D, max_pages=max_pages, n_pages=n_pages)
 
 
+def float64_attention(c, window=0):
+    """The formula itself (crates/bc-infer/src/model.rs:448-481) in float64 on the values as
+    bfloat16 stores them: every row's heads against its sequence's cached positions."""
+    q, k, v = (c[n].float().cpu().numpy().astype(np.float64) for n in ("q", "k", "v"))
+    table, pos, slot = (c[n].cpu().numpy() for n in ("table", "pos", "slot"))
+    H, G, D = c["H"], c["G"], c["D"]
+    out = np.zeros((c["rows"], H, D))
+    for r in range(c["rows"]):
+        if slot[r] < 0:
+            continue
+        n = int(pos[r]) + 1
+        lo = max(0, n - window) if window > 0 else 0
+        where = [(int(table[slot[r], t // 64]), t % 64) for t in range(lo, n)]
+        for h in range(H):
+            g = h // (H // G)
+            keys = np.stack([k[p, g, i] for p, i in where])
+            vals = np.stack([v[p, g, i] for p, i in where])
+            s = keys @ q[r].reshape(H, D)[h] / np.sqrt(D)
+            w = np.exp(s - s.max())
+            out[r, h] = (w / w.sum()) @ vals
+    return out.reshape(c["rows"], H * D)
+
+
 def call_static(lib, c, out, splits, window=0):
     fn = lib.bc_attention_decode_static_bf16
     fn.restype = ctypes.c_int
@@ -56,6 +80,9 @@ def test_static_scratch_entry_point_matches_the_ordinary_one():
 
     lib = ops.lib()
     cases = [(make_case(1, 32, 8, 128, [700, 64, 1, 65, 300]), 5, 0), (make_case(2, 6, 3, 48, [130, 17, 1000]), 3, 70)]
+    for c, splits, window in cases:                           # each head size's first call on a device does set-up work: done here,
+        warm = torch.empty((c["rows"], c["H"] * c["D"]), dtype=torch.bfloat16, device="cuda")       # so that every call below is an ordinary one
+        assert call_static(lib, c, warm, splits, window) == 0, lib.bc_last_error().decode()
     for i, (c, splits, window) in enumerate(cases):           # two calls in a row; the second reuses what the first left
         want = torch.empty((c["rows"], c["H"] * c["D"]), dtype=torch.bfloat16, device="cuda")
         ops.attention_decode(c["q"], c["H"] * c["D"], c["k"], c["v"], c["table"], c["pos"], c["slot"], want, c["H"], c["G"], c["D"],
@@ -66,9 +93,11 @@ def test_static_scratch_entry_point_matches_the_ordinary_one():
         status = call_static(lib, c, got, splits, window)
         torch.cuda.synchronize()
         assert status == 0, lib.bc_last_error().decode()
-        if i > 0:                                             # the first call on a device may still do set-up work
-            assert torch.cuda.mem_get_info()[0] == free_before, "the call changed the amount of free device memory"
+        assert torch.cuda.mem_get_info()[0] == free_before, "the call changed the amount of free device memory"
         assert torch.isfinite(got.float()).all()
+        # against the formula in float64 (probabilities are rounded to bfloat16 before they weigh the values)
+        ref = float64_attention(c, window)
+        assert np.abs(got.float().cpu().numpy() - ref).max() <= 2.0 ** -7 * (1 + np.abs(ref).max())
         # Both run the same kernel with the same split of the work: within the decode kernel's tolerance, and in fact equal.
         assert (got.float() - want.float()).abs().max().item() <= 2.0 ** -7 * (1 + want.float().abs().max().item())
         assert torch.equal(got, want)
