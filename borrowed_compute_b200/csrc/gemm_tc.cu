@@ -255,22 +255,28 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         if (finish && ok) {
             const float* all = split ? p.partial + (size_t)tile * gridDim.z * part_tile + 32 * q + lane : nullptr;
             // 16 token columns of one accumulator: apply the epilogue and write.
+            // The sixteen results are worked out first, with nothing that branches between them,
+            // so that their chains of exponential, reciprocal and rounding run side by side;
+            // then they are stored (a loop that tests, computes and stores one column at a time
+            // runs the chains one after another: measured 60 ns a column).
             auto emit = [&](const uint32_t* v, const uint32_t* u, int cc) {
                 const int acc_i = cc / BN, c0 = cc - acc_i * BN;     // which accumulator (stacked weight tile), which token column
                 const int n = n_first + TC_BM * acc_i;
+                if (n >= p.N) return;
+                float r[16];
+#pragma unroll
+                for (int j = 0; j < 16; j++) r[j] = EPI == EPI_SWIGLU ? silu_mul(__uint_as_float(v[j]), __uint_as_float(u[j])) : __uint_as_float(v[j]);
+                const int t_first = t0 + c0;
+                const size_t o = (size_t)t_first * p.N + n;
 #pragma unroll
                 for (int j = 0; j < 16; j++) {
-                    const int t = t0 + c0 + j;
-                    const float val = __uint_as_float(v[j]);
-                    if (t < p.T && n < p.N) {
-                        const size_t o = (size_t)t * p.N + n;
-                        if (EPI == EPI_STORE) ((bf16*)p.out)[o] = __float2bfloat16_rn(val);
-                        if (EPI == EPI_STORE_F32) ((float*)p.out)[o] = val;
-                        // One thread owns each element, so a fire-and-forget reduction gives the same
-                        // sum as a load, add and store, without waiting for the load.
-                        if (EPI == EPI_ADD_F32) atomicAdd(&((float*)p.out)[o], val);
-                        if (EPI == EPI_SWIGLU) ((bf16*)p.out)[o] = __float2bfloat16_rn(silu_mul(val, __uint_as_float(u[j])));
-                    }
+                    if (t_first + j >= p.T) break;
+                    const size_t at = o + (size_t)j * p.N;
+                    if (EPI == EPI_STORE || EPI == EPI_SWIGLU) ((bf16*)p.out)[at] = __float2bfloat16_rn(r[j]);
+                    if (EPI == EPI_STORE_F32) ((float*)p.out)[at] = r[j];
+                    // One thread owns each element, so a fire-and-forget reduction gives the same
+                    // sum as a load, add and store, without waiting for the load.
+                    if (EPI == EPI_ADD_F32) atomicAdd(&((float*)p.out)[at], r[j]);
                 }
             };
             constexpr int TOTAL = OUT_TILES * BN;
@@ -337,38 +343,41 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                     if (EPI == EPI_SWIGLU) ((bf16*)p.out)[o] = __float2bfloat16_rn(silu_mul(v, u));
                 }
             };
-            // A read of a peer's shared memory takes a good tenth of a microsecond, so all the
-            // reads of two token columns are asked for at once and only then added up, in the
-            // order of the splits as ever (a loop that adds each value as it comes waits for
-            // every read in turn).
+            // A read of a peer's shared memory takes up to half a microsecond when all blocks of
+            // the cluster read at once, so the reads of several of this block's token columns (32
+            // reads a thread) are asked for before any is used, and only then added up, in the order
+            // of the splits as ever (a loop that adds each value as it comes waits for every
+            // read in turn).
             auto finish = [&](auto splits) {
                 constexpr int SS = decltype(splits)::value;
+                constexpr int CB = EPI == EPI_SWIGLU ? 16 / SS : 32 / SS;   // columns a batch: 32 reads in flight a thread (64 cost the registers that let two blocks share an SM)
                 const float* peer[SS];
 #pragma unroll
                 for (int z = 0; z < SS; z++) peer[z] = cl.map_shared_rank(base, z);
                 const int last = min(BN, p.T - t0);
-                for (int c = rank; c < last; c += 2 * SS) {
-                    const int c2 = c + SS;
-                    const bool two = c2 < last;
-                    float v1[SS], u1[SS], v2[SS], u2[SS];
+                for (int c = rank; c < last; c += CB * SS) {
+                    float v[CB][SS], u[CB][SS];
 #pragma unroll
-                    for (int z = 0; z < SS; z++) {
-                        v1[z] = peer[z][(size_t)c * TC_BM];
-                        v2[z] = two ? peer[z][(size_t)c2 * TC_BM] : 0.0f;
-                        if (EPI == EPI_SWIGLU) {
-                            u1[z] = peer[z][(size_t)(BN + c) * TC_BM];
-                            u2[z] = two ? peer[z][(size_t)(BN + c2) * TC_BM] : 0.0f;
+                    for (int b = 0; b < CB; b++) {
+                        const int cb = c + b * SS;
+#pragma unroll
+                        for (int z = 0; z < SS; z++) {
+                            v[b][z] = cb < last ? peer[z][(size_t)cb * TC_BM] : 0.0f;
+                            if (EPI == EPI_SWIGLU) u[b][z] = cb < last ? peer[z][(size_t)(BN + cb) * TC_BM] : 0.0f;
                         }
                     }
-                    float a = 0.0f, b = 0.0f, ua = 0.0f, ub = 0.0f;
 #pragma unroll
-                    for (int z = 0; z < SS; z++) {
-                        a += v1[z];
-                        b += v2[z];
-                        if (EPI == EPI_SWIGLU) ua += u1[z], ub += u2[z];
+                    for (int b = 0; b < CB; b++) {
+                        const int cb = c + b * SS;
+                        if (cb >= last) break;
+                        float a = 0.0f, ua = 0.0f;
+#pragma unroll
+                        for (int z = 0; z < SS; z++) {
+                            a += v[b][z];
+                            if (EPI == EPI_SWIGLU) ua += u[b][z];
+                        }
+                        write(cb, a, ua);
                     }
-                    write(c, a, ua);
-                    if (two) write(c2, b, ub);
                 }
             };
             if (S == 8) finish(std::integral_constant<int, 8>());
@@ -564,19 +573,23 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             const int out_n = tile_n * 2 * OUT_ROWS + (int)rank * OUT_ROWS + 32 * q + lane + (EPI == EPI_SWIGLU ? 0 : TC_BM * set);
             const uint32_t lanes = tmem + ((uint32_t)(32 * q) << 16);
             // 16 token columns at a time, the next piece on its way while this one is written.
+            // All sixteen results first, then the stores: see the one-block kernel's epilogue.
             auto emit = [&](const uint32_t* v, const uint32_t* u, int c0) {
+                if (out_n >= p.N) return;
+                float r[16];
+#pragma unroll
+                for (int j = 0; j < 16; j++) r[j] = EPI == EPI_SWIGLU ? silu_mul(__uint_as_float(v[j]), __uint_as_float(u[j])) : __uint_as_float(v[j]);
+                const int t_first = t0 + c0;
+                const size_t o = (size_t)t_first * p.N + out_n;
 #pragma unroll
                 for (int j = 0; j < 16; j++) {
-                    const int t = t0 + c0 + j;
-                    if (t >= p.T || out_n >= p.N) continue;
-                    const size_t o = (size_t)t * p.N + out_n;
-                    const float val = __uint_as_float(v[j]);
-                    if (EPI == EPI_SWIGLU) ((bf16*)p.out)[o] = __float2bfloat16_rn(silu_mul(val, __uint_as_float(u[j])));
-                    if (EPI == EPI_STORE) ((bf16*)p.out)[o] = __float2bfloat16_rn(val);
-                    if (EPI == EPI_STORE_F32) ((float*)p.out)[o] = val;
+                    if (t_first + j >= p.T) break;
+                    const size_t at = o + (size_t)j * p.N;
+                    if (EPI == EPI_STORE || EPI == EPI_SWIGLU) ((bf16*)p.out)[at] = __float2bfloat16_rn(r[j]);
+                    if (EPI == EPI_STORE_F32) ((float*)p.out)[at] = r[j];
                     // One thread owns each element, so a fire-and-forget reduction gives the same
                     // sum as a load, add and store, without waiting for the load.
-                    if (EPI == EPI_ADD_F32) atomicAdd(&((float*)p.out)[o], val);
+                    if (EPI == EPI_ADD_F32) atomicAdd(&((float*)p.out)[at], r[j]);
                 }
             };
             const int COLS = EPI == EPI_SWIGLU ? bn / 2 : bn;              // token columns this warp writes (a multiple of 32)
