@@ -24,6 +24,7 @@ namespace cg = cooperative_groups;
 #define SMP_THREADS 512
 #define SMP_WARPS (SMP_THREADS / 32)
 #define SMP_CLUSTER 8      // blocks that share a row (the portable cluster size)
+#define SMP_KEEP 36        // weights a thread keeps in registers: rows of up to 8 x 512 x 36 = 147,456 scores are read once
 
 // splitmix64's finaliser; the top 24 bits over 2^24 (sample.rs:64-71).
 __device__ __forceinline__ float uniform_from(uint64_t seed) {
@@ -77,17 +78,31 @@ struct RowView {
 // its own in shared memory, a warp a bucket adds the threads' sums in a fixed order, and
 // the blocks' sums are added in rank order, so every block takes the same decision and
 // the result is the same bits on every run.
-__device__ Walk walk_down(cg::cluster_group& cl, SampleShared& sh, float* hist, const RowView& rv, float target, int& turn) {
+// `kept` holds this thread's weights (elements lo + thread + 512 k, k < n_kept) when the row is
+// short enough for that (`cached`): the sixteen passes of the two walks then read registers
+// instead of fetching the scores and taking their exponentials again.
+__device__ __forceinline__ Walk walk_down(cg::cluster_group& cl, SampleShared& sh, float* hist, const RowView& rv, float target, int& turn,
+                                          const float (&kept)[SMP_KEEP], int n_kept, bool cached) {
     unsigned prefix = 0, mask = 0;
     float above = 0.0f;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     for (int shift = 28; shift >= 0; shift -= 4) {
 #pragma unroll
         for (int j = 0; j < 16; j++) hist[j * SMP_THREADS + threadIdx.x] = 0.0f;
-        for (int i = rv.lo + threadIdx.x; i < rv.hi; i += SMP_THREADS) {
-            const float w = rv.weight(i);
-            const unsigned key = __float_as_uint(w);
-            if ((key & mask) == prefix) hist[((key >> shift) & 15u) * SMP_THREADS + threadIdx.x] += w;
+        if (cached) {
+#pragma unroll
+            for (int k = 0; k < SMP_KEEP; k++)
+                if (k < n_kept) {
+                    const float w = kept[k];
+                    const unsigned key = __float_as_uint(w);
+                    if ((key & mask) == prefix) hist[((key >> shift) & 15u) * SMP_THREADS + threadIdx.x] += w;
+                }
+        } else {
+            for (int i = rv.lo + threadIdx.x; i < rv.hi; i += SMP_THREADS) {
+                const float w = rv.weight(i);
+                const unsigned key = __float_as_uint(w);
+                if ((key & mask) == prefix) hist[((key >> shift) & 15u) * SMP_THREADS + threadIdx.x] += w;
+            }
         }
         __syncthreads();
         {   // warp j adds bucket j over the threads
@@ -214,8 +229,20 @@ __global__ void __launch_bounds__(SMP_THREADS) sample_kernel(const float* __rest
     rv.max_score = argmax_key_value(best);
     rv.inv_t = 1.0f / temp;
 
+    // This thread's weights, kept for the walks below if there are few enough of them.
+    float held[SMP_KEEP];
+    const bool cached = chunk <= SMP_KEEP * SMP_THREADS;
+    const int n_kept = cached ? max(0, (rv.hi - rv.lo - (int)threadIdx.x + SMP_THREADS - 1) / SMP_THREADS) : 0;
     float mine = 0.0f;
-    for (int i = rv.lo + threadIdx.x; i < rv.hi; i += SMP_THREADS) mine += rv.weight(i);
+    if (cached) {
+#pragma unroll
+        for (int k = 0; k < SMP_KEEP; k++) {
+            held[k] = k < n_kept ? rv.weight(rv.lo + (int)threadIdx.x + k * SMP_THREADS) : 0.0f;
+            if (k < n_kept) mine += held[k];
+        }
+    } else {
+        for (int i = rv.lo + threadIdx.x; i < rv.hi; i += SMP_THREADS) mine += rv.weight(i);
+    }
     mine = block_sum(mine, red);
     if (threadIdx.x == 0) sh.sum = mine;
     cl.sync();
@@ -226,17 +253,24 @@ __global__ void __launch_bounds__(SMP_THREADS) sample_kernel(const float* __rest
     // exactly that weight the first `n_cut` by id.
     int turn = 0;
     const float want = top_p[r] * total;
-    const Walk cut = walk_down(cl, sh, hist, rv, want, turn);
-    const float w_cut = __uint_as_float(cut.key);
+    // With top_p of one or more every token is kept: no cut to look for (eight passes less).
+    const bool all_kept = top_p[r] >= 1.0f;
     int before, inside, t_lo, t_hi;
-    const int ties_cut = count_with_key(cl, sh, rv, cut.key, 0, before, inside, t_lo, t_hi);
-    int n_cut = w_cut > 0.0f ? (int)ceilf((want - cut.above) / w_cut) : ties_cut;
-    n_cut = max(1, min(n_cut, ties_cut));
-    const float kept = cut.above + (float)n_cut * w_cut;
+    Walk cut = {0u, total};
+    int n_cut = 0x7fffffff;
+    float kept = total;
+    if (!all_kept) {
+        cut = walk_down(cl, sh, hist, rv, want, turn, held, n_kept, cached);
+        const float w_cut = __uint_as_float(cut.key);
+        const int ties_cut = count_with_key(cl, sh, rv, cut.key, 0, before, inside, t_lo, t_hi);
+        n_cut = w_cut > 0.0f ? (int)ceilf((want - cut.above) / w_cut) : ties_cut;
+        n_cut = max(1, min(n_cut, ties_cut));
+        kept = cut.above + (float)n_cut * w_cut;
+    }
 
     const uint64_t st = (uint64_t)(long long)step[r];
     const float rr = uniform_from(seed[r] ^ (st * 0x9e3779b97f4a7c15ull)) * kept;
-    const Walk hit = walk_down(cl, sh, hist, rv, rr, turn);
+    const Walk hit = walk_down(cl, sh, hist, rv, rr, turn, held, n_kept, cached);
     const float w_hit = __uint_as_float(hit.key);
     int n_hit = w_hit > 0.0f ? (int)ceilf((rr - hit.above) / w_hit) : 1;
     n_hit = max(1, n_hit);
@@ -299,6 +333,11 @@ __global__ void argmax_finish_kernel(unsigned long long* __restrict__ best, int*
 #define ARGMAX_MAX_ROWS 4096
 __device__ unsigned long long g_argmax_best[ARGMAX_MAX_ROWS];   // zero between launches
 
+// Blocks that share a row: 0 lets the launcher choose, 1, 2, 4 or 8 force it (measurements and
+// tests; every choice gives the same picks).
+static int g_smp_share = 0;
+extern "C" void bc_sample_set_blocks_per_row(int n) { g_smp_share = (n == 1 || n == 2 || n == 4 || n == 8) ? n : 0; }
+
 // scores [rows, V] float; temperature, top_p, seed (64-bit), step (the position of the row
 // sampled) one a row; out [rows] token ids.
 extern "C" int bc_sample(const float* scores, int rows, int V, const float* temperature, const float* top_p,
@@ -307,14 +346,22 @@ extern "C" int bc_sample(const float* scores, int rows, int V, const float* temp
     if (rows == 0) return BC_OK;
     BC_CHECK_ARG(rows <= 65535, "sample: %d rows are more than 65535", rows);
     const size_t smem = 16 * SMP_THREADS * sizeof(float);
+    // Blocks a row: eight (a cluster) while all rows' blocks still run at once, one to an SM;
+    // with more rows fewer blocks share a row, so that the rows still run side by side instead
+    // of in turns (64 rows: 344 us with eight blocks a row, in four turns).
+    int share = g_smp_share > 0 ? g_smp_share : SMP_CLUSTER;
+    if (g_smp_share == 0) {
+        const int sms = bc_sm_count();
+        while (share > 1 && rows * share > sms) share /= 2;
+    }
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(SMP_CLUSTER, rows);
+    cfg.gridDim = dim3(share, rows);
     cfg.blockDim = dim3(SMP_THREADS);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = s;
     cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = SMP_CLUSTER;
+    attr[0].val.clusterDim.x = share;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
     attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;

@@ -683,6 +683,12 @@ def argmax(scores: torch.Tensor, out: torch.Tensor) -> None:
     _call(_fn("bc_argmax"), _ptr(scores), _c_int(rows), _c_int(V), _ptr(out), _stream())
 
 
+def set_sample_blocks_per_row(n: int) -> None:
+    """Blocks that share a row of the sampler: 0 lets the launcher choose (eight while all
+    rows still run at once, fewer for more rows), 1, 2, 4 or 8 force it.  For measurements and tests."""
+    lib().bc_sample_set_blocks_per_row(_c_int(int(n)))
+
+
 def sample(scores: torch.Tensor, temperature: torch.Tensor, top_p: torch.Tensor, seed: torch.Tensor, step: torch.Tensor,
            out: torch.Tensor) -> None:
     """One draw a row: greedy where temperature <= 0, else temperature / nucleus sampling

@@ -638,3 +638,31 @@ def test_sampler_rows_are_independent():
     scores = (rng(11).standard_normal((8, 777)) * 2).astype(np.float32)
     alone = [run_sampler(scores[i:i + 1], 0.9, 0.9, 42, [50 + i])[0] for i in range(8)]
     assert run_sampler(scores, 0.9, 0.9, 42, range(50, 58)) == alone
+
+
+def test_sampler_on_a_row_too_long_to_keep_in_registers():
+    """Past 147,456 scores a thread no longer keeps its weights between the passes and takes
+    them from the scores again: the same picks as the plain sampler."""
+    V = 150_001
+    scores = (rng(V).standard_normal((6, V)) * 3.0).astype(np.float32)
+    seed = 12345
+    got = run_sampler(scores, 0.9, 0.8, seed, range(40, 46))
+    same = sum(got[r] == plain_llama.sample(scores[r], 0.9, 0.8, seed, 40 + r) for r in range(6))
+    for r in range(6):
+        order, w = plain_llama.nucleus(scores[r], 0.9, 0.8)
+        assert got[r] in order
+    assert same >= 5
+
+
+def test_sampler_picks_do_not_depend_on_how_many_blocks_share_a_row():
+    from borrowed_compute_b200 import ops
+
+    scores = (rng(21).standard_normal((5, 9001)) * 2.5).astype(np.float32)
+    picks = []
+    try:
+        for share in (8, 4, 2, 1, 0):
+            ops.set_sample_blocks_per_row(share)
+            picks.append(run_sampler(scores, 0.7, 0.9, 99, range(5)))
+    finally:
+        ops.set_sample_blocks_per_row(0)
+    assert all(p == picks[0] for p in picks)
