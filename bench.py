@@ -11,7 +11,8 @@ decode step's mandatory bytes (every weight once, the live requests' cache once)
 measured copy bandwidth.  ``points`` adds decoding at batch 1 and 64 (device-timed and end to
 end) and two more workloads of other shapes: the Llama-2-13B shape (one kv head a head) with
 16 prompts of unequal lengths, and the Llama-3.2-3B shape (tied head) at batch 64 sampled at
-temperature 1.0 through the entry point.  ``classes`` times every kernel class of one decode
+temperature 1.0 through the entry point, and the two tiny workloads on the device and on the
+library's plain C++ twin on the host (the CPU baseline).  ``classes`` times every kernel class of one decode
 step and one prompt step launch by launch and sets each against its own bytes or operations.
 ``checked`` says that the tokens of the end-to-end run equal those of the same prompts
 stepped without captured graphs; the line is not printed otherwise.  Every decode step
@@ -59,6 +60,19 @@ CONFIG_3B = {
     "architectures": ["LlamaForCausalLM"], "num_hidden_layers": 28, "hidden_size": 3072, "num_attention_heads": 24,
     "num_key_value_heads": 8, "head_dim": 128, "intermediate_size": 8192, "vocab_size": 128256, "rope_theta": 500000.0,
     "rope_scaling": _llama3_scaling(32.0), "rms_norm_eps": 1e-5, "tie_word_embeddings": True, "max_position_embeddings": 16384,
+}
+# The two tiny configurations, which differ in every size and option; their workloads are timed
+# against the library's plain C++ twin on the host.
+CONFIG_TINY_A = {
+    "architectures": ["LlamaForCausalLM"], "num_hidden_layers": 2, "hidden_size": 64, "num_attention_heads": 4, "num_key_value_heads": 2,
+    "intermediate_size": 176, "vocab_size": 256, "rope_theta": 10000.0, "rms_norm_eps": 1e-5, "tie_word_embeddings": False,
+    "max_position_embeddings": 128,
+}
+CONFIG_TINY_B = {
+    "architectures": ["LlamaForCausalLM"], "num_hidden_layers": 3, "hidden_size": 96, "num_attention_heads": 4, "num_key_value_heads": 1,
+    "head_dim": 32, "intermediate_size": 256, "vocab_size": 320, "rope_theta": 500000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 4.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0, "original_max_position_embeddings": 64},
+    "rms_norm_eps": 1e-6, "tie_word_embeddings": True, "max_position_embeddings": 256,
 }
 CONTEXT = 8192
 PROMPT = 2048
@@ -311,6 +325,39 @@ def breakdown(eng, cfg, layers, batch, pk, rng):
     return out
 
 
+def bench_tiny(rng) -> dict:
+    """The two tiny workloads (float32): a batch of 3 prompts of 5 / 17 / 1 tokens and 8 greedy
+    steps; a batch of 4 prompts of 1 / 9 / 33 / 70 tokens and 16 steps at temperature 0.8,
+    top_p 0.9.  Through the entry point on the device, and through the plain C++ twin on the
+    host (which recomputes the whole sequence every step): the twin's time is the CPU baseline,
+    and its tokens must be the engine's."""
+    import torch
+
+    from borrowed_compute_b200 import Local, Sampling, twin
+    from borrowed_compute_b200.weights import random_tensors
+
+    out = {}
+    for name, cfg, lengths, new, sampling in (("tiny_a", CONFIG_TINY_A, (5, 17, 1), 8, Sampling()),
+                                              ("tiny_b", CONFIG_TINY_B, (1, 9, 33, 70), 16, Sampling(temperature=0.8, top_p=0.9, seed=1234567))):
+        model = Local.random(cfg, seed=1, dtype="float32", max_tokens=1024, max_slots=4, max_seq=cfg["max_position_embeddings"])
+        weights = {k: v.float().cpu().numpy() for k, v in random_tensors(model.engine.model.expected_tensors(), 1, torch.float32, "cuda").items()}
+        host = twin.TwinLlama(cfg, weights)
+        prompts = [[int(t) for t in rng.integers(0, cfg["vocab_size"], n)] for n in lengths]
+        model.generate(prompts, new, sampling, stop_ids=())                      # first-use set-up outside the timed call
+        started = time.perf_counter()
+        got, _ = model.generate(prompts, new, sampling, stop_ids=())
+        engine_ms = 1000.0 * (time.perf_counter() - started)
+        started = time.perf_counter()
+        want = [host.generate(p, new, sampling.temperature, sampling.top_p, sampling.seed) for p in prompts]
+        twin_ms = 1000.0 * (time.perf_counter() - started)
+        if got != want:
+            raise AssertionError(f"bench: {name}: the engine generated {got}, the plain C++ twin {want}")
+        out[f"{name}_engine_ms"], out[f"{name}_cpu_twin_ms"] = round(engine_ms, 2), round(twin_ms, 2)
+        del model
+    free_device_memory()
+    return out
+
+
 def bench_13b(pk, rng) -> dict:
     """The Llama-2-13B shape: 16 prompts of unequal lengths (uniform in 64 .. 2,048, seeded)
     in ONE ragged prompt step, then 128 decode steps, device-timed."""
@@ -479,6 +526,7 @@ def run_ours(args) -> dict:
     if not args.no_points and not args.layers:
         points.update(bench_13b(pk, rng))
         points.update(bench_3b(pk, rng))
+        points.update(bench_tiny(rng))
 
     config = {"model": "llama-3.1-8b-shape", "layers": layers, "layers_full": full_layers, "hidden": cfg["hidden_size"],
               "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],

@@ -157,3 +157,23 @@ def test_command_line_options_and_generation_config(locals_, tmp_path):
     res = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "bc-infer"), "generate", mine, "5,17,3", "--max-tokens", "6", "--max-seq", "5"],
                          capture_output=True, text=True, timeout=300)
     assert res.returncode != 0 and "--max-seq" in res.stderr
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_the_engine_and_the_plain_cxx_twin_generate_the_same(locals_, name):
+    """The third restatement of the formulas, in plain C++ on the host, against the engine in
+    float32: the same tokens, greedy and sampled."""
+    from borrowed_compute_b200 import Sampling, twin
+
+    model, cfg, weights, _ = locals_(name, "float32")
+    host = twin.TwinLlama(cfg, weights)
+    prompts = [seeded_tokens(80 + i, n, cfg["vocab_size"]) for i, n in enumerate([7, 1, 40])]
+    got, _ = model.generate(prompts, 10, Sampling(), stop_ids=())
+    assert got == [host.generate(p, 10) for p in prompts]
+    s = Sampling(temperature=0.9, top_p=0.85, seed=42)
+    got, _ = model.generate(prompts, 10, s, stop_ids=())
+    assert got == [host.generate(p, 10, 0.9, 0.85, 42) for p in prompts]
+    scores = model.scores(prompts[2], 0).numpy()
+    model.reset()
+    ref = host.logits(prompts[2])
+    assert np.abs(scores - ref).max() <= tolerance("float32", ref)
