@@ -117,23 +117,25 @@ def rope(x: np.ndarray, positions, inv_freq: np.ndarray, pairing: str) -> np.nda
     return out
 
 
-def attention(q: np.ndarray, k: np.ndarray, v: np.ndarray) -> np.ndarray:
+def attention(q: np.ndarray, k: np.ndarray, v: np.ndarray, only=None) -> np.ndarray:
     """Causal grouped-query attention over one whole sequence (model.rs:448-481).
 
     ``q[row, head, d]``, ``k, v[row, kv_head, d]``.  Row ``i`` sees rows ``0..i``; head
     ``h`` reads kv head ``h // (heads / kv_heads)`` (463); scores are scaled by
     ``1/sqrt(d)`` (451), the maximum is subtracted before the exponential (466-470).
+    ``only``: the rows whose result is wanted; then ``q`` holds these rows alone, in this
+    order, and so does the result (a long sequence of which the test reads the end).
     """
-    rows, heads, d = q.shape
+    heads, d = q.shape[1], q.shape[2]
     group = heads // k.shape[1]
     scale = 1.0 / math.sqrt(d)
     out = np.zeros_like(q)
-    for i in range(rows):
+    for at, i in enumerate(range(q.shape[0]) if only is None else only):
         for h in range(heads):
             g = h // group
-            s = (k[: i + 1, g, :] @ q[i, h, :]) * scale
+            s = (k[: i + 1, g, :] @ q[at, h, :]) * scale
             p = np.exp(s - s.max())
-            out[i, h, :] = (p / p.sum()) @ v[: i + 1, g, :]
+            out[at, h, :] = (p / p.sum()) @ v[: i + 1, g, :]
     return out
 
 
@@ -145,17 +147,21 @@ def swiglu(x: np.ndarray, gate: np.ndarray, up: np.ndarray, down: np.ndarray) ->
     return (g / (1.0 + np.exp(-g)) * u) @ down.T
 
 
-def layer(x, w, prefix, c, positions, inv_freq):
+def layer(x, w, prefix, c, positions, inv_freq, only=None):
     """One pre-norm block (model.rs:323-345): attention and feed-forward, each added to
-    the stream it read through a norm."""
+    the stream it read through a norm.  ``only``: rows whose result is wanted (every row
+    still gives its key and value); the result then holds these rows alone."""
     rows = x.shape[0]
     n = rms_norm(x, w[prefix + "input_layernorm.weight"], c["eps"])
-    q = (n @ w[prefix + "self_attn.q_proj.weight"].T).reshape(rows, c["heads"], c["head_dim"])
     k = (n @ w[prefix + "self_attn.k_proj.weight"].T).reshape(rows, c["kv_heads"], c["head_dim"])
     v = (n @ w[prefix + "self_attn.v_proj.weight"].T).reshape(rows, c["kv_heads"], c["head_dim"])
-    q = rope(q, positions, inv_freq, c["pairing"])
     k = rope(k, positions, inv_freq, c["pairing"])
-    att = attention(q, k, v).reshape(rows, c["heads"] * c["head_dim"])
+    if only is not None:
+        x, n, rows = x[list(only)], n[list(only)], len(only)
+        positions = [positions[i] for i in only]
+    q = (n @ w[prefix + "self_attn.q_proj.weight"].T).reshape(rows, c["heads"], c["head_dim"])
+    q = rope(q, positions, inv_freq, c["pairing"])
+    att = attention(q, k, v, only).reshape(rows, c["heads"] * c["head_dim"])
     x = x + att @ w[prefix + "self_attn.o_proj.weight"].T
     n = rms_norm(x, w[prefix + "post_attention_layernorm.weight"], c["eps"])
     return x + swiglu(
@@ -174,16 +180,18 @@ def head(x, w, c):
     return n @ out.T
 
 
-def logits(cfg: dict, weights: dict, tokens, dtype=np.float64) -> np.ndarray:
+def logits(cfg: dict, weights: dict, tokens, dtype=np.float64, only=None) -> np.ndarray:
     """Scores after every token of one sequence fed from position 0: ``[len, vocab]``
-    (the sequence of crates/bc-infer/src/lib.rs:50-54: embed, layers, head)."""
+    (the sequence of crates/bc-infer/src/lib.rs:50-54: embed, layers, head).  ``only``:
+    the positions whose scores are wanted; the last layer and the head then run for these
+    alone (every layer before it runs whole, since later rows read its keys and values)."""
     c = read_config(cfg)
     w = {k: np.asarray(v).astype(dtype) for k, v in weights.items()}
     positions = list(range(len(tokens)))
     inv_freq = rope_inv_freq(c["head_dim"], c["theta"], c["scaling"])
     x = embed(w["model.embed_tokens.weight"], tokens).astype(dtype)
     for l in range(c["layers"]):
-        x = layer(x, w, f"model.layers.{l}.", c, positions, inv_freq)
+        x = layer(x, w, f"model.layers.{l}.", c, positions, inv_freq, only if l == c["layers"] - 1 else None)
     return head(x, w, c)
 
 

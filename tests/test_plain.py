@@ -104,3 +104,14 @@ def test_generate_stops_without_emitting():
     assert len(free) == 6
     stopped = plain_llama.generate(cfg, w, [1, 2, 3], 6, stops=(free[2],))
     assert stopped == free[:free.index(free[2])]
+
+
+def test_wanted_rows_alone_give_the_rows_of_the_whole():
+    from conftest import TINY_B, make_weights
+
+    w = make_weights(TINY_B, 4)
+    tokens = [int(t) for t in np.random.default_rng(0).integers(0, TINY_B["vocab_size"], 23)]
+    whole = plain_llama.logits(TINY_B, w, tokens)
+    some = plain_llama.logits(TINY_B, w, tokens, only=[22, 3, 17])
+    assert some.shape == (3, TINY_B["vocab_size"])
+    assert np.allclose(some, whole[[22, 3, 17]], rtol=0, atol=1e-11)   # the library's products round by their shapes
