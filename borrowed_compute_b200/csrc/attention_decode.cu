@@ -365,29 +365,36 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
         }
     }
     if (n_splits == 1) return;
+    // With a cluster, up to eight neighbouring splits merge among themselves first; what is
+    // left to merge through scratch memory are the clusters' results (`parts` of them).
+    const int csize = use_cluster ? use_cluster : 1;   // the launcher's cluster size: the splits themselves, or 8, 4 or 2 dividing them
+    const int parts = n_splits / csize, part = split / csize;
     if (use_cluster) {
-        // The splits of this (row, kv head) are one thread-block cluster: each block reads its
-        // peers' results out of their shared memory and finishes a share of the outputs, adding
-        // the splits in order.  No scratch memory, no counters, no round trip through the L2.
+        // The splits of this (row, kv head), or eight neighbours among them, are one thread-block
+        // cluster: each block reads its peers' results out of their shared memory and finishes a
+        // share of the outputs, adding the splits in order.  No scratch memory, no counters, no
+        // round trip through the L2 (unless there are more splits than a cluster holds: then
+        // the cluster's sum goes to scratch memory as one part).
         cg::cluster_group cl = cg::this_cluster();
         cl.sync();
-        const int total = group * D, share = (total + n_splits - 1) / n_splits;
+        const int crank = split - part * csize;
+        const int total = group * D, share = (total + csize - 1) / csize;
         // All reads of the peers' shared memory (a good tenth of a microsecond each) are asked
         // for before any is used; the splits are added in their order as ever.
         const float *ppm[8], *ppl[8], *ppo[8];
 #pragma unroll
         for (int sp = 0; sp < 8; sp++) {
-            const int from = sp < n_splits ? sp : 0;
+            const int from = sp < csize ? sp : 0;
             ppm[sp] = cl.map_shared_rank(pm, from);
             ppl[sp] = cl.map_shared_rank(pl, from);
             ppo[sp] = cl.map_shared_rank(po, from);
         }
-        for (int i = split * share + threadIdx.x; i < min(total, (split + 1) * share); i += AD_THREADS) {
+        for (int i = crank * share + threadIdx.x; i < min(total, (crank + 1) * share); i += AD_THREADS) {
             const int hr = i / D, d = i - hr * D;
             float ms[8], ls[8], os[8];
 #pragma unroll
             for (int sp = 0; sp < 8; sp++) {
-                const bool has = sp < n_splits;
+                const bool has = sp < csize;
                 ms[sp] = has ? ppm[sp][hr] : -INFINITY;
                 ls[sp] = has ? ppl[sp][hr] : 0.0f;
                 os[sp] = has ? ppo[sp][i] : 0.0f;
@@ -402,13 +409,23 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
                 L += ls[sp] * f;
                 O += os[sp] * f;
             }
-            out[((size_t)r * H + g * group + hr) * D + d] = __float2bfloat16_rn(L > 0.0f ? O / L : 0.0f);
+            if (parts == 1) {
+                out[((size_t)r * H + g * group + hr) * D + d] = __float2bfloat16_rn(L > 0.0f ? O / L : 0.0f);
+            } else {
+                float* dst = scratch + (((size_t)r * H + g * group + hr) * parts + part) * stride;
+                __stcg(dst + d, O);
+                if (d == 0) {
+                    __stcg(dst + D, M);
+                    __stcg(dst + D + 1, L);
+                }
+            }
         }
         cl.sync();   // no block may leave while a peer still reads its shared memory
-        return;
+        if (parts == 1) return;
     }
 
-    // The last block of this (row, kv head) to arrive merges the splits in order.
+    // The last block of this (row, kv head) to arrive merges the parts in order (every block
+    // arrives, also those of a cluster that wrote a share of its part each).
     __threadfence();
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -422,11 +439,11 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
     for (int i = threadIdx.x; i < group * D; i += AD_THREADS) {
         const int hr = i / D, d = i - hr * D;
         const int h = g * group + hr;
-        const float* src = scratch + ((size_t)r * H + h) * n_splits * stride;
+        const float* src = scratch + ((size_t)r * H + h) * parts * stride;
         float M = -INFINITY;
-        for (int sp = 0; sp < n_splits; sp++) M = fmaxf(M, __ldcg(src + (size_t)sp * stride + D));
+        for (int sp = 0; sp < parts; sp++) M = fmaxf(M, __ldcg(src + (size_t)sp * stride + D));
         float L = 0.0f, O = 0.0f;
-        for (int sp = 0; sp < n_splits; sp++) {
+        for (int sp = 0; sp < parts; sp++) {
             const float ms = __ldcg(src + (size_t)sp * stride + D);
             const float f = ms == -INFINITY ? 0.0f : exp2f(ms - M);
             L += __ldcg(src + (size_t)sp * stride + D + 1) * f;
@@ -468,12 +485,15 @@ static int launch_as(const CUtensorMap& mk, const CUtensorMap& mv, const void* q
     dim3 grid(n_splits, G, rows);
     // Up to eight splits (the portable cluster size) exchange their results through
     // distributed shared memory; more go through the caller's scratch memory.
-    const bool clustered = n_splits > 1 && n_splits <= 8 && fr.allow_cluster;
+    // More than eight: clusters of eight, four or two where that divides them, whose sums then go through scratch.
+    int csize = n_splits <= 8 ? n_splits : n_splits % 8 == 0 ? 8 : n_splits % 4 == 0 ? 4 : n_splits % 2 == 0 ? 2 : 1;
+    if (n_splits > 8 && !(scratch && counters)) csize = 1;
+    const bool clustered = n_splits > 1 && fr.allow_cluster && csize > 1;
     if (clustered)
-        bc_launch_clustered(attention_decode_kernel<D, TMA>, grid, dim3(AD_THREADS), (size_t)SMEM, s, dim3(n_splits, 1, 1), mk, mv, (const bf16*)q,
+        bc_launch_clustered(attention_decode_kernel<D, TMA>, grid, dim3(AD_THREADS), (size_t)SMEM, s, dim3(csize, 1, 1), mk, mv, (const bf16*)q,
                             q_stride, (const bf16*)k_cache, (const bf16*)v_cache, page_table, row_pos, row_slot, (bf16*)out, scratch, counters, H, G,
                             max_pages, n_pages, window, scale * 1.4426950408889634f, (const float2*)fr.cos_sin, fr.pairing, fr.fuse,
-                            fr.k_off, fr.v_off, (bf16*)k_cache, (bf16*)v_cache, 1);
+                            fr.k_off, fr.v_off, (bf16*)k_cache, (bf16*)v_cache, csize);
     else
         bc_launch(attention_decode_kernel<D, TMA>, grid, dim3(AD_THREADS), (size_t)SMEM, s, mk, mv, (const bf16*)q, q_stride, (const bf16*)k_cache,
                   (const bf16*)v_cache, page_table, row_pos, row_slot, (bf16*)out, scratch, counters, H, G, max_pages, n_pages, window,

@@ -15,7 +15,7 @@ from __future__ import annotations
 import gc
 import weakref
 
-from typing import Any, Dict, List, Mapping, Optional, Sequence
+from typing import Any, Dict, List, Mapping, Optional, Sequence, Tuple
 
 import numpy as np
 import torch
@@ -44,10 +44,12 @@ DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.f
 
 
 class _DecodeGraph:
-    """One captured decode step for a fixed number of rows."""
+    """One captured decode step for a fixed number of rows, none of which reaches past
+    ``reach`` positions (parts may plan by that bound: the decode attention cuts long
+    sequences into more pieces)."""
 
-    def __init__(self, engine: "Engine", rows: int):
-        self._engine, self.rows = weakref.ref(engine), rows   # no cycle: a dropped engine and its graphs go at once
+    def __init__(self, engine: "Engine", rows: int, reach: int):
+        self._engine, self.rows, self.reach = weakref.ref(engine), rows, reach   # no cycle: a dropped engine and its graphs go at once
         dev = engine.rt.device
         # tokens, row_pos, row_slot, seq_rows (+1), seq_slot, seq_start, want_rows
         self.sizes = [("tokens", rows), ("row_pos", rows), ("row_slot", rows), ("seq_rows", rows + 1), ("seq_slot", rows),
@@ -109,7 +111,7 @@ class _DecodeGraph:
     def _forward(self) -> torch.Tensor:
         v, rows = self.views, self.rows
         ctx = StepContext(rows=rows, seqs=rows, tokens=v["tokens"], row_pos=v["row_pos"], row_slot=v["row_slot"], seq_rows=v["seq_rows"],
-                          seq_slot=v["seq_slot"], seq_start=v["seq_start"], max_new=1, max_total=self.engine.max_seq, decode=True,
+                          seq_slot=v["seq_slot"], seq_start=v["seq_start"], max_new=1, max_total=self.reach, decode=True,
                           extras={"graph": True})
         return self.engine.model.forward(ctx, self.engine.cache, v["want_rows"], rows)
 
@@ -161,7 +163,7 @@ class Engine:
         self._ints: Optional[torch.Tensor] = None
         self._host_ints: Optional[torch.Tensor] = None
         self._staged: Optional[torch.cuda.Event] = None
-        self._graphs: Dict[int, "_DecodeGraph"] = {}
+        self._graphs: Dict[Tuple[int, int], "_DecodeGraph"] = {}
         self._ahead: Optional[_Ahead] = None
         self.last_graph: Optional[_DecodeGraph] = None   # the captured step the last call of step() replayed, if it did
         # Decode steps replay a captured CUDA graph unless a part plans on the host.
@@ -339,11 +341,20 @@ class Engine:
             b *= 2
         return b if n <= 16 else -(-n // 16) * 16
 
-    def _graph_for(self, n: int) -> _DecodeGraph:
-        bucket = self._bucket(n)
-        g = self._graphs.get(bucket)
+    def _reach(self, total: int) -> int:
+        """The bound on positions that a captured step is made for: ``total`` rounded up to a
+        power of two from 4,096 on, at most what a sequence can hold."""
+        reach = 4096
+        while reach < total:
+            reach *= 2
+        return min(reach, self.max_seq)
+
+    def _graph_for(self, n: int, total: int) -> _DecodeGraph:
+        """The captured step for ``n`` sequences of which the longest reaches ``total`` positions."""
+        key = (self._bucket(n), self._reach(total))
+        g = self._graphs.get(key)
         if g is None:
-            g = self._graphs[bucket] = _DecodeGraph(self, bucket)
+            g = self._graphs[key] = _DecodeGraph(self, *key)
         return g
 
     def can_step_again(self, slots: Sequence[int]) -> bool:
@@ -389,7 +400,7 @@ class Engine:
         else:
             starts = self.check_entries(entries)
             self.cache.slots.reserve_many([(slot, start + 1, 1) for slot, start in zip(slots, starts)])
-            g = self._graph_for(n)
+            g = self._graph_for(n, max(starts) + 1)
             packed = g.pack(tokens, starts, slots, n)
         count_traffic("h2d", self.cache.sync_tables(), True)
         scores = g.run(packed, keep_tokens=tokens_on_device)[:n]
@@ -405,7 +416,8 @@ class Engine:
             if max(nxt) + 1 <= self.max_seq:
                 self.cache.slots.reserve_many([(slot, start + 1, 1) for slot, start in zip(slots, nxt)])
                 count_traffic("h2d", self.cache.sync_tables(), True)
-                self._ahead = _Ahead(slots, nxt, g, g.pack(None, nxt, slots, n))
+                after = self._graph_for(n, max(nxt) + 1)   # another one where the longest sequence crosses a bound
+                self._ahead = _Ahead(slots, nxt, after, after.pack(None, nxt, slots, n))
         except CacheError:
             self._ahead = None   # the step itself will say what is wrong, if it comes
         return scores

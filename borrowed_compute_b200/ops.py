@@ -547,14 +547,16 @@ def attention_decode_splits(rows: int, kv_heads: int, max_pages: int) -> int:
     and stay within, one wave of two blocks on each SM; never more than a sequence
     can have pages.  Up to eight splits merge inside a thread-block cluster, which costs
     about 4 us less than the merge through scratch memory; so eight is the cap unless the
-    batch is so small that eight leave most SMs idle and sequences can grow so long (beyond
-    256 pages) that each split's share of the keys outweighs the dearer merge."""
+    batch is so small that eight leave most SMs idle and sequences are so long (beyond
+    192 pages) that each split's share of the keys outweighs the dearer merge.  Then the
+    count is a multiple of eight: clusters of eight merge among themselves and only their
+    sums go through scratch memory."""
     blocks = max(1, rows * kv_heads)
     sms = sm_count()
     fill = max(1, min(2 * sms // blocks, max_pages, 64))
-    if fill <= 8 or blocks * 8 >= sms or max_pages <= 256:
+    if fill <= 8 or blocks * 8 >= sms or max_pages <= 192:
         return min(fill, 8)
-    return fill
+    return fill // 8 * 8
 
 
 def _decode_workspace(device: torch.device, floats: int, ints: int):
@@ -576,14 +578,17 @@ def _decode_workspace(device: torch.device, floats: int, ints: int):
 def attention_decode(q: torch.Tensor, q_stride: int, k_cache: torch.Tensor, v_cache: torch.Tensor, page_table: torch.Tensor,
                      row_pos: torch.Tensor, row_slot: torch.Tensor, out: torch.Tensor, heads: int, kv_heads: int, head_dim: int,
                      window: int = 0, scale: Optional[float] = None, splits: Optional[int] = None, fuse: int = 0,
-                     cos_sin: Optional[torch.Tensor] = None, pairing: int = 0, via_scratch: bool = False) -> None:
+                     cos_sin: Optional[torch.Tensor] = None, pairing: int = 0, via_scratch: bool = False,
+                     reach: Optional[int] = None) -> None:
     """Attention of one new row a sequence (bf16): the cached positions are split across
     blocks and the heads of a kv head share each read; results are merged in a fixed order.
     Two to eight splits form a thread-block cluster and merge through one another's shared
     memory; more (or ``via_scratch``) merge through scratch memory, with the same result.
     ``fuse`` 1 or 2: ``q`` is the fused projection as the product left it; q is rotated on
     the fly by ``cos_sin`` (None: no rotation), and with 2 the row's rotated key and its
-    value are appended to the cache first (what rope_append would have done)."""
+    value are appended to the cache first (what rope_append would have done).  ``reach``:
+    a bound on the positions any row reaches (else what the page table can hold); the
+    number of splits is chosen by it, no result depends on it."""
     _need(q, "q", torch.bfloat16)
     _need(k_cache, "k_cache", torch.bfloat16)
     _need(v_cache, "v_cache", torch.bfloat16)
@@ -599,7 +604,12 @@ def attention_decode(q: torch.Tensor, q_stride: int, k_cache: torch.Tensor, v_ca
     if scale is None:
         scale = 1.0 / float(head_dim) ** 0.5
     if splits is None:
-        splits = attention_decode_splits(rows, kv_heads, page_table.shape[1])
+        pages = page_table.shape[1]
+        if reach is not None:
+            pages = min(pages, -(-max(1, reach) // PAGE))
+        if window > 0:
+            pages = min(pages, -(-window // PAGE) + 1)
+        splits = attention_decode_splits(rows, kv_heads, pages)
     scratch = counters = None
     if splits > 1:
         scratch, counters = _decode_workspace(q.device, rows * heads * splits * (head_dim + 2), rows * kv_heads)

@@ -63,7 +63,8 @@ class GroupedQueryAttention(Mixer):
             # One token a sequence: rotation and the cache append ride inside the attention kernel.
             ops.attention_decode(qkv, (H + 2 * G) * D, mem.k_pages, mem.v_pages, mem.page_table, ctx.row_pos, ctx.row_slot, att,
                                  H, G, D, window=self.window, scale=self.scale, fuse=2 if mem.writes else 1,
-                                 cos_sin=None if table is None else table.cos_sin, pairing=0 if table is None else table.pairing)
+                                 cos_sin=None if table is None else table.cos_sin, pairing=0 if table is None else table.pairing,
+                                 reach=ctx.max_total)
         else:
             ops.rope_append(qkv, None if table is None else table.cos_sin, ctx.row_pos, ctx.row_slot, mem.page_table,
                             mem.k_pages, mem.v_pages, H, G, D, 0 if table is None else table.pairing, write_cache=mem.writes)

@@ -109,7 +109,7 @@ def test_the_8b_shape_under_every_cut(engines):
         assert np.array_equal(f32[turn]["B"], f32["B alone"]) and np.array_equal(f32[turn]["C"], f32["C alone"]), turn
     # bfloat16 (captured decode steps; sizes 1, 2, 4): within the bound of the float32 engine over the same weights
     b16 = run_cuts(engines["bfloat16"])
-    assert sorted(engines["bfloat16"]._graphs) == [1, 2, 4]
+    assert sorted(rows for rows, _ in engines["bfloat16"]._graphs) == [1, 2, 4]
     layers, worst = CONFIG_8B["num_hidden_layers"], 0.0
     for name, got, want in [("whole", b16["whole"], ref), ("one by one", b16["one by one"], ref), ("B alone", b16["B alone"], f32["B alone"]),
                             ("C alone", b16["C alone"], f32["C alone"])] + \
@@ -137,7 +137,7 @@ def test_a_decode_step_of_64_sequences(engines):
         res[dtype] = [eng.step([StepEntry(s, [nxt[i][k]], want=(0,)) for i, s in enumerate(slots)]).cpu().numpy() for k in range(3)]
         for s in slots:
             eng.release(s)
-    assert 64 in engines["bfloat16"]._graphs
+    assert 64 in [rows for rows, _ in engines["bfloat16"]._graphs]
     for k in range(3):
         want, got = res["float32"][k], res["bfloat16"][k]
         assert got.shape == (64, VOCAB)

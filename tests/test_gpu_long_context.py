@@ -21,6 +21,8 @@ import pytest
 import plain_llama
 from conftest import make_weights, seeded_tokens, tolerance, weights_as_stored, write_folder
 
+torch = pytest.importorskip("torch")
+
 LENGTH, PROMPT = 17000, 16900
 FAR, NEAR = 300, 16450            # the fifth page and the 258th
 MARK_FAR, MARK_NEAR, ASKS = 7, 8, 11   # the tokens that are found and the token that looks for them
@@ -128,3 +130,41 @@ def test_the_marked_positions_hold_the_weight():
             without = list(t)
             without[at] = 20
             assert np.abs(plain_llama.logits(cfg, w, without, only=[row]) - ref).max() > 10 * tolerance("bfloat16", ref)
+
+
+@pytest.mark.gpu
+def test_captured_steps_change_when_a_sequence_crosses_a_bound(tmp_path):
+    """A captured decode step is made for a bound on the positions it reaches (a power of
+    two from 4,096 on), by which the attention plans its splits.  Two sequences, one of which
+    crosses 4,096 while the other stays short: the steps before, at and after the crossing,
+    staged ahead and fed from the device as the generation loop does, give the scores of
+    steps that are not captured, to the bit (at these lengths both ways cut the same)."""
+    from borrowed_compute_b200.engine import Engine, StepEntry
+
+    cfg = CONFIGS["head64"]
+    w = make_weights(cfg, 3, std=0.05, embed_std=1.0, head_std=0.1)
+    folder = write_folder(str(tmp_path / "m"), cfg, w, "bfloat16")
+    long, short = seeded_tokens(5, 4110, cfg["vocab_size"]), seeded_tokens(6, 60, cfg["vocab_size"])
+    runs = {}
+    for captured in (True, False):
+        eng = Engine.from_folder(folder, dtype="bfloat16", max_tokens=4352, max_slots=2, max_seq=cfg["max_position_embeddings"])
+        eng.use_graphs = eng.use_graphs and captured
+        a, b = eng.acquire(), eng.acquire()
+        eng.step([StepEntry(a, long[:4090], want=()), StepEntry(b, short[:40], want=())])
+        got = []
+        for i in range(20):
+            feed = (long[4090 + i], short[40 + i])
+            if captured and i > 0 and eng.can_step_again((a, b)):
+                eng.last_graph.views["tokens"][:2].copy_(torch.tensor(feed, dtype=torch.int32))   # as a sampler on the device would
+                got.append(eng.step_again().cpu().numpy())
+            else:
+                assert not captured or i == 0 or 4090 + i == 4096, f"step {i} was not staged"   # the step that crosses starts anew
+                got.append(eng.step([StepEntry(a, (feed[0],), want=(0,)), StepEntry(b, (feed[1],), want=(0,))]).cpu().numpy())
+        if captured:
+            assert sorted(eng._graphs) == [(2, 4096), (2, min(8192, eng.max_seq))]
+        eng.release(a), eng.release(b)
+        eng.cache.slots.check()
+        runs[captured] = np.stack(got)
+    assert np.array_equal(runs[True], runs[False])
+    ref = plain_llama.logits(cfg, weights_as_stored(w, "bfloat16"), long, only=list(range(4090, 4110)))
+    assert np.abs(runs[True][:, 0] - ref).max() <= tolerance("bfloat16", ref)
