@@ -18,6 +18,8 @@
 // step of a batch.
 #include <cooperative_groups.h>
 
+#include <type_traits>
+
 #include "common.cuh"
 #include "mma_tiles.cuh"
 #include "tc_ptx.cuh"
@@ -28,6 +30,7 @@ namespace cg = cooperative_groups;
 #define AD_THREADS 128
 #define AD_STAGES 3
 #define AD_MAX_GROUP 16
+#define AD_MAX_CLUSTER 16    // splits that merge through one another's shared memory (more than 8: not portable, asked for per kernel)
 
 // Byte offset of 16-byte chunk c of row r in a page as TMA writes it: blocks of [64 rows][64
 // elements] with the 128-byte swizzle (chunk xor row within each 128-byte row).
@@ -381,45 +384,46 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
         const int total = group * D, share = (total + csize - 1) / csize;
         // All reads of the peers' shared memory (a good tenth of a microsecond each) are asked
         // for before any is used; the splits are added in their order as ever.
-        const float *ppm[8], *ppl[8], *ppo[8];
+        auto merge = [&](auto cap) {
+            constexpr int CAP = decltype(cap)::value;   // peers the unrolled loops are written for
+            // (A peer's maxima and normalisers lie behind its sums, as here: one address a peer.)
+            const float* ppo[CAP];
 #pragma unroll
-        for (int sp = 0; sp < 8; sp++) {
-            const int from = sp < csize ? sp : 0;
-            ppm[sp] = cl.map_shared_rank(pm, from);
-            ppl[sp] = cl.map_shared_rank(pl, from);
-            ppo[sp] = cl.map_shared_rank(po, from);
-        }
-        for (int i = crank * share + threadIdx.x; i < min(total, (crank + 1) * share); i += AD_THREADS) {
-            const int hr = i / D, d = i - hr * D;
-            float ms[8], ls[8], os[8];
+            for (int sp = 0; sp < CAP; sp++) ppo[sp] = cl.map_shared_rank(po, sp < csize ? sp : 0);
+            for (int i = crank * share + threadIdx.x; i < min(total, (crank + 1) * share); i += AD_THREADS) {
+                const int hr = i / D, d = i - hr * D;
+                float ms[CAP], ls[CAP], os[CAP];
 #pragma unroll
-            for (int sp = 0; sp < 8; sp++) {
-                const bool has = sp < csize;
-                ms[sp] = has ? ppm[sp][hr] : -INFINITY;
-                ls[sp] = has ? ppl[sp][hr] : 0.0f;
-                os[sp] = has ? ppo[sp][i] : 0.0f;
-            }
-            float M = -INFINITY;
+                for (int sp = 0; sp < CAP; sp++) {
+                    const bool has = sp < csize;
+                    ms[sp] = has ? ppo[sp][16 * D + hr] : -INFINITY;
+                    ls[sp] = has ? ppo[sp][16 * D + 16 + hr] : 0.0f;
+                    os[sp] = has ? ppo[sp][i] : 0.0f;
+                }
+                float M = -INFINITY;
 #pragma unroll
-            for (int sp = 0; sp < 8; sp++) M = fmaxf(M, ms[sp]);
-            float L = 0.0f, O = 0.0f;
+                for (int sp = 0; sp < CAP; sp++) M = fmaxf(M, ms[sp]);
+                float L = 0.0f, O = 0.0f;
 #pragma unroll
-            for (int sp = 0; sp < 8; sp++) {
-                const float f = ms[sp] == -INFINITY ? 0.0f : exp2f(ms[sp] - M);
-                L += ls[sp] * f;
-                O += os[sp] * f;
-            }
-            if (parts == 1) {
-                out[((size_t)r * H + g * group + hr) * D + d] = __float2bfloat16_rn(L > 0.0f ? O / L : 0.0f);
-            } else {
-                float* dst = scratch + (((size_t)r * H + g * group + hr) * parts + part) * stride;
-                __stcg(dst + d, O);
-                if (d == 0) {
-                    __stcg(dst + D, M);
-                    __stcg(dst + D + 1, L);
+                for (int sp = 0; sp < CAP; sp++) {
+                    const float f = ms[sp] == -INFINITY ? 0.0f : exp2f(ms[sp] - M);
+                    L += ls[sp] * f;
+                    O += os[sp] * f;
+                }
+                if (parts == 1) {
+                    out[((size_t)r * H + g * group + hr) * D + d] = __float2bfloat16_rn(L > 0.0f ? O / L : 0.0f);
+                } else {
+                    float* dst = scratch + (((size_t)r * H + g * group + hr) * parts + part) * stride;
+                    __stcg(dst + d, O);
+                    if (d == 0) {
+                        __stcg(dst + D, M);
+                        __stcg(dst + D + 1, L);
+                    }
                 }
             }
-        }
+        };
+        if (csize > 8) merge(std::integral_constant<int, AD_MAX_CLUSTER>());
+        else merge(std::integral_constant<int, 8>());
         cl.sync();   // no block may leave while a peer still reads its shared memory
         if (parts == 1) return;
     }
@@ -465,6 +469,9 @@ struct FusedRope {
 // everywhere; both give the same bits.  For measurements and tests.
 static int g_ad_tma = 1;
 extern "C" void bc_attention_decode_set_tma(int on) { g_ad_tma = on != 0; }
+// Whether sixteen splits may run as one cluster of sixteen (else as two of eight).  For measurements and tests.
+static int g_ad_cluster16 = 1;
+extern "C" void bc_attention_decode_set_cluster16(int on) { g_ad_cluster16 = on != 0; }
 
 template <int D, bool TMA>
 static int launch_as(const CUtensorMap& mk, const CUtensorMap& mv, const void* q, int q_stride, const void* k_cache, const void* v_cache,
@@ -487,7 +494,32 @@ static int launch_as(const CUtensorMap& mk, const CUtensorMap& mv, const void* q
     // distributed shared memory; more go through the caller's scratch memory.
     // More than eight: clusters of eight, four or two where that divides them, whose sums then go through scratch.
     int csize = n_splits <= 8 ? n_splits : n_splits % 8 == 0 ? 8 : n_splits % 4 == 0 ? 4 : n_splits % 2 == 0 ? 2 : 1;
-    if (n_splits > 8 && !(scratch && counters)) csize = 1;
+    if (n_splits == 16 && fr.allow_cluster && g_ad_cluster16 && (long long)rows * G * 16 <= bc_sm_count()) {
+        // One cluster of sixteen, where every block has an SM to itself (with more blocks than SMs two clusters of
+        // eight place better: measured).  Sixteen blocks a cluster is more than every device must offer: asked for
+        // once, and taken only if the device can place one.
+        static int sixteen = -1;
+        if (sixteen < 0) {
+            sixteen = 0;
+            if (cudaFuncSetAttribute(attention_decode_kernel<D, TMA>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess) {
+                cudaLaunchConfig_t cfg = {};
+                cfg.gridDim = dim3(16, 1, 1);
+                cfg.blockDim = dim3(AD_THREADS);
+                cfg.dynamicSmemBytes = SMEM;
+                cudaLaunchAttribute attr[1];
+                attr[0].id = cudaLaunchAttributeClusterDimension;
+                attr[0].val.clusterDim.x = 16;
+                attr[0].val.clusterDim.y = attr[0].val.clusterDim.z = 1;
+                cfg.attrs = attr;
+                cfg.numAttrs = 1;
+                int fit = 0;
+                if (cudaOccupancyMaxActiveClusters(&fit, attention_decode_kernel<D, TMA>, &cfg) == cudaSuccess && fit > 0) sixteen = 1;
+            }
+            (void)cudaGetLastError();
+        }
+        if (sixteen == 1) csize = 16;
+    }
+    if (n_splits > 8 && csize < n_splits && !(scratch && counters)) csize = 1;
     const bool clustered = n_splits > 1 && fr.allow_cluster && csize > 1;
     if (clustered)
         bc_launch_clustered(attention_decode_kernel<D, TMA>, grid, dim3(AD_THREADS), (size_t)SMEM, s, dim3(csize, 1, 1), mk, mv, (const bf16*)q,

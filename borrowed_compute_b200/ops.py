@@ -536,6 +536,13 @@ def set_attention_decode_tma(on: bool) -> None:
     lib().bc_attention_decode_set_tma(_c_int(1 if on else 0))
 
 
+def set_attention_decode_cluster16(on: bool) -> None:
+    """Whether sixteen splits of the decode attention run as one thread-block cluster of
+    sixteen where the device places one (the default) or as two clusters of eight whose sums
+    go through scratch memory.  For measurements and tests."""
+    lib().bc_attention_decode_set_cluster16(_c_int(1 if on else 0))
+
+
 def attention_decode_accepts(heads: int, kv_heads: int, head_dim: int, dtype: torch.dtype) -> bool:
     """Whether the split decode kernel takes these sizes (bf16; at most 16 heads a kv head;
     head size a multiple of 16 up to 128).  Otherwise attention_rows serves."""
@@ -547,15 +554,24 @@ def attention_decode_splits(rows: int, kv_heads: int, max_pages: int) -> int:
     and stay within, one wave of two blocks on each SM; never more than a sequence
     can have pages.  Up to eight splits merge inside a thread-block cluster, which costs
     about 4 us less than the merge through scratch memory; so eight is the cap unless the
-    batch is so small that eight leave most SMs idle and sequences are so long (beyond
-    192 pages) that each split's share of the keys outweighs the dearer merge.  Then the
-    count is a multiple of eight: clusters of eight merge among themselves and only their
-    sums go through scratch memory."""
+    batch is so small that eight leave most SMs idle and the sequences are long.  Then:
+    sixteen as one cluster of sixteen, where all of these find an SM each (one sequence of
+    eight kv heads, from 64 pages on: 13 against 18 us a launch at 8,000 positions); and
+    beyond 192 pages (320 where sixteen serve) a multiple of eight: clusters of eight merge
+    among themselves and only their sums go through scratch memory (32 against 59 us at
+    32,000 positions)."""
     blocks = max(1, rows * kv_heads)
     sms = sm_count()
     fill = max(1, min(2 * sms // blocks, max_pages, 64))
-    if fill <= 8 or blocks * 8 >= sms or max_pages <= 192:
-        return min(fill, 8)
+    if fill <= 8 or blocks * 8 >= sms:
+        # A power of two: clusters of 3, 5, 6 or 7 blocks place badly once the SMs fill up
+        # (five sequences of eight kv heads: 20.7 us with 7 splits, 14.7 us with 4).
+        return 1 << (min(fill, 8).bit_length() - 1)
+    sixteen = blocks * 16 <= sms and fill >= 16
+    if sixteen and 64 < max_pages <= 320:
+        return 16
+    if max_pages <= 192 or (sixteen and max_pages <= 64):
+        return 8
     return fill // 8 * 8
 
 
