@@ -382,6 +382,29 @@ def bench_13b(pk, rng) -> dict:
     return out
 
 
+def bench_long(pk, rng) -> dict:
+    """The 8B shape with one sequence of 32,000 tokens (the context that Llama-3.1 is made
+    for is 131,072): the prompt in ONE step, then 64 decode steps, device-timed.  At this
+    length a decode step reads 4 GB of keys and values beside the 16 GB of weights, and the
+    prompt's work is half attention."""
+    from borrowed_compute_b200 import Local
+
+    cfg, layers = dict(CONFIG_8B, max_position_embeddings=32768), CONFIG_8B["num_hidden_layers"]
+    length, steps, warmup = 32000, 64, 4
+    model = Local.random(cfg, seed=0, dtype="bfloat16", max_tokens=32768, max_slots=1, max_seq=32768)
+    prompts = [[int(t) for t in rng.integers(0, cfg["vocab_size"], length)]]
+    r = timed_decode(model.engine, prompts, steps, warmup, rng, cfg["vocab_size"], prompts_a_step=1)
+    need = decode_bytes(cfg, layers, 1, r["cached_tokens"])
+    flops = prefill_flops(cfg, layers, [length])
+    out = {"decode_b1_ctx32k": round(r["tok_s"], 1), "decode_b1_ctx32k_ms_per_step": round(r["ms_per_step"], 4),
+           "decode_b1_ctx32k_hbm_frac": round(need / (r["ms_per_step"] / 1000.0) / 1e9 / pk["hbm_gbs"], 4),
+           "prefill_32k_tok_s": round(length / (r["prompt_ms"] / 1000.0), 1),
+           "prefill_32k_frac": round(flops / (r["prompt_ms"] / 1000.0) / (pk["bf16_tflops"] * 1e12), 4)}
+    del model
+    free_device_memory()
+    return out
+
+
 def bench_3b(pk, rng) -> dict:
     """The Llama-3.2-3B shape (tied head): 64 prompts of 1,024 tokens, then 512 tokens each
     sampled at temperature 1.0, through the entry point (the sampler runs every step)."""
@@ -524,6 +547,7 @@ def run_ours(args) -> dict:
     del model, eng
     free_device_memory()
     if not args.no_points and not args.layers:
+        points.update(bench_long(pk, rng))
         points.update(bench_13b(pk, rng))
         points.update(bench_3b(pk, rng))
         points.update(bench_tiny(rng))
