@@ -79,8 +79,12 @@ __device__ __forceinline__ void tc_stamp(const TcParams& p, int what) {
 // tiles of one or two token tiles, and each is fetched from HBM once, not once a token tile.
 #define TC_RASTER 16
 
+// Threads a block: warp 0 asks for tiles, warp 1 issues the products, then the epilogue warps: four, or eight from 64
+// tokens a tile on.
+__host__ __device__ constexpr int tc_threads(int bn) { return bn >= 64 ? TC_THREADS + 128 : TC_THREADS; }
+
 template <int BN, int EPI, bool STACK>
-__global__ void __launch_bounds__(TC_THREADS, 1)
+__global__ void __launch_bounds__(tc_threads(BN), BN == 64 ? 2 : 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, const TcParams p) {
     constexpr int A_BYTES = TC_BM * TC_BK * 2;
     constexpr int B_BYTES = BN * TC_BK * 2;
@@ -92,6 +96,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     constexpr int OUT_TILES = TWO_TILES ? 2 : 1;
     constexpr int STAGE_BYTES = N_ACC * A_BYTES + B_BYTES;
     constexpr int TMEM_COLS = N_ACC * BN < 32 ? 32 : N_ACC * BN;
+    // From 64 tokens a tile on, eight warps share the epilogue: the two warps that may read a
+    // quarter of the TMEM lanes (a warp reads lanes 32 (warp % 4) ..) take half of the token
+    // columns each.  What the epilogue costs grows with the tile; at few tokens four suffice.
+    constexpr int HALVES = (tc_threads(BN) - 64) / 128;
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     // Tiles need 1024-byte alignment for the 128-byte swizzle.
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -197,9 +205,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         }
     } else {
         // Epilogue: this warp reads TMEM lanes 32 q .. 32 q + 31, i.e. weight rows n0 + 32 q + lane.
-        const int q = warp & 3;
+        const int q = warp & 3, half = (warp - 2) >> 2;
         const int n_first = n0 + 32 * q + lane;
         const bool split = gridDim.z > 1;
+        constexpr int ACC_COLS = N_ACC * BN / HALVES;        // accumulator columns this warp moves out of TMEM
+        const int acc_first = half * ACC_COLS;
         const int tile = blockIdx.x;
         // Split-K: every split leaves its partial tile in scratch memory; the four row
         // quarters of a tile each have a counter, and the warp that arrives last adds the
@@ -222,7 +232,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             if (ok) {
                 float* mine = reinterpret_cast<float*>(smem) + 32 * q + lane;
 #pragma unroll 1
-                for (int c0 = 0; c0 < N_ACC * BN; c0 += 16) {
+                for (int c0 = acc_first; c0 < acc_first + ACC_COLS; c0 += 16) {
                     uint32_t v[16];
                     tmem_load16(taddr + c0, v);
                     tmem_load_wait();
@@ -233,7 +243,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         } else if (split) {
             if (ok) {
 #pragma unroll 1
-                for (int c0 = 0; c0 < N_ACC * BN; c0 += 16) {   // the second accumulator follows the first in TMEM and in scratch
+                for (int c0 = acc_first; c0 < acc_first + ACC_COLS; c0 += 16) {   // the second accumulator follows the first in TMEM and in scratch
                     uint32_t v[16];
                     tmem_load16(taddr + c0, v);
                     tmem_load_wait();
@@ -246,7 +256,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             int arrived = 0;
             if (lane == 0) arrived = atomicAdd(counter, 1);
             arrived = __shfl_sync(0xffffffffu, arrived, 0);
-            finish = arrived == (int)gridDim.z - 1;
+            finish = arrived == HALVES * (int)gridDim.z - 1;   // every warp of the quarter, in every split, has left its columns
             if (finish) {
                 __threadfence();
                 if (lane == 0) *counter = 0;   // ready for the next launch
@@ -281,22 +291,24 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             };
             constexpr int TOTAL = OUT_TILES * BN;
             if (!split) {
+                constexpr int MINE = TOTAL / HALVES;             // output columns this warp writes
+                const int first = half * MINE, end = first + MINE;
                 // The accumulator comes out of TMEM 16 columns at a time, the next piece on its way
                 // while this one is written, so the round trip to TMEM is paid once, not per piece.
                 uint32_t va[16], vb[16], ua[16], ub[16];
-                tmem_load16(taddr, va);
-                if (EPI == EPI_SWIGLU) tmem_load16(taddr + BN, ua);
+                tmem_load16(taddr + first, va);
+                if (EPI == EPI_SWIGLU) tmem_load16(taddr + BN + first, ua);
 #pragma unroll 1
-                for (int cc = 0; cc < TOTAL; cc += 32) {
+                for (int cc = first; cc < end; cc += 32) {
                     tmem_load_wait();
-                    if (cc + 16 < TOTAL) {
+                    if (cc + 16 < end) {
                         tmem_load16(taddr + cc + 16, vb);
                         if (EPI == EPI_SWIGLU) tmem_load16(taddr + BN + cc + 16, ub);
                     }
                     emit(va, ua, cc);
-                    if (cc + 16 < TOTAL) {
+                    if (cc + 16 < end) {
                         tmem_load_wait();
-                        if (cc + 32 < TOTAL) {
+                        if (cc + 32 < end) {
                             tmem_load16(taddr + cc + 32, va);
                             if (EPI == EPI_SWIGLU) tmem_load16(taddr + BN + cc + 32, ua);
                         }
@@ -331,7 +343,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         cl.sync();
         if (warp == 2 && lane == 0) TC_STAMP(9);
         if (warp >= 2) {
-            const int q = warp & 3, row = 32 * q + lane, n = n0 + row;
+            const int q = warp & 3, half = (warp - 2) >> 2, row = 32 * q + lane, n = n0 + row;
             const int S = (int)gridDim.z, rank = (int)blockIdx.z;
             const float* base = reinterpret_cast<const float*>(smem) + row;
             auto write = [&](int c, float v, float u) {
@@ -355,7 +367,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 #pragma unroll
                 for (int z = 0; z < SS; z++) peer[z] = cl.map_shared_rank(base, z);
                 const int last = min(BN, p.T - t0);
-                for (int c = rank; c < last; c += CB * SS) {
+                for (int c = rank + half * CB * SS; c < last; c += HALVES * CB * SS) {   // batches in turn to the two warps of a quarter
                     float v[CB][SS], u[CB][SS];
 #pragma unroll
                     for (int b = 0; b < CB; b++) {
@@ -384,7 +396,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             else if (S == 4) finish(std::integral_constant<int, 4>());
             else if (S == 2) finish(std::integral_constant<int, 2>());
             else
-                for (int c = rank; c < BN && t0 + c < p.T; c += S) {
+                for (int c = rank + half * S; c < BN && t0 + c < p.T; c += HALVES * S) {
                     float v = 0.0f, u = 0.0f;
                     for (int z = 0; z < S; z++) {
                         const float* theirs = cl.map_shared_rank(base, z);
@@ -737,8 +749,8 @@ static int launch(const CUtensorMap& mw, const CUtensorMap& mx, TcParams p, int 
         bc_set_error("gemm_tc: this split-K needs a workspace");
         return BC_ERR_ARG;
     }
-    cudaError_t e = p.clustered ? bc_launch_clustered(gemm_tc_kernel<BN, EPI, STACK>, grid, dim3(TC_THREADS), (size_t)smem, s, dim3(1, 1, splits), mw, mx, p)
-                                : bc_launch(gemm_tc_kernel<BN, EPI, STACK>, grid, dim3(TC_THREADS), (size_t)smem, s, mw, mx, p);
+    cudaError_t e = p.clustered ? bc_launch_clustered(gemm_tc_kernel<BN, EPI, STACK>, grid, dim3(tc_threads(BN)), (size_t)smem, s, dim3(1, 1, splits), mw, mx, p)
+                                : bc_launch(gemm_tc_kernel<BN, EPI, STACK>, grid, dim3(tc_threads(BN)), (size_t)smem, s, mw, mx, p);
     if (e != cudaSuccess) {
         bc_set_error("gemm_tc: launch failed: %s", cudaGetErrorString(e));
         return (int)e;

@@ -11,7 +11,7 @@ enum { EPI_STORE = 0, EPI_STORE_F32 = 1, EPI_ADD_F32 = 2, EPI_SWIGLU = 3 };
 
 #define TC_BM 128          // weight rows a tile (MMA M)
 #define TC_BK 64           // k a stage: 64 bf16 = one 128-byte swizzle row
-#define TC_THREADS 192     // warp 0 TMA, warp 1 MMA, warps 2-5 epilogue
+#define TC_THREADS 192     // warp 0 TMA, warp 1 MMA, warps 2-5 epilogue (the one-block product adds four more from 64 tokens a tile on)
 #define TC_SMEM_LIMIT 230400   // dynamic bytes asked for at most; static barriers take a little more
 #define TC_WAIT_CYCLES 2000000000ll   // clocks a wait may take before it gives up: about a second
 
