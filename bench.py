@@ -382,21 +382,22 @@ def bench_13b(pk, rng) -> dict:
     return out
 
 
-def bench_long(pk, rng) -> dict:
+def bench_long(pk, rng, layers=0) -> dict:
     """The 8B shape with one sequence of 32,000 tokens (the context that Llama-3.1 is made
     for is 131,072): the prompt in ONE step, then 64 decode steps, device-timed.  At this
     length a decode step reads 4 GB of keys and values beside the 16 GB of weights, and the
     prompt's work is half attention."""
     from borrowed_compute_b200 import Local
 
-    cfg, layers = dict(CONFIG_8B, max_position_embeddings=32768), CONFIG_8B["num_hidden_layers"]
+    layers = layers or CONFIG_8B["num_hidden_layers"]
+    cfg = dict(CONFIG_8B, max_position_embeddings=32768, num_hidden_layers=layers)
     length, steps, warmup = 32000, 64, 4
     model = Local.random(cfg, seed=0, dtype="bfloat16", max_tokens=32768, max_slots=1, max_seq=32768)
     prompts = [[int(t) for t in rng.integers(0, cfg["vocab_size"], length)]]
     r = timed_decode(model.engine, prompts, steps, warmup, rng, cfg["vocab_size"], prompts_a_step=1)
     need = decode_bytes(cfg, layers, 1, r["cached_tokens"])
     flops = prefill_flops(cfg, layers, [length])
-    out = {"decode_b1_ctx32k": round(r["tok_s"], 1), "decode_b1_ctx32k_ms_per_step": round(r["ms_per_step"], 4),
+    out = {"layers": layers, "decode_b1_ctx32k": round(r["tok_s"], 1), "decode_b1_ctx32k_ms_per_step": round(r["ms_per_step"], 4),
            "decode_b1_ctx32k_hbm_frac": round(need / (r["ms_per_step"] / 1000.0) / 1e9 / pk["hbm_gbs"], 4),
            "prefill_32k_tok_s": round(length / (r["prompt_ms"] / 1000.0), 1),
            "prefill_32k_frac": round(flops / (r["prompt_ms"] / 1000.0) / (pk["bf16_tflops"] * 1e12), 4)}
@@ -580,6 +581,8 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 and 64 and the two other shapes")
     ap.add_argument("--no-breakdown", action="store_true", help="skip the per-class timing of one decode and one prompt step")
+    ap.add_argument("--point", default="", choices=["", "long", "13b", "3b", "tiny"],
+                    help="run one of the further workloads alone and print its figures (not the contract's line)")
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable": "the reference is a Rust workspace (no setup.py or pyproject) "
@@ -590,6 +593,14 @@ def main() -> int:
         return 2
     if args.warmup < 3:
         args.warmup = 3
+    if args.point:
+        import numpy as np
+
+        rng = np.random.default_rng(0)
+        one = {"long": lambda: bench_long(peaks(), rng, args.layers), "13b": lambda: bench_13b(peaks(), rng), "3b": lambda: bench_3b(peaks(), rng),
+               "tiny": lambda: bench_tiny(rng)}[args.point]
+        print(json.dumps({"point": args.point, **one()}))
+        return 0
     print(json.dumps(run_ours(args)))
     return 0
 
