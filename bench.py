@@ -397,7 +397,7 @@ def bench_long(pk, rng, layers=0) -> dict:
     r = timed_decode(model.engine, prompts, steps, warmup, rng, cfg["vocab_size"], prompts_a_step=1)
     need = decode_bytes(cfg, layers, 1, r["cached_tokens"])
     flops = prefill_flops(cfg, layers, [length])
-    out = {"layers": layers, "decode_b1_ctx32k": round(r["tok_s"], 1), "decode_b1_ctx32k_ms_per_step": round(r["ms_per_step"], 4),
+    out = {"decode_b1_ctx32k_layers": layers, "decode_b1_ctx32k": round(r["tok_s"], 1), "decode_b1_ctx32k_ms_per_step": round(r["ms_per_step"], 4),
            "decode_b1_ctx32k_hbm_frac": round(need / (r["ms_per_step"] / 1000.0) / 1e9 / pk["hbm_gbs"], 4),
            "prefill_32k_tok_s": round(length / (r["prompt_ms"] / 1000.0), 1),
            "prefill_32k_frac": round(flops / (r["prompt_ms"] / 1000.0) / (pk["bf16_tflops"] * 1e12), 4)}
