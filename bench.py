@@ -495,6 +495,8 @@ def run_ours(args) -> dict:
     flops = prefill_flops(cfg, layers, [PROMPT])
     prefill = {"value": round(PROMPT / (pms / 1000.0), 1), "tokens": PROMPT, "ms": round(pms, 3),
                "frac": round(flops / (pms / 1000.0) / (pk["bf16_tflops"] * 1e12), 4), "tflops": round(flops / (pms / 1000.0) / 1e12, 1)}
+    if "bf16_tflops_sustained" in pk:   # what the same library product holds for seconds under the power cap, beside the burst figure above
+        prefill["frac_of_sustained"] = round(flops / (pms / 1000.0) / (pk["bf16_tflops_sustained"] * 1e12), 4)
 
     # --- end to end through the Python entry point: host ids in, host ids out, every step.
     # As on the device: W passes that are not timed (the clocks settle after the prompt burst),
