@@ -227,11 +227,14 @@ def attention_reference(q, k, v, window=0):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("window", [0, 20])
-def test_attention_rows(dtype, window):
-    """Rows of five sequences of lengths around the page and tile edges, pages scattered."""
+@pytest.mark.parametrize("H,G,D", [(6, 3, 48), (2, 1, 256), (4, 2, 160), (34, 1, 16)])
+def test_attention_rows(dtype, window, H, G, D):
+    """Rows of five sequences of lengths around the page and tile edges, pages scattered; head
+    sizes up to the largest the kernel takes (256) and more heads on a kv head than the tiled
+    kernels take (34)."""
     from borrowed_compute_b200 import ops
 
-    H, G, D, n_pages = 6, 3, 48, 16
+    n_pages = 16
     lengths = [1, 32, 64, 65, 200]
     r = rng(8)
     page_lists = [[5], [9], [2], [11, 0], [7, 3, 14, 1]]

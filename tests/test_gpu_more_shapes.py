@@ -1,6 +1,7 @@
 """Whole models at further sizes, against the plain implementation: a head size of 48 (the
-mma.sync prompt kernel), 64 with five heads a kv head and a tied head, and 128 with eight
-heads on one kv head (the tcgen05 prompt kernel); widths, feed-forward sizes and
+mma.sync prompt kernel), 64 with five heads a kv head and a tied head, 128 with eight
+heads on one kv head (the tcgen05 prompt kernel), 256 and 34 heads on one kv head (beyond
+the tiled kernels: the one-warp-a-row kernel); widths, feed-forward sizes and
 vocabularies that are no powers of two; prompts of more than 128 tokens (the product on
 pairs of SMs) in a batch of two whose shorter request ends earlier, then single tokens.
 The engines are made one after another in one process and dropped without ceremony: a
@@ -26,6 +27,14 @@ CONFIGS = {
     "head128": {"architectures": ["LlamaForCausalLM"], "num_hidden_layers": 1, "hidden_size": 1024, "num_attention_heads": 8,
                 "num_key_value_heads": 1, "head_dim": 128, "intermediate_size": 1536, "vocab_size": 515, "rope_theta": 500000.0,
                 "rms_norm_eps": 1e-5, "max_position_embeddings": 2048},
+    # a head size beyond the tiled bf16 kernels (the one-warp-a-row kernel serves prompts and single tokens)
+    "head256": {"architectures": ["LlamaForCausalLM"], "num_hidden_layers": 2, "hidden_size": 200, "num_attention_heads": 2,
+                "num_key_value_heads": 1, "head_dim": 256, "intermediate_size": 328, "vocab_size": 401, "rope_theta": 10000.0,
+                "rms_norm_eps": 1e-5, "max_position_embeddings": 1024, "rope_pairing": "adjacent"},
+    # more heads on a kv head (34) than the tiled decode kernel takes
+    "group34": {"architectures": ["LlamaForCausalLM"], "num_hidden_layers": 1, "hidden_size": 272, "num_attention_heads": 34,
+                "num_key_value_heads": 1, "head_dim": 16, "intermediate_size": 136, "vocab_size": 333, "rope_theta": 10000.0,
+                "rms_norm_eps": 1e-6, "max_position_embeddings": 1024},
 }
 
 
