@@ -31,6 +31,10 @@ CONFIGS = {
     "head256": {"architectures": ["LlamaForCausalLM"], "num_hidden_layers": 2, "hidden_size": 200, "num_attention_heads": 2,
                 "num_key_value_heads": 1, "head_dim": 256, "intermediate_size": 328, "vocab_size": 401, "rope_theta": 10000.0,
                 "rms_norm_eps": 1e-5, "max_position_embeddings": 1024, "rope_pairing": "adjacent"},
+    # a width and a feed-forward size that are no multiples of 8: no TMA box starts on a 16-byte boundary there, the products run on CUDA cores
+    "odd_widths": {"architectures": ["LlamaForCausalLM"], "num_hidden_layers": 2, "hidden_size": 90, "num_attention_heads": 2,
+                   "num_key_value_heads": 1, "head_dim": 48, "intermediate_size": 77, "vocab_size": 203, "rope_theta": 10000.0,
+                   "rms_norm_eps": 1e-5, "max_position_embeddings": 1024},
     # more heads on a kv head (34) than the tiled decode kernel takes
     "group34": {"architectures": ["LlamaForCausalLM"], "num_hidden_layers": 1, "hidden_size": 272, "num_attention_heads": 34,
                 "num_key_value_heads": 1, "head_dim": 16, "intermediate_size": 136, "vocab_size": 333, "rope_theta": 10000.0,
