@@ -233,8 +233,14 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             const bool whole = window == 0 && page_ok && tile * BC_PAGE + BC_PAGE - 1 <= warp_first_pos;
             float tmax = -INFINITY;
             if (whole) {
+                // Two chains of three-input maxima: 32 instructions, each chain 16 long.
+                float ta = -INFINITY, tb = -INFINITY;
 #pragma unroll
-                for (int c = 0; c < 64; c++) tmax = fmaxf(tmax, __uint_as_float(sv[c]));
+                for (int c = 0; c < 64; c += 4) {
+                    ta = max3(ta, __uint_as_float(sv[c]), __uint_as_float(sv[c + 1]));
+                    tb = max3(tb, __uint_as_float(sv[c + 2]), __uint_as_float(sv[c + 3]));
+                }
+                tmax = fmaxf(ta, tb);
             } else {
 #pragma unroll
                 for (int c = 0; c < 64; c++) {
@@ -282,21 +288,30 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 tmem_store_wait();
             }
             const float base = m_used == -INFINITY ? 0.0f : m_used;
-            float sum = 0.0f;
+            // Scores scaled and shifted two at a time (fma.rn.f32x2: the same roundings as fmaf),
+            // the exponentials' sums kept in four pairs, so that no chain of additions is longer than 8.
+            const uint64_t scale2 = pack_f32x2(scale_log2, scale_log2), shift2 = pack_f32x2(-base, -base);
+            uint64_t sums[4] = {0ull, 0ull, 0ull, 0ull};
             uint8_t* p_row = p_smem + (PB * t + (j & (PB - 1))) * ROW_BLOCK + (32 * q + lane) * 128;
 #pragma unroll
             for (int c8 = 0; c8 < 8; c8++) {
                 uint32_t packed[4];
 #pragma unroll
                 for (int i = 0; i < 4; i++) {
-                    const float a = fast_exp2(fmaf(__uint_as_float(sv[c8 * 8 + 2 * i]), scale_log2, -base));
-                    const float b = fast_exp2(fmaf(__uint_as_float(sv[c8 * 8 + 2 * i + 1]), scale_log2, -base));
-                    sum += a + b;
+                    float a, b;
+                    unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(sv[c8 * 8 + 2 * i]), __uint_as_float(sv[c8 * 8 + 2 * i + 1])), scale2, shift2), a, b);
+                    a = fast_exp2(a), b = fast_exp2(b);
+                    sums[i] = add_f32x2(sums[i], pack_f32x2(a, b));
                     packed[i] = pack_bf16(a, b);
                 }
                 *reinterpret_cast<uint4*>(p_row + ((c8 ^ (lane & 7)) << 4)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
             }
-            l += sum;
+            {
+                float s0, s1, s2, s3;
+                unpack_f32x2(add_f32x2(sums[0], sums[1]), s0, s1);
+                unpack_f32x2(add_f32x2(sums[2], sums[3]), s2, s3);
+                l += (s0 + s1) + (s2 + s3);
+            }
             // Value rows that hold no position of this sequence: the whole page if there is none,
             // else what lies past the sequence's last position in its last page (a sequence that
             // held the page before may have left not-a-numbers there, and 0 x NaN is NaN in the
