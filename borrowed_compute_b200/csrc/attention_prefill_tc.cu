@@ -15,10 +15,12 @@
 //   - Four softmax warps a query tile own 32 rows each, one row a thread (TMEM lane = row), so row
 //     maxima and sums need no shuffles: tcgen05.ld the scores, mask what the row may not
 //     see (positions after its own, before its window), exponentiate against the running
-//     maximum, round to bf16 and write P to shared memory in the A-operand layout.
-//   - O += P V is a second chain of tcgen05.mma (N = head size, K = 64 positions) into a
-//     TMEM accumulator that stays there for the whole block.  Values are the n-major B
-//     operand ([position][d] with d contiguous), exactly as TMA wrote the page.
+//     maximum (scaled two at a time, fma.rn.f32x2), round to bf16 and write P back into tensor
+//     memory (tcgen05.st), two to a column, over the first half of the scores it came from.
+//   - O += P V is a second chain of tcgen05.mma (N = head size, K = 64 positions) whose A
+//     operand is read out of tensor memory, into a TMEM accumulator that stays there for the
+//     whole block.  Values are the n-major B operand ([position][d] with d contiguous),
+//     exactly as TMA wrote the page.  Shared memory holds Q and the ring of pages, nothing else.
 //   - The running maximum is only raised when the new maximum exceeds it by more than 8 (in
 //     log2 units), so P stays below 2^8 and the accumulator is rescaled (TMEM load, multiply,
 //     store) a few times a block instead of once a page.  Sums and outputs use the same
@@ -34,7 +36,39 @@
 
 #define APT_ROWS 128        // query rows of one tile: the M of the MMAs, the lanes of TMEM
 #define APT_PAGES_KEPT 256
+// Where P (the exponentials, bf16) goes between the softmax and the product with the values:
+// into tensor memory, over the first half of the scores it came from (1, the default: the
+// product then reads its A operand out of TMEM and shared memory carries 72 KB a page less for
+// two query tiles of head size 128), or into shared memory (0, for comparison).
+#ifndef APT_P_TMEM
+#define APT_P_TMEM 1
+#endif
+#define APT_SMEM_LIMIT 232448
+#define APT_Q_BYTES(D, NT) (((D) / 64) * (NT) * APT_ROWS * 128)
+#define APT_STAGE_BYTES(D) (2 * ((D) / 64) * 64 * 128)
+#define APT_PB(D, NT) (APT_P_TMEM ? 0 : ((D) == 128 && (NT) == 2) ? 1 : 2)
+#define APT_STAGES_FIT(D, NT) ((APT_SMEM_LIMIT - 1024 - APT_Q_BYTES(D, NT)) / APT_STAGE_BYTES(D))
+#define APT_STAGES(D, NT) (!APT_P_TMEM ? 4 : APT_STAGES_FIT(D, NT) > 6 ? 6 : APT_STAGES_FIT(D, NT))
 #define APT_RAISE 8.0f      // the running maximum follows the true one at this distance at most
+
+// Time stamps of one block's life, for measurement builds only (-DBC_APT_TRACE; compiled out
+// otherwise): the block (0, trace_y, 0) writes clock64() values, [page][what], what 0-7 by the
+// MMA thread (0 P of tile 0 seen, 1 its product issued, 2 P of tile 1 seen, 3 its product issued,
+// 4 the page after next seen, 5 its scores issued), 8-15 by the first softmax warp of tile 0
+// (8 scores seen, 9 read out of TMEM, 10 maximum known, 11 the product before seen, 12 P written
+// and handed over).
+#ifdef BC_APT_TRACE
+__device__ long long* g_apt_trace = nullptr;
+__device__ int g_apt_trace_y = 0;
+extern "C" int bc_attention_prefill_tc_set_trace(long long* buf, int y) {
+    cudaError_t e = cudaMemcpyToSymbol(g_apt_trace, &buf, sizeof(buf));
+    if (e == cudaSuccess) e = cudaMemcpyToSymbol(g_apt_trace_y, &y, sizeof(y));
+    return (int)e;
+}
+#define APT_STAMP(page, what) do { if (g_apt_trace && blockIdx.x == 0 && (int)blockIdx.y == g_apt_trace_y && blockIdx.z == 0 && (page) < 64) g_apt_trace[(page) * 16 + (what)] = clock64(); } while (0)
+#else
+#define APT_STAMP(page, what)
+#endif
 
 // NT query tiles a block (1 or 2).  Two tiles share every page of keys and values, and their
 // two groups of softmax warps give every SM sub-partition two warps to switch between while
@@ -47,11 +81,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                             const int* __restrict__ seq_slot, const int* __restrict__ seq_start, bf16* __restrict__ out, int H, int G,
                             int max_pages, int n_pages, int window, float scale_log2) {
     constexpr int THREADS = 64 + NT * 128;
-    constexpr int STAGES = 4;
-    // Two P tiles a query tile let the softmax of page j + 1 write while the product of page j
-    // reads; with two query tiles of head size 128 shared memory has room for one only, and
-    // the softmax then waits for that product (the fourth stage of pages is worth more).
-    constexpr int PB = (D == 128 && NT == 2) ? 1 : 2;
+    constexpr int STAGES = APT_STAGES(D, NT);
+    // P in shared memory only (APT_P_TMEM 0): two P tiles a query tile let the softmax of page
+    // j + 1 write while the product of page j reads; with two query tiles of head size 128 shared
+    // memory has room for one only, and the softmax then waits for that product.
+    constexpr int PB = APT_PB(D, NT);
     constexpr int DB = D / 64;                         // 64-element blocks of the head size
     constexpr int ROW_BLOCK = APT_ROWS * 128;          // bytes of a [128 rows][64 elements] block
     constexpr int KV_BLOCK = BC_PAGE * 128;            // bytes of a [64 positions][64 elements] block
@@ -160,15 +194,21 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         if (lane == 0) {
             constexpr uint32_t idesc_s = instr_desc_b(BC_PAGE, false);   // S: N = 64 positions, keys k-major
             constexpr uint32_t idesc_o = instr_desc_b(D, true);          // O: N = head size, values n-major
-            const uint32_t q_addr = smem_u32(q_smem);
+            // The operand descriptors are worked out once; an address further on is the descriptor
+            // plus that many 16-byte units, so that a product costs its issuing thread an addition
+            // or two (this one thread issues every product of the block: what it spends between
+            // two of them, the tensor core waits).
+            const uint64_t q_desc0 = smem_desc(smem_u32(q_smem));
+            const uint64_t k_desc0 = smem_desc(smem_u32(kv_smem));
+            const uint64_t v_desc0 = smem_desc_mn(smem_u32(kv_smem) + DB * KV_BLOCK, KV_BLOCK);
             auto scores = [&](int j) {   // S[t][j & 1] = Q_t K(j)^T for every query tile t
-                const uint32_t k_addr = smem_u32(kv_smem + (size_t)(j % STAGES) * STAGE_BYTES);
+                const uint64_t k_desc = k_desc0 + (uint64_t)((j % STAGES) * (STAGE_BYTES >> 4));
 #pragma unroll
                 for (int t = 0; t < NT; t++) {
 #pragma unroll
                     for (int kk = 0; kk < D / 16; kk++)
-                        mma_bf16(tmem + (2 * t + (j & 1)) * BC_PAGE, smem_desc(q_addr + (kk >> 2) * NT * ROW_BLOCK + t * ROW_BLOCK) + 2 * (kk & 3),
-                                 smem_desc(k_addr + (kk >> 2) * KV_BLOCK) + 2 * (kk & 3), idesc_s, kk != 0);
+                        mma_bf16(tmem + (2 * t + (j & 1)) * BC_PAGE, q_desc0 + (uint64_t)((((kk >> 2) * NT + t) * ROW_BLOCK >> 4) + 2 * (kk & 3)),
+                                 k_desc + (uint64_t)(((kk >> 2) * KV_BLOCK >> 4) + 2 * (kk & 3)), idesc_s, kk != 0);
                     mma_commit(s_full(t, j & 1));
                 }
             };
@@ -180,17 +220,27 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 scores(j);
             }
             for (int j = 0; j < n_tiles && ok; j++) {
-                const uint32_t v_addr = smem_u32(kv_smem + (size_t)(j % STAGES) * STAGE_BYTES + DB * KV_BLOCK);
+                const uint64_t v_desc = v_desc0 + (uint64_t)((j % STAGES) * (STAGE_BYTES >> 4));   // 16 positions on: 2048 bytes
 #pragma unroll
                 for (int t = 0; t < NT; t++) {
                     ok = ok && mbar_wait(p_full(t, j & 1), (j >> 1) & 1, 4);
                     if (!ok) break;
+                    APT_STAMP(j, 2 * t);
                     tc_fence_after();
+#if APT_P_TMEM
+                    // P lies over the first 32 columns of the scores it came from: 8 columns a k-step of 16 positions.
+#pragma unroll
+                    for (int kk = 0; kk < BC_PAGE / 16; kk++)
+                        mma_bf16_a_tmem(tmem + O_COL + t * D, tmem + (2 * t + (j & 1)) * BC_PAGE + 8 * kk, v_desc + (uint64_t)(kk * (2048 >> 4)), idesc_o,
+                                        (j | kk) != 0);
+#else
                     const uint32_t p_addr = smem_u32(p_smem + (PB * t + (j & (PB - 1))) * ROW_BLOCK);
 #pragma unroll
                     for (int kk = 0; kk < BC_PAGE / 16; kk++)
-                        mma_bf16(tmem + O_COL + t * D, smem_desc(p_addr) + 2 * kk, smem_desc_mn(v_addr + kk * 2048, KV_BLOCK), idesc_o, (j | kk) != 0);
+                        mma_bf16(tmem + O_COL + t * D, smem_desc(p_addr) + 2 * kk, v_desc + (uint64_t)(kk * (2048 >> 4)), idesc_o, (j | kk) != 0);
+#endif
                     mma_commit(o_done(t, j & 1));
+                    APT_STAMP(j, 2 * t + 1);
                 }
                 if (!ok) break;
                 mma_commit(kv_empty0 + 8 * (j % STAGES));
@@ -198,8 +248,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                     const int s = (j + 2) % STAGES;
                     ok = mbar_wait(kv_full0 + 8 * s, ((j + 2) / STAGES) & 1, 5);
                     if (!ok) break;
+                    APT_STAMP(j, 4);
                     tc_fence_after();
                     scores(j + 2);
+                    APT_STAMP(j, 5);
                 }
             }
         }
@@ -221,11 +273,13 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             if (lane == 0) ok = mbar_wait(s_full(t, j & 1), (j >> 1) & 1, 6);
             ok = __shfl_sync(0xffffffffu, ok, 0);
             if (!ok) break;
+            if (warp == 2 && lane == 0) APT_STAMP(j, 8);
             tc_fence_after();
             uint32_t sv[64];
 #pragma unroll
             for (int c = 0; c < 4; c++) tmem_load16(lane_base + (2 * t + (j & 1)) * BC_PAGE + 16 * c, sv + 16 * c);
             tmem_load_wait();
+            if (warp == 2 && lane == 0) APT_STAMP(j, 9);
             const int tile = t_begin + j;
             const bool page_ok = page_at(j) >= 0;
             // A page that ends at or before the position of this warp's first row is seen whole
@@ -259,18 +313,21 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 m_used = m_true;
                 l *= corr;
             }
-            if (j >= PB) {
+            if (warp == 2 && lane == 0) APT_STAMP(j, 10);
+            if (j >= (APT_P_TMEM ? 2 : PB)) {
                 // The P tile written below was last read by the product of page j - PB (with two
                 // P tiles: done long ago as a rule, the scores of page j were issued after it).
                 // Waiting for every phase in order also keeps the parities apart: a parity tells
                 // two phases apart, not more.
-                if (lane == 0) ok = mbar_wait(o_done(t, (j - PB) & 1), ((j - PB) >> 1) & 1, 7);
+                constexpr int BACK = APT_P_TMEM ? 2 : PB;   // in TMEM, P lies over the scores of the page two before: that product is long done
+                if (lane == 0) ok = mbar_wait(o_done(t, (j - BACK) & 1), ((j - BACK) >> 1) & 1, 7);
                 ok = __shfl_sync(0xffffffffu, ok, 0);
                 if (!ok) break;
             }
+            if (warp == 2 && lane == 0) APT_STAMP(j, 11);
             if (j > 0 && __any_sync(0xffffffffu, raise)) {
                 // Rescale this warp's rows of the accumulator, once every product issued so far is in it.
-                if (PB == 2) {
+                if (PB != 1) {
                     if (lane == 0) ok = mbar_wait(o_done(t, (j - 1) & 1), ((j - 1) >> 1) & 1, 9);
                     ok = __shfl_sync(0xffffffffu, ok, 0);
                     if (!ok) break;
@@ -292,6 +349,24 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             // the exponentials' sums kept in four pairs, so that no chain of additions is longer than 8.
             const uint64_t scale2 = pack_f32x2(scale_log2, scale_log2), shift2 = pack_f32x2(-base, -base);
             uint64_t sums[4] = {0ull, 0ull, 0ull, 0ull};
+#if APT_P_TMEM
+            // P goes back into tensor memory, two bf16 a column, over the scores just read (this
+            // thread's own lane): the product reads it there as its A operand.
+            const uint32_t p_addr = lane_base + (2 * t + (j & 1)) * BC_PAGE;
+#pragma unroll
+            for (int c16 = 0; c16 < 2; c16++) {
+                uint32_t packed[16];
+#pragma unroll
+                for (int i = 0; i < 16; i++) {
+                    float a, b;
+                    unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(sv[c16 * 32 + 2 * i]), __uint_as_float(sv[c16 * 32 + 2 * i + 1])), scale2, shift2), a, b);
+                    a = fast_exp2(a), b = fast_exp2(b);
+                    sums[i & 3] = add_f32x2(sums[i & 3], pack_f32x2(a, b));
+                    packed[i] = pack_bf16(a, b);
+                }
+                tmem_store16(p_addr + 16 * c16, packed);
+            }
+#else
             uint8_t* p_row = p_smem + (PB * t + (j & (PB - 1))) * ROW_BLOCK + (32 * q + lane) * 128;
 #pragma unroll
             for (int c8 = 0; c8 < 8; c8++) {
@@ -306,6 +381,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 }
                 *reinterpret_cast<uint4*>(p_row + ((c8 ^ (lane & 7)) << 4)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
             }
+#endif
             {
                 float s0, s1, s2, s3;
                 unpack_f32x2(add_f32x2(sums[0], sums[1]), s0, s1);
@@ -325,9 +401,15 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                     *reinterpret_cast<uint4*>(v_tile + (within >> 3) * KV_BLOCK + vrow * 128 + (within & 7) * 16) = make_uint4(0u, 0u, 0u, 0u);
                 }
             }
+#if APT_P_TMEM
+            if (t == 0 && first_bad < BC_PAGE) fence_proxy_async();   // the cleared value rows, for the tensor core's reads
+            tmem_store_wait();
+#else
             fence_proxy_async();
+#endif
             tc_fence_before();
             mbar_arrive(p_full(t, j & 1));
+            if (warp == 2 && lane == 0) APT_STAMP(j, 12);
         }
         // The output: the accumulator over this row's sum.
         if (ok) {
@@ -385,8 +467,9 @@ static int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMa
                   const int* seq_slot, const int* seq_start, void* out, int seqs, int max_new, int H, int G, int max_pages, int n_pages,
                   int window, float scale, cudaStream_t s) {
     constexpr int DB = D / 64;
-    constexpr int STAGES = 4, PB = (D == 128 && NT == 2) ? 1 : 2;
+    constexpr int STAGES = APT_STAGES(D, NT), PB = APT_PB(D, NT);
     constexpr int SMEM = DB * NT * APT_ROWS * 128 + NT * PB * APT_ROWS * 128 + STAGES * 2 * DB * BC_PAGE * 128 + 1024;
+    static_assert(SMEM <= APT_SMEM_LIMIT, "the ring does not fit");
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel<D, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
