@@ -27,17 +27,35 @@
 
 namespace cg = cooperative_groups;
 
-#define AD_THREADS 128
+#define AD_THREADS 128            // the threads that compute: four warps, each 16 of a page's 64 positions
+#define AD_THREADS_TMA 160        // with pages by TMA a fifth warp asks for them (one thread of it)
 #define AD_STAGES 3
 #define AD_MAX_GROUP 16
+#define AD_PAGES_KEPT 256   // page numbers a block keeps in shared memory (it looks up the rest one by one)
 #define AD_MAX_CLUSTER 16    // splits that merge through one another's shared memory (more than 8: not portable, asked for per kernel)
 
 // Byte offset of 16-byte chunk c of row r in a page as TMA writes it: blocks of [64 rows][64
 // elements] with the 128-byte swizzle (chunk xor row within each 128-byte row).
 __device__ __forceinline__ int tma_tile_offset(int r, int c) { return (c >> 3) * 8192 + r * 128 + (((c & 7) ^ (r & 7)) << 4); }
 
+// Clock stamps of the block (0, 0, 0), for measurement builds only (-DBC_AD_TRACE; compiled out
+// otherwise): [0..15] the block's life (0 entry, 1 first pages asked for, 2 the kernel before is
+// done, 3 query rotated, 4 pages done, 5 warps merged, 6 after the cluster's first barrier, 7
+// outputs written, 8 end), then six a page from [16] on (top, page there, next page asked for,
+// scores, softmax, product).
+#ifdef BC_AD_TRACE
+__device__ long long* g_ad_trace = nullptr;
+extern "C" int bc_attention_decode_set_trace(long long* buf) { return (int)cudaMemcpyToSymbol(g_ad_trace, &buf, sizeof(buf)); }
+#define AD_STAMP(at) do { if (g_ad_trace && threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (at) < 400) g_ad_trace[at] = clock64(); } while (0)
+#else
+#define AD_STAMP(at)
+#endif
+
+// The four computing warps among themselves (the fifth warp, where there is one, is not part of it).
+__device__ __forceinline__ void ad_workers_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
 template <int D, bool TMA>
-__global__ void __launch_bounds__(AD_THREADS)
+__global__ void __launch_bounds__(TMA ? AD_THREADS_TMA : AD_THREADS)
 attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, const bf16* __restrict__ q, int q_stride, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
                         const int* __restrict__ page_table, const int* __restrict__ row_pos, const int* __restrict__ row_slot,
                         bf16* __restrict__ out, float* __restrict__ scratch, int* __restrict__ counters, int H, int G, int max_pages,
@@ -50,18 +68,22 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);   // TMA's swizzle wants 1024-byte alignment
     __shared__ int is_last;
-    __shared__ __align__(8) uint64_t full_bars[AD_STAGES];
+    __shared__ int page_ids[AD_PAGES_KEPT];   // the pages of this block's first tiles (-1: none)
+    __shared__ __align__(8) uint64_t full_bars[AD_STAGES], empty_bars[AD_STAGES];
     auto offset = [](int r, int c) { return TMA ? tma_tile_offset(r, c) : tile_offset<D>(r, c); };
-    const uint32_t full0 = smem_u32(&full_bars[0]);
+    const uint32_t full0 = smem_u32(&full_bars[0]), empty0 = smem_u32(&empty_bars[0]);
     if (TMA && threadIdx.x == 0) {
-        for (int s = 0; s < AD_STAGES; s++) mbar_init(full0 + 8 * s, 1);
+        for (int s = 0; s < AD_STAGES; s++) {
+            mbar_init(full0 + 8 * s, 1);    // the asking thread, with the bytes that are to come
+            mbar_init(empty0 + 8 * s, 4);   // one thread of each computing warp: done with the stage
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (TMA) __syncthreads();
 
     // Slots, positions and page tables are in place before the step starts, and the pages read
     // here were written by earlier steps: the first pages are asked for before the wait for
     // the preceding kernel (which makes this row's q, k and v).  Nothing is written before it.
+    AD_STAMP(0);
     pdl_launch_dependents();
     const int split = blockIdx.x, n_splits = gridDim.x, g = blockIdx.y, r = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -85,15 +107,24 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
 
     // A tile without a page (behind a window, or past what the sequence holds) is neither
     // fetched nor multiplied: what another sequence left in some page never meets this row.
-    auto page_of = [&](int tile) {
+    // The block's page numbers are fetched once, all at a time, not one by one inside the page
+    // loop, where each would cost a trip to global memory.
+    for (int i = threadIdx.x; i < min(n_tiles, AD_PAGES_KEPT); i += blockDim.x) {
+        const int tile = t_begin + i;
+        const int page = tile < max_pages ? pages[tile] : -1;
+        page_ids[i] = page >= 0 && page < n_pages ? page : -1;
+    }
+    __syncthreads();   // the page numbers, and the barriers set up above (every thread of the block, the asking warp too)
+    auto page_of = [&](int tile) {   // of one of this block's tiles
+        const int i = tile - t_begin;
+        if (i < AD_PAGES_KEPT) return page_ids[i];
         const int page = tile < max_pages ? pages[tile] : -1;
         return page >= 0 && page < n_pages ? page : -1;
     };
     auto load_tile = [&](int tile, int stage) {
         const int page = page_of(tile);
         const uint32_t kb = ad_smem(smem + (size_t)stage * 2 * TILE_BYTES), vb = kb + TILE_BYTES;
-        if (TMA) {
-            if (threadIdx.x != 0) return;
+        if (TMA) {   // called by the asking thread alone
             if (page < 0) {
                 mbar_arrive(full0 + 8 * stage);   // nothing comes: the stage's phase ends at once
                 return;
@@ -124,13 +155,38 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
     // the copy in shared memory by hand; where a kernel before this one wrote them, the page
     // is fetched after the wait for that kernel.
     const bool appends = fuse == 2 && n_tiles > 0 && t_end == end_tile;
-    int asked = 0;   // stages of the first ring asked for so far, in order
-    for (; asked < AD_STAGES - 1; asked++) {
-        if (fuse != 2 && t_begin + asked == end_tile - 1) break;
-        if (asked < n_tiles) load_tile(t_begin + asked, asked);
-        if (!TMA) cp_async_commit();
+    if (TMA && warp == 4) {
+        // The asking warp: one thread of it asks for page after page, as far ahead as the ring has
+        // stages, each as soon as the four computing warps have let go of the stage.  (Asked for
+        // by a computing thread, a page costs that thread's warp some 450 clocks of the 1,750
+        // that a page takes, and the other warps wait for it at the block's barrier: measured.)
+        if (lane == 0) {
+            for (int it = 0; it < n_tiles; it++) {
+                const int stage = it % AD_STAGES;
+                if (it >= AD_STAGES && !mbar_wait(empty0 + 8 * stage, ((it / AD_STAGES) & 1) ^ 1, 2)) break;
+                if (fuse != 2 && t_begin + it == end_tile - 1) pdl_wait();   // the row's own page: written by the kernel before this one
+                load_tile(t_begin + it, stage);
+            }
+        }
+        __syncwarp();
+        // It takes no part in the merges, but in the cluster's barriers it must (they count every thread).
+        if (n_splits > 1 && use_cluster) {
+            cg::cluster_group cl = cg::this_cluster();
+            cl.sync();
+            cl.sync();
+        }
+        return;
     }
+    int asked = 0;   // by cp.async: stages of the first ring asked for so far, in order
+    if (!TMA)
+        for (; asked < AD_STAGES - 1; asked++) {
+            if (fuse != 2 && t_begin + asked == end_tile - 1) break;
+            if (asked < n_tiles) load_tile(t_begin + asked, asked);
+            cp_async_commit();
+        }
+    AD_STAMP(1);
     pdl_wait();
+    AD_STAMP(2);
 
     // Q fragments: row i of the tile is head g * group + i (zero past the group).
     uint32_t qf[KD][4];
@@ -181,11 +237,13 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
                 }
         }
     }
-    for (; asked < AD_STAGES - 1; asked++) {
-        if (asked < n_tiles) load_tile(t_begin + asked, asked);
-        if (!TMA) cp_async_commit();
-    }
+    if (!TMA)
+        for (; asked < AD_STAGES - 1; asked++) {
+            if (asked < n_tiles) load_tile(t_begin + asked, asked);
+            cp_async_commit();
+        }
 
+    AD_STAMP(3);
     float o[ND][4];
 #pragma unroll
     for (int i = 0; i < ND; i++) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
@@ -193,21 +251,36 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
 
     bool waits_ok = true;
     for (int it = 0; it < n_tiles; it++) {
+        AD_STAMP(16 + 6 * it);
         if (TMA) {
-            waits_ok = mbar_wait(full0 + 8 * (it % AD_STAGES), (it / AD_STAGES) & 1, 1);
-            if (__syncthreads_or(!waits_ok)) {   // also: everybody is done with the stage that is filled next
-                waits_ok = false;
-                break;
-            }
+            // Every thread sees the page arrive for itself; a warp goes on or gives up as one.  A
+            // warp that has given up (its wait ran out: recorded) still walks through the pages
+            // without working, so that the others find it at the barrier of the last page.
+            if (waits_ok) waits_ok = mbar_wait(full0 + 8 * (it % AD_STAGES), (it / AD_STAGES) & 1, 1);
+            waits_ok = __all_sync(0xffffffffu, waits_ok);
         } else {
             cp_async_wait<AD_STAGES - 2>();
-            __syncthreads();
+            ad_workers_sync();
         }
-        if (it + AD_STAGES - 1 < n_tiles) load_tile(t_begin + it + AD_STAGES - 1, (it + AD_STAGES - 1) % AD_STAGES);
-        if (!TMA) cp_async_commit();
+        AD_STAMP(16 + 6 * it + 1);
+        if (!TMA) {
+            if (it + AD_STAGES - 1 < n_tiles) load_tile(t_begin + it + AD_STAGES - 1, (it + AD_STAGES - 1) % AD_STAGES);
+            cp_async_commit();
+        }
+        AD_STAMP(16 + 6 * it + 2);
         const int tile = t_begin + it;
         const bool page_ok = page_of(tile) >= 0;
-        if (!page_ok) continue;
+        // This warp is done with the stage once the page's products are issued and read (end of the iteration).
+        auto let_go = [&]() {
+            if (!TMA) return;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(empty0 + 8 * (it % AD_STAGES));
+        };
+        if (!page_ok || !waits_ok) {
+            if (page_ok && tile == end_tile - 1) ad_workers_sync();   // the barrier of the row's own page, below
+            let_go();
+            continue;
+        }
         const uint32_t kb = ad_smem(smem + (size_t)(it % AD_STAGES) * 2 * TILE_BYTES), vb = kb + TILE_BYTES;
         const int key0 = 16 * warp;   // this warp's 16 positions of the page
         if (tile == end_tile - 1) {
@@ -252,7 +325,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
                     *reinterpret_cast<bf16*>(vt + offset(pr, d >> 3) + (d & 7) * 2) = val;
                 }
             }
-            __syncthreads();
+            ad_workers_sync();
         }
 
         float s[2][4] = {};
@@ -264,6 +337,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
             mma_16816(s[0], qf[kd], b0, b1);
             mma_16816(s[1], qf[kd], b2, b3);
         }
+        AD_STAMP(16 + 6 * it + 3);
         // Scores in the log2 domain; positions outside [lo, pos] do not exist for this row.
         float tmax0 = -INFINITY, tmax1 = -INFINITY;
 #pragma unroll
@@ -295,6 +369,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
         l1 = l1 * c1 + (p[0][2] + p[0][3] + p[1][2] + p[1][3]);
         m0 = mn0;
         m1 = mn1;
+        AD_STAMP(16 + 6 * it + 4);
         uint32_t pf[4] = {pack_bf16(p[0][0], p[0][1]), pack_bf16(p[0][2], p[0][3]), pack_bf16(p[1][0], p[1][1]), pack_bf16(p[1][2], p[1][3])};
 #pragma unroll
         for (int nd = 0; nd < ND; nd += 2) {
@@ -306,13 +381,16 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
             mma_16816(o[nd], pf, b0, b1);
             mma_16816(o[nd + 1], pf, b2, b3);
         }
+        let_go();
+        AD_STAMP(16 + 6 * it + 5);
     }
+    AD_STAMP(4);
     if (!TMA) cp_async_wait<0>();
     l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
     l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
-    __syncthreads();
+    ad_workers_sync();
 
     // Merge the four warps (each saw other positions) in the order 0, 1, 2, 3.
     float* wm = reinterpret_cast<float*>(smem);              // [4][16] maxima
@@ -335,7 +413,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
         base[(size_t)(gq + 8) * D] = o[nd][2];
         base[(size_t)(gq + 8) * D + 1] = o[nd][3];
     }
-    __syncthreads();
+    ad_workers_sync();
     // scratch: [row][head][split][D + 2]: the un-normalised sum, then maximum and normaliser.
     const int stride = D + 2;
     for (int i = threadIdx.x; i < group * D; i += AD_THREADS) {
@@ -367,6 +445,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
             }
         }
     }
+    AD_STAMP(5);
     if (n_splits == 1) return;
     // With a cluster, up to eight neighbouring splits merge among themselves first; what is
     // left to merge through scratch memory are the clusters' results (`parts` of them).
@@ -380,6 +459,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
         // the cluster's sum goes to scratch memory as one part).
         cg::cluster_group cl = cg::this_cluster();
         cl.sync();
+        AD_STAMP(6);
         const int crank = split - part * csize;
         const int total = group * D, share = (total + csize - 1) / csize;
         // All reads of the peers' shared memory (a good tenth of a microsecond each) are asked
@@ -424,20 +504,22 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
         };
         if (csize > 8) merge(std::integral_constant<int, AD_MAX_CLUSTER>());
         else merge(std::integral_constant<int, 8>());
+        AD_STAMP(7);
         cl.sync();   // no block may leave while a peer still reads its shared memory
+        AD_STAMP(8);
         if (parts == 1) return;
     }
 
     // The last block of this (row, kv head) to arrive merges the parts in order (every block
     // arrives, also those of a cluster that wrote a share of its part each).
     __threadfence();
-    __syncthreads();
+    ad_workers_sync();
     if (threadIdx.x == 0) {
         const int arrived = atomicAdd(&counters[r * G + g], 1);
         is_last = arrived == n_splits - 1;
         if (is_last) counters[r * G + g] = 0;   // ready for the next launch
     }
-    __syncthreads();
+    ad_workers_sync();
     if (!is_last) return;
     __threadfence();
     for (int i = threadIdx.x; i < group * D; i += AD_THREADS) {
@@ -504,7 +586,7 @@ static int launch_as(const CUtensorMap& mk, const CUtensorMap& mv, const void* q
             if (cudaFuncSetAttribute(attention_decode_kernel<D, TMA>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess) {
                 cudaLaunchConfig_t cfg = {};
                 cfg.gridDim = dim3(16, 1, 1);
-                cfg.blockDim = dim3(AD_THREADS);
+                cfg.blockDim = dim3(TMA ? AD_THREADS_TMA : AD_THREADS);
                 cfg.dynamicSmemBytes = SMEM;
                 cudaLaunchAttribute attr[1];
                 attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -522,12 +604,12 @@ static int launch_as(const CUtensorMap& mk, const CUtensorMap& mv, const void* q
     if (n_splits > 8 && csize < n_splits && !(scratch && counters)) csize = 1;
     const bool clustered = n_splits > 1 && fr.allow_cluster && csize > 1;
     if (clustered)
-        bc_launch_clustered(attention_decode_kernel<D, TMA>, grid, dim3(AD_THREADS), (size_t)SMEM, s, dim3(csize, 1, 1), mk, mv, (const bf16*)q,
+        bc_launch_clustered(attention_decode_kernel<D, TMA>, grid, dim3(TMA ? AD_THREADS_TMA : AD_THREADS), (size_t)SMEM, s, dim3(csize, 1, 1), mk, mv, (const bf16*)q,
                             q_stride, (const bf16*)k_cache, (const bf16*)v_cache, page_table, row_pos, row_slot, (bf16*)out, scratch, counters, H, G,
                             max_pages, n_pages, window, scale * 1.4426950408889634f, (const float2*)fr.cos_sin, fr.pairing, fr.fuse,
                             fr.k_off, fr.v_off, (bf16*)k_cache, (bf16*)v_cache, csize);
     else
-        bc_launch(attention_decode_kernel<D, TMA>, grid, dim3(AD_THREADS), (size_t)SMEM, s, mk, mv, (const bf16*)q, q_stride, (const bf16*)k_cache,
+        bc_launch(attention_decode_kernel<D, TMA>, grid, dim3(TMA ? AD_THREADS_TMA : AD_THREADS), (size_t)SMEM, s, mk, mv, (const bf16*)q, q_stride, (const bf16*)k_cache,
                   (const bf16*)v_cache, page_table, row_pos, row_slot, (bf16*)out, scratch, counters, H, G, max_pages, n_pages, window,
                   scale * 1.4426950408889634f, (const float2*)fr.cos_sin, fr.pairing, fr.fuse, fr.k_off, fr.v_off, (bf16*)k_cache,
                   (bf16*)v_cache, 0);
