@@ -405,13 +405,12 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
         wl[warp * 16 + gq] = l0;
         wl[warp * 16 + gq + 8] = l1;
     }
+    // Only the rows that are heads of the group are read below (4 of the tile's 16 with four heads a kv head): the others are not written.
 #pragma unroll
     for (int nd = 0; nd < ND; nd++) {
         float* base = wo + (size_t)warp * 16 * D + nd * 8 + 2 * tq;
-        base[(size_t)gq * D] = o[nd][0];
-        base[(size_t)gq * D + 1] = o[nd][1];
-        base[(size_t)(gq + 8) * D] = o[nd][2];
-        base[(size_t)(gq + 8) * D + 1] = o[nd][3];
+        if (gq < group) *reinterpret_cast<float2*>(base + (size_t)gq * D) = make_float2(o[nd][0], o[nd][1]);
+        if (gq + 8 < group) *reinterpret_cast<float2*>(base + (size_t)(gq + 8) * D) = make_float2(o[nd][2], o[nd][3]);
     }
     ad_workers_sync();
     // scratch: [row][head][split][D + 2]: the un-normalised sum, then maximum and normaliser.
