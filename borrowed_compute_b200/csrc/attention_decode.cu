@@ -29,7 +29,9 @@ namespace cg = cooperative_groups;
 
 #define AD_THREADS 128            // the threads that compute: four warps, each 16 of a page's 64 positions
 #define AD_THREADS_TMA 160        // with pages by TMA a fifth warp asks for them (one thread of it)
+#ifndef AD_STAGES
 #define AD_STAGES 3
+#endif
 #define AD_MAX_GROUP 16
 #define AD_PAGES_KEPT 256   // page numbers a block keeps in shared memory (it looks up the rest one by one)
 #define AD_MAX_CLUSTER 16    // splits that merge through one another's shared memory (more than 8: not portable, asked for per kernel)
