@@ -186,10 +186,6 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
             if (asked < n_tiles) load_tile(t_begin + asked, asked);
             cp_async_commit();
         }
-    // The row of the rotary table for this position (a new one every step: not in any cache yet)
-    // is asked for before the wait, so that it is there when the query is rotated after it.
-    if (fuse > 0 && cos_sin != nullptr && threadIdx.x * 128 < (D / 2) * (int)sizeof(float2))
-        asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const char*>(cos_sin + (size_t)pos * (D / 2)) + threadIdx.x * 128));
     AD_STAMP(1);
     pdl_wait();
     AD_STAMP(2);
