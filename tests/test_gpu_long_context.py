@@ -28,11 +28,12 @@ FAR, NEAR = 300, 16450            # the fifth page and the 258th
 MARK_FAR, MARK_NEAR, ASKS = 7, 8, 11   # the tokens that are found and the token that looks for them
 
 CONFIGS = {
-    # head size 32: pages by cp.async, the mma.sync prompt kernel
+    # head size 32: pages by cp.async, the mma.sync prompt kernel; a sequence may grow to 24,576 positions, for which
+    # a decode step is cut into 64 splits (clusters of eight, their sums through scratch memory)
     "head32": {"architectures": ["LlamaForCausalLM"], "num_hidden_layers": 1, "hidden_size": 128, "num_attention_heads": 4,
                "num_key_value_heads": 2, "intermediate_size": 200, "vocab_size": 301, "rope_theta": 500000.0,
-               "rms_norm_eps": 1e-5, "max_position_embeddings": 20480},
-    # head size 64: pages by TMA, the tcgen05 prompt kernel
+               "rms_norm_eps": 1e-5, "max_position_embeddings": 24576},
+    # head size 64: pages by TMA, the tcgen05 prompt kernel; up to 20,480 positions: sixteen splits, one cluster of sixteen
     "head64": {"architectures": ["LlamaForCausalLM"], "num_hidden_layers": 1, "hidden_size": 192, "num_attention_heads": 3,
                "num_key_value_heads": 1, "head_dim": 64, "intermediate_size": 264, "vocab_size": 259, "rope_theta": 500000.0,
                "rms_norm_eps": 1e-6, "max_position_embeddings": 20480,
@@ -85,9 +86,10 @@ def test_a_sequence_of_seventeen_thousand_positions(name, tmp_path):
         stored = weights_as_stored(w, dtype)
         ref = plain_llama.logits(cfg, stored, t, only=wanted)
         folder = write_folder(str(tmp_path / dtype), cfg, w, dtype)
-        eng = Engine.from_folder(folder, dtype=dtype, max_tokens=LENGTH + 64, max_slots=1, max_seq=cfg["max_position_embeddings"])
+        eng = Engine.from_folder(folder, dtype=dtype, max_tokens=cfg["max_position_embeddings"], max_slots=1, max_seq=cfg["max_position_embeddings"])
         if dtype == "bfloat16":
-            assert ops.attention_decode_splits(1, cfg["num_key_value_heads"], eng.cache.slots.max_pages) > 8
+            splits = ops.attention_decode_splits(1, cfg["num_key_value_heads"], eng.cache.slots.max_pages)
+            assert splits == (64 if name == "head32" else 16), "the split counts this test is meant to run"
         s = eng.acquire()
         got = []
         cuts = [0, 8192, 16384, PROMPT - 40, PROMPT]                   # the last piece of the prompt is read row by row
