@@ -288,6 +288,7 @@ def sm_count() -> int:
 
 _tc_workspace = {}
 _TC_FILL = float(os.environ.get("BC_B200_TC_FILL", "2"))      # measurement knobs: blocks an SM a split product aims at,
+_SWIGLU_SPLIT = os.environ.get("BC_B200_SWIGLU_SPLIT", "1") == "1"
 _TC_MIN_K = int(os.environ.get("BC_B200_TC_MIN_K", "8"))       # and the fewest k-steps of 64 a split keeps
 TC_SCRATCH_FLOATS = 148 * 256 * 256   # split-K partial tiles: a capacity of 37 MiB (148 tiles of 256 x 256 floats), whatever the device
 
@@ -325,7 +326,12 @@ def gemm_tc_splits(T: int, N: int, K: int, epilogue: int) -> int:
     fits = TC_SCRATCH_FLOATS // (tiles * accs * rows * bn)   # splits whose partial tiles fit the scratch
     if epilogue == EPI_SWIGLU:
         # The kernel can split SwiGLU (the gate is applied to the full sums), but measured on the
-        # 8B shapes two half-depth blocks an SM stream slower than one full-depth block: unsplit.
+        # 8B shapes two half-depth blocks an SM stream slower than one full-depth block: unsplit,
+        # unless the tiles are so few that they leave half of the SMs or more without a block
+        # (a feed-forward width of 8,192 is 64 tiles): then one block an SM.
+        if bn <= 64 and tiles * 2 <= sms and _SWIGLU_SPLIT:
+            s = max(1, min(sms // tiles, -(-K // 64) // _TC_MIN_K, 8, fits))   # two blocks an SM measured slower here too
+            return 1 << (s.bit_length() - 1)
         return 1
     if bn <= 64:
         # Few tokens: the product streams weights, two blocks fit an SM, and measured rates keep
