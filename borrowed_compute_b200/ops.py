@@ -289,7 +289,7 @@ def sm_count() -> int:
 _tc_workspace = {}
 _TC_FILL = float(os.environ.get("BC_B200_TC_FILL", "2"))      # measurement knobs: blocks an SM a split product aims at,
 _SWIGLU_SPLIT = os.environ.get("BC_B200_SWIGLU_SPLIT", "1") == "1"
-_TC_MIN_K = int(os.environ.get("BC_B200_TC_MIN_K", "8"))       # and the fewest k-steps of 64 a split keeps
+_TC_MIN_K = int(os.environ.get("BC_B200_TC_MIN_K", "4"))       # and the fewest k-steps of 64 a split keeps
 TC_SCRATCH_FLOATS = 148 * 256 * 256   # split-K partial tiles: a capacity of 37 MiB (148 tiles of 256 x 256 floats), whatever the device
 
 
@@ -317,7 +317,8 @@ def _tc_tiling(T: int, N: int, epilogue: int):
 
 def gemm_tc_splits(T: int, N: int, K: int, epilogue: int) -> int:
     """How many ways to split K so that a product with few weight tiles still fills the
-    device's SMs: as many as fit, each at least 8 k-steps of 64."""
+    device's SMs: as many as fit, each at least 4 k-steps of 64 (8 measured 3 % slower on the
+    3B shape, whose products of K = 3,072 then stopped at 4 splits, and 0.6 % on the 8B shape)."""
     bn, rows, tiles = _tc_tiling(T, N, epilogue)
     if tiles == 0:
         return 1
@@ -335,7 +336,7 @@ def gemm_tc_splits(T: int, N: int, K: int, epilogue: int) -> int:
         return 1
     if bn <= 64:
         # Few tokens: the product streams weights, two blocks fit an SM, and measured rates keep
-        # rising up to about two blocks an SM as long as a split still has 8 k-steps of 64.
+        # rising up to about two blocks an SM as long as a split still has a few k-steps of 64.
         s = max(1, min(int(_TC_FILL * sms) // tiles, -(-K // 64) // _TC_MIN_K, 16, fits))
         # Up to eight splits add up inside a thread-block cluster, which saves the trip through
         # scratch memory; clusters of 2, 4 or 8 place well on the SMs, other sizes measured
