@@ -92,13 +92,13 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
     const int gq = lane >> 2, tq = lane & 3;
     const int group = H / G;
     const int slot = row_slot[r];
+    const int pos = row_pos[r];   // asked for together with the slot: one trip to global memory instead of two in a row
     if (slot < 0) {
         pdl_wait();
         if (split == 0)
             for (int i = threadIdx.x; i < group * D; i += AD_THREADS) out[((size_t)r * H + (size_t)g * group) * D + i] = __float2bfloat16_rn(0.0f);
         return;
     }
-    const int pos = row_pos[r];
     const int lo = window > 0 && pos + 1 > window ? pos + 1 - window : 0;
     const int first_tile = lo / BC_PAGE, end_tile = pos / BC_PAGE + 1;
     const int per_split = (end_tile - first_tile + n_splits - 1) / n_splits;
