@@ -62,3 +62,23 @@ def test_the_rotary_part_scales_frequencies_as_the_plain_implementation_does():
     with pytest.raises(ValueError, match="inconsistent"):
         inverse_frequencies(32, 1e4, {"rope_type": "llama3", "factor": 2.0, "low_freq_factor": 4.0, "high_freq_factor": 1.0,
                                       "original_max_position_embeddings": 64})
+
+
+def test_how_the_decode_attention_is_cut_into_splits(monkeypatch):
+    """The split counts that were measured best on 148 SMs, pinned: few blocks are cut until they
+    fill the SMs, by powers of two up to a cluster of eight; one sequence of eight kv heads
+    takes a cluster of sixteen from 64 pages on; beyond 192 pages (320 where sixteen serve)
+    clusters of eight whose sums go through scratch memory.  (Pages are 64 positions.)"""
+    from borrowed_compute_b200 import ops
+
+    monkeypatch.setattr(ops, "sm_count", lambda: 148)
+    splits = ops.attention_decode_splits
+    assert splits(64, 8, 33) == 1 and splits(16, 8, 33) == 2 and splits(8, 8, 33) == 4     # 512, 128 and 64 blocks before cutting
+    assert splits(5, 8, 33) == 4 and splits(7, 8, 33) == 4                                  # 7 and 5 would fill better but place badly
+    assert splits(1, 8, 33) == 8 and splits(1, 8, 64) == 8                                  # one sequence of up to 4,096 positions
+    assert splits(1, 8, 128) == 16 and splits(1, 8, 320) == 16                              # 8,192 to 20,480: one cluster of sixteen
+    assert splits(1, 8, 512) == 32 and splits(1, 8, 2048) == 32                             # beyond: four clusters of eight
+    assert splits(2, 8, 128) == 8 and splits(2, 8, 512) == 16                               # two sequences: sixteen blocks before cutting
+    assert splits(4, 8, 512) == 8                                                           # 32 blocks: eight fill the SMs
+    assert splits(1, 8, 3) == 2 and splits(1, 1, 1) == 1                                    # never more than the pages
+    assert splits(16, 40, 18) == 1                                                          # every head its own keys: 640 blocks
